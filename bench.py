@@ -1,0 +1,414 @@
+"""Benchmark of the Binade hot path on B200: load-time Rice->R4 expansion and the batch-1 fused
+R4-decode matvec on 12B-class shapes (seven projection matrices of one decoder layer).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+One step = one token's seven matvecs (q, k, v, o, gate, up, down) over weights resident in HBM
+in the R4 layout. Steps rotate over several copies of the weights so that no step finds its
+weights in L2 (one copy is 338 MB, L2 is 126 MB). The metric is the compressed bytes the
+kernels stream per second. The last stdout line is one JSON object; see DESIGN.md for the keys.
+
+With N > 1 (launched by torch.distributed.run, one rank per GPU) every rank holds its own row
+shard of an N-times taller layer (same per-GPU work: weak scaling) and all-gathers each
+projection's output over NCCL inside the timed step.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import time
+from pathlib import Path
+
+import numpy as np
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+SHAPES = [("q", 4096, 3840), ("k", 2048, 3840), ("v", 2048, 3840), ("o", 3840, 4096), ("gate", 15360, 3840), ("up", 15360, 3840), ("down", 3840, 15360)]
+WORKLOAD = "config2: Rice->R4 expansion + batch-1 fused R4 matvec, 7 matrices of a 12B-class layer (q 4096x3840, k/v 2048x3840, o 3840x4096, gate/up 15360x3840, down 3840x15360), N(0,0.02) BF16 with 0.1% x64 outliers, x ~ N(0,1)"
+METRIC, UNIT = "r4_matvec_hbm_gbs", "GB/s"
+NOMINAL_HBM_GBS = 8000.0
+
+
+def synthetic_weight(name: str, n: int, k: int, seed_base: int = 0) -> np.ndarray:
+    """BF16 words [n, k]: N(0, 0.02), 0.1 % of entries scaled x64, seeded per matrix."""
+    import torch
+
+    seed = seed_base * 1000 + sum(ord(c) for c in name) + n + k
+    g = torch.Generator().manual_seed(seed)
+    w = torch.randn((n, k), generator=g) * 0.02
+    w = torch.where(torch.rand((n, k), generator=g) < 1e-3, w * 64, w)
+    return w.to(torch.bfloat16).view(torch.int16).numpy().view(np.uint16)
+
+
+def synthetic_input(k: int, seed: int) -> np.ndarray:
+    import torch
+
+    g = torch.Generator().manual_seed(77 + seed)
+    return torch.randn(k, generator=g).to(torch.bfloat16).view(torch.int16).numpy().view(np.uint16)
+
+
+def measured_peaks() -> dict:
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return {"hbm_gbs": float(d["hbm_gbs"]), "source": "measured (MEASURED_PEAKS.json)"}
+    return {"hbm_gbs": 6650.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """nvidia-smi in the background during the timed region (reads settings, changes none)."""
+
+    FIELDS = "index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap"
+
+    def __init__(self, gpu: int):
+        self.gpu, self.proc, self.path = gpu, None, None
+
+    def __enter__(self):
+        try:
+            f = tempfile.NamedTemporaryFile("w", suffix=".csv", delete=False)
+            self.path = f.name
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "50", "-i", str(self.gpu)], stdout=f, stderr=subprocess.DEVNULL)
+        except OSError:
+            self.proc = None
+        return self
+
+    def __exit__(self, *exc):
+        if self.proc:
+            time.sleep(0.12)
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+
+    def summary(self) -> dict:
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        if not self.path or not os.path.exists(self.path):
+            return out
+        sm, mx, reasons = [], [], set()
+        for line in Path(self.path).read_text().splitlines():
+            f = [s.strip() for s in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        os.unlink(self.path)
+        if sm:
+            out.update(sm_mhz=float(np.median(sm)), sm_max_mhz=max(mx), reasons=sorted(reasons), samples=len(sm))
+        return out
+
+
+# ----------------------------------------------------------------------------- CPU arm
+def cpu_r4_layer(seed_base: int, names=None):
+    """The layer's R4 arrays built on the host by the oracle (for the CPU arms only)."""
+    from oracle import oracle as o
+
+    mats = []
+    for name, n, k in SHAPES:
+        if names and name not in names:
+            continue
+        a = o.pack_r4(synthetic_weight(name, n, k, seed_base))
+        mats.append((name, n, k, a, sum(a[key].nbytes for key in ("raw", "codes", "flags", "esc", "table", "row_esc")) + 2 * k + 2 * n))
+    return mats
+
+
+def cpu_step(mats, xs, frac: float = 1.0):
+    """One CPU step over the first `frac` of every matrix's rows; returns the bytes it streamed."""
+    from oracle import oracle as o
+
+    z = np.zeros(1, np.uint32)
+    done = 0
+    for _, n, k, a, nbytes in mats:
+        rows = max(1, int(n * frac))
+        o.c_r4_gather(a, xs[k], z, z, rows, k, 0, 0)
+        done += nbytes * rows / n
+    return done
+
+
+def cpu_cores() -> int:
+    return len(os.sched_getaffinity(0))
+
+
+def run_reference(args) -> dict:
+    """The CPU arm: the oracle's C restatement of the same step on all host threads. The
+    reference project has no CPU matvec (its CPU code is the numpy codec) and its GPU kernels
+    need MLX, which this box lacks, so the C port of its kernel semantics stands in. Each step
+    covers the same fraction of every matrix's rows, sized so the run ends within about a minute."""
+    mats = cpu_r4_layer(0)
+    xs = {k: synthetic_input(k, 0) for k in {k for _, _, k in SHAPES}}
+    t0 = time.perf_counter()
+    cpu_step(mats, xs, 1 / 32)
+    full = (time.perf_counter() - t0) * 32
+    frac = min(1.0, 60.0 / (full * (args.steps + args.warmup)))
+    for _ in range(args.warmup):
+        cpu_step(mats, xs, frac)
+    t0, done = time.perf_counter(), 0.0
+    for _ in range(args.steps):
+        done += cpu_step(mats, xs, frac)
+    dt = time.perf_counter() - t0
+    val = done / dt / 1e9
+    base = {"value": val, "unit": UNIT, "cores": cpu_cores(), "kind": "port", "sample": f"every step: the first {frac:.4f} of the rows of each of the 7 matrices, C oracle with OpenMP over rows"}
+    return {
+        "impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16 weights (R4 coded), fp32 accumulate",
+        "data": "synthetic", "config": {"workload": WORKLOAD, "where": "host CPU", "row_fraction_per_step": frac}, "cpu_baseline": base,
+        "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}, "gpu_launches": 0,
+    }  # fmt: skip
+
+
+# ----------------------------------------------------------------------------- GPU arm
+def run_ours(args) -> dict | None:
+    import torch
+
+    from binade_b200 import pack
+    from binade_b200.cuda import kernels as ck
+    from binade_b200.cuda import r4
+
+    rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
+    local = int(os.environ.get("LOCAL_RANK", 0))
+    torch.cuda.set_device(local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    dev = torch.device("cuda", local)
+    copies = args.copies
+
+    # ---- build: host Rice encode (product packer), device expand (timed), R4 resident
+    layers, expand_ms, expand_bytes, host_pack_s, bits_file, bits_r4 = [], 0.0, 0, 0.0, 0, 0
+    numel = 0
+    for name, n, k in SHAPES:
+        u = synthetic_weight(name, n, k, rank)
+        t0 = time.perf_counter()
+        p = pack.pack(u)
+        host_pack_s += time.perf_counter() - t0
+        d = {key: ck.to_device(p[key]) for key in ("raw", "table", "meta", "bits", "roff")}
+        torch.cuda.synchronize()
+        a = r4.transcode(d)  # warm-up (also the copy every matvec copy is cloned from)
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        reps = 3
+        ev0.record()
+        for _ in range(reps):
+            a = r4.transcode(d)
+        ev1.record()
+        torch.cuda.synchronize()
+        expand_ms += ev0.elapsed_time(ev1) / reps
+        # algorithmic bytes of the expander: Rice arrays read + R4 arrays written (raw passes through)
+        expand_bytes += sum(d[key].numel() * d[key].element_size() for key in ("meta", "bits", "roff", "table")) + sum(a[key].numel() * a[key].element_size() for key in ("codes", "flags", "esc", "row_esc"))
+        bits_file += 8 * u.size + 8 * 256 + 8 * p["meta"].size + 32 * p["bits"].size + 32 * p["roff"].size
+        bits_r4 += 8 * r4.r4_bytes(a)
+        numel += u.size
+        mods = [r4.R4Linear(a)] + [r4.R4Linear({key: (v.clone() if torch.is_tensor(v) else v) for key, v in a.items()}) for _ in range(copies - 1)]
+        layers.append((name, n, k, mods, r4.r4_bytes(a) + 2 * k + 2 * n))
+        del d, p, u
+    step_bytes = sum(l[4] for l in layers)
+    xs = {k: ck.to_device(synthetic_input(k, rank)).view(torch.bfloat16) for k in {k for _, _, k in SHAPES}}
+    gathered = {n: torch.empty(world * n, dtype=torch.bfloat16, device=dev) for _, n, _ in SHAPES} if world > 1 else None
+
+    def step(i: int):
+        out = []
+        for name, n, k, mods, _ in layers:
+            y = mods[i % copies]._matvec(xs[k])
+            if world > 1:
+                dist.all_gather_into_tensor(gathered[n], y)
+            out.append(y)
+        return out
+
+    # ---- parity of this very workload against the oracle, on one small projection
+    if rank == 0:
+        from oracle import oracle as o
+
+        name, n, k = SHAPES[1]
+        want = o.c_r4_matvec(o.pack_r4(synthetic_weight(name, n, k, rank)), synthetic_input(k, rank), n, k)
+        got = layers[1][3][0]._matvec(xs[k]).view(torch.int16).cpu().numpy().view(np.uint16)
+        if not np.array_equal(got, want):
+            raise SystemExit("bench: GPU matvec differs from the oracle; refusing to report a number")
+
+    # ---- timed region: W warm-up steps, then exactly K steps as replays of a CUDA graph that
+    # holds one step per weight copy (plus a shorter graph for K % copies)
+    for i in range(max(args.warmup, 3)):
+        step(i)
+    torch.cuda.synchronize()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+
+    def capture(n_steps: int):
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(side):
+            step(0)
+            side.synchronize()
+            with torch.cuda.graph(g, stream=side):
+                for i in range(n_steps):
+                    step(i)
+        torch.cuda.synchronize()
+        g.replay()  # untimed: graph upload
+        torch.cuda.synchronize()
+        return g
+
+    full, rem = divmod(args.steps, copies)
+    g_full = capture(copies) if full else None
+    g_rem = capture(rem) if rem else None
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local) as clocks:
+        ev0.record()
+        for _ in range(full):
+            g_full.replay()
+        if g_rem:
+            g_rem.replay()
+        ev1.record()
+        torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    ms = ev0.elapsed_time(ev1)
+    if world > 1:
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    ms_per_step = ms / args.steps
+    value = world * step_bytes / (ms_per_step * 1e-3) / 1e9
+
+    # ---- per shape: the matvec alone, rotating copies, graph-captured
+    per_shape = {}
+    for name, n, k, mods, nbytes in layers:
+        g = torch.cuda.CUDAGraph()
+        iters = 40
+        with torch.cuda.stream(side):
+            mods[0]._matvec(xs[k])
+            side.synchronize()
+            with torch.cuda.graph(g, stream=side):
+                for i in range(iters):
+                    mods[i % copies]._matvec(xs[k])
+        torch.cuda.synchronize()
+        g.replay()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        g.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        us = e0.elapsed_time(e1) * 1e3 / iters
+        # BF16 baseline: cuBLAS GEMV on the pre-decoded weight, same rotation
+        dense = [m.dense() for m in mods]
+        for i in range(3):
+            torch.mv(dense[i % copies], xs[k])
+        torch.cuda.synchronize()
+        e0.record()
+        for i in range(iters):
+            torch.mv(dense[i % copies], xs[k])
+        e1.record()
+        torch.cuda.synchronize()
+        us_bf16 = e0.elapsed_time(e1) * 1e3 / iters
+        per_shape[name] = {"us": round(us, 2), "gbs": round(nbytes / us / 1e3, 1), "bf16_gemv_us": round(us_bf16, 2), "speedup_vs_bf16": round(us_bf16 / us, 3)}
+        del dense, g
+
+    # ---- end to end through the public hook with host buffers
+    k_list = sorted({k for _, _, k in SHAPES})
+    h_x = {k: torch.from_numpy(synthetic_input(k, rank).view(np.int16)).view(torch.bfloat16).pin_memory() for k in k_list}
+    h_y = [torch.empty(n, dtype=torch.bfloat16).pin_memory() for _, n, _ in SHAPES]
+
+    def e2e_step(i: int):
+        dx = {k: h_x[k].to(dev, non_blocking=True) for k in k_list}
+        for j, (name, n, k, mods, _) in enumerate(layers):
+            y = mods[i % copies](dx[k])
+            if world > 1:
+                dist.all_gather_into_tensor(gathered[n], y)
+            h_y[j].copy_(y, non_blocking=True)
+        torch.cuda.synchronize()
+
+    for i in range(3):
+        e2e_step(i)
+    if world > 1:
+        dist.barrier()
+    e2e_steps = min(args.steps, 200)
+    ev0.record()
+    for i in range(e2e_steps):
+        e2e_step(i)
+    ev1.record()
+    torch.cuda.synchronize()
+    e2e_ms = ev0.elapsed_time(ev1) / e2e_steps
+    if world > 1:
+        t = torch.tensor([e2e_ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_ms = float(t.item())
+    e2e_val = world * step_bytes / (e2e_ms * 1e-3) / 1e9
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return None
+
+    peaks = measured_peaks()
+    launches = args.steps * len(SHAPES)
+    per_launch_bytes = step_bytes / len(SHAPES)
+    achieved = step_bytes / (ms_per_step * 1e-3) / 1e9
+    result = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+        "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16 weights (R4 coded), fp32 accumulate", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "copies_rotated": copies, "bytes_per_step": step_bytes, "l2": f"each step streams {step_bytes / 1e6:.0f} MB of distinct weights (> 126 MB L2), {copies} copies rotated", "timing": "CUDA-graph replays (one step per weight copy per graph), CUDA events, max over ranks", "collective": "NCCL all-gather of every projection output" if world > 1 else "none"},
+        "pct_of_nominal_8tbs": round(100 * value / world / NOMINAL_HBM_GBS, 2),
+        "bits_per_weight": {"file_format2": round(bits_file / numel, 3), "r4_in_memory": round(bits_r4 / numel, 3)},
+        "shapes": per_shape,
+        "speedup_vs_bf16_gemv_per_token": round(sum(v["bf16_gemv_us"] for v in per_shape.values()) / sum(v["us"] for v in per_shape.values()), 3),
+        "expander": {"ms_per_layer": round(expand_ms, 3), "gbs": round(expand_bytes / expand_ms / 1e6, 1), "algorithmic_bytes": expand_bytes, "host_pack_s": round(host_pack_s, 2), "host_pack_cores": cpu_cores()},
+        "roofline": {"bound": "hbm", "kernel": "r4_rows_kernel<M=1> (all 7 launches of a step)", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"], "peak_source": peaks["source"], "bytes_per_launch": per_launch_bytes, "traffic": args.traffic},
+        "e2e": {"value": e2e_val, "unit": UNIT, "ms_per_step": e2e_ms, "h2d_bytes_per_step": sum(2 * k for k in k_list), "d2h_bytes_per_step": sum(2 * n for _, n, _ in SHAPES), "api": "R4Linear.__call__ on host-resident inputs, outputs copied back to pinned host memory"},
+        "gpu_launches": launches,
+        "clocks": clocks.summary(),
+    }  # fmt: skip
+    # ---- CPU baseline on a bounded sample (rank 0, single GPU runs only)
+    if world == 1 and not args.no_cpu:
+        mats = cpu_r4_layer(0, names={"q", "k"})
+        cxs = {k: synthetic_input(k, 0) for k in {m[2] for m in mats}}
+        cpu_step(mats, cxs)
+        t0, n_rep = time.perf_counter(), 0
+        while time.perf_counter() - t0 < 10.0 and n_rep < 40:
+            cpu_step(mats, cxs)
+            n_rep += 1
+        dt = (time.perf_counter() - t0) / n_rep
+        result["cpu_baseline"] = {"value": sum(m[4] for m in mats) / dt / 1e9, "unit": UNIT, "cores": cpu_cores(), "kind": "port", "sample": f"q and k projections only (2 of 7 matvecs), {n_rep} repetitions, C oracle with OpenMP"}
+    else:
+        result["cpu_baseline"] = None
+    if world > 1:
+        dist.destroy_process_group()
+    return result
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=3000)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=("ours", "reference"))
+    ap.add_argument("--copies", type=int, default=3, help="weight copies rotated between steps")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--traffic", type=float, default=None, help="DRAM bytes per launch from an ncu capture, if known")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        if int(os.environ.get("RANK", 0)) != 0:
+            return
+        print(json.dumps(run_reference(args)))
+        return
+    out = run_ours(args)
+    if out is not None:
+        print(json.dumps(out))
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,83 @@
+// Shared device/host helpers of the binade_b200 CUDA library (sm_100a only).
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/binade_b200.h"
+
+#define BN_TILE 128
+#define BN_WARP 32
+#define BN_FULL 0xffffffffu
+
+namespace bn {
+
+// Records `msg` as the calling thread's last error and returns `code`.
+int fail(int code, const char *msg);
+int fail_cuda(cudaError_t e, const char *where);
+
+#define BN_CUDA(call)                                   \
+  do {                                                  \
+    cudaError_t e_ = (call);                            \
+    if (e_ != cudaSuccess) return bn::fail_cuda(e_, #call); \
+  } while (0)
+
+// Result of a kernel launch: picks up configuration errors without synchronising.
+inline int launched(const char *what) {
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? BN_OK : fail_cuda(e, what);
+}
+
+inline int64_t tiles(int64_t K) { return (K + BN_TILE - 1) / BN_TILE; }
+
+// Raises a kernel's dynamic shared memory limit once per (kernel, device).
+template <typename Kernel>
+inline cudaError_t allow_smem(Kernel k, size_t bytes) {
+  return cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+}
+
+#ifdef __CUDACC__
+__device__ __forceinline__ uint32_t lane_id() { return threadIdx.x & 31; }
+__device__ __forceinline__ uint32_t lanemask_lt() {
+  uint32_t m;
+  asm("mov.u32 %0, %%lanemask_lt;" : "=r"(m));
+  return m;
+}
+
+// Streaming global loads: read once, keep out of L1.
+__device__ __forceinline__ uint32_t ldg_stream_u32(const void *p) {
+  uint32_t v;
+  asm volatile("ld.global.nc.L1::no_allocate.u32 %0, [%1];" : "=r"(v) : "l"(p));
+  return v;
+}
+__device__ __forceinline__ uint32_t ldg_stream_u16(const void *p) {
+  uint16_t v;
+  asm volatile("ld.global.nc.L1::no_allocate.u16 %0, [%1];" : "=h"(v) : "l"(p));
+  return v;
+}
+__device__ __forceinline__ uint32_t lds_u32(uint32_t addr) {
+  uint32_t v;
+  asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ uint32_t smem_addr(const void *p) {
+  return (uint32_t)__cvta_generic_to_shared(p);
+}
+
+// fp32 -> BF16 bit pattern, round to nearest even (cvt.rn.bf16.f32; NaN -> 0x7FFF).
+__device__ __forceinline__ uint16_t f32_to_bf16_bits(float f) {
+  uint16_t r;
+  asm("cvt.rn.bf16.f32 %0, %1;" : "=h"(r) : "f"(f));
+  return r;
+}
+
+// Exclusive prefix (over lanes, in lane order) and warp total of a per-lane count in 0..7,
+// from three ballots instead of a five-step shuffle scan. All 32 lanes must call.
+__device__ __forceinline__ void warp_scan_small(uint32_t cnt, uint32_t lt, uint32_t &pre, uint32_t &tot) {
+  uint32_t b0 = __ballot_sync(BN_FULL, cnt & 1u), b1 = __ballot_sync(BN_FULL, cnt & 2u), b2 = __ballot_sync(BN_FULL, cnt & 4u);
+  pre = __popc(b0 & lt) + 2 * __popc(b1 & lt) + 4 * __popc(b2 & lt);
+  tot = __popc(b0) + 2 * __popc(b1) + 4 * __popc(b2);
+}
+#endif
+
+}  // namespace bn

@@ -1,0 +1,344 @@
+// R4 kernels: dense decode, and the fused decode + product kernels (matvec, small-M rows,
+// expert gather). One warp owns whole weight rows; lane l owns weights 128t + 4l + j of every
+// tile t, which is both the layout of an R4 lane word (4 raw bytes + one uint16 of codes) and
+// the documented summation order.
+#include "common.cuh"
+
+namespace bn {
+
+// ---------------------------------------------------------------------------------------------
+// Exponent lookup. A code byte holds two 4-bit codes (c0 | c1 << 4); the pair table maps it to
+// the two exponents already placed in a BF16x2 word: table[c0] << 7 | table[c1] << 23. Code 15
+// (escape) maps to exponent bits 0 so that the escape byte can be OR-ed in afterwards. The table
+// is replicated once per lane (entry i of lane l at word i * 32 + l): a lookup never conflicts.
+// ---------------------------------------------------------------------------------------------
+constexpr int LUT_WORDS = 256 * 32;
+
+__device__ __forceinline__ void build_pair_lut(uint32_t *lut, const uint8_t *table) {
+  __shared__ uint32_t t16[16];
+  if (threadIdx.x < 16) t16[threadIdx.x] = threadIdx.x == 15 ? 0u : (uint32_t)table[threadIdx.x];
+  __syncthreads();
+  for (uint32_t i = threadIdx.x; i < LUT_WORDS; i += blockDim.x) {
+    uint32_t code = i >> 5;
+    lut[i] = (t16[code & 15] << 7) | (t16[code >> 4] << 23);
+  }
+}
+
+// Four weights of one lane word as two BF16x2 words (w01 = weight0 | weight1 << 16, w23 alike).
+// raw4: the four raw bytes (sign << 7 | mantissa); c: the uint16 of codes; lut_lane: shared
+// address of this lane's column of the pair table.
+__device__ __forceinline__ void decode4(uint32_t raw4, uint32_t c, uint32_t lut_lane, uint32_t &w01, uint32_t &w23) {
+  uint32_t e01 = lds_u32(lut_lane + ((c << 7) & 0x7F80u));
+  uint32_t e23 = lds_u32(lut_lane + ((c >> 1) & 0x7F80u));
+  uint32_t p01 = __byte_perm(raw4, 0u, 0x1100);  // bytes b0 b0 b1 b1
+  uint32_t p23 = __byte_perm(raw4, 0u, 0x3322);  // bytes b2 b2 b3 b3
+  w01 = (p01 & 0x807F807Fu) | e01;
+  w23 = (p23 & 0x807F807Fu) | e23;
+}
+
+// Patches the escaped weights (code 15) of a flagged tile with the row's next escape bytes, in
+// weight order across the warp, and advances the row's escape cursor. Whole warp takes part.
+__device__ __forceinline__ void apply_escapes(uint32_t c, const uint8_t *__restrict__ esc, uint32_t &epos, uint32_t lt, uint32_t &w01, uint32_t &w23) {
+  uint32_t hit = c & (c >> 1) & (c >> 2) & (c >> 3) & 0x1111u;  // bit 4j: code j == 15
+  uint32_t pre, tot;
+  warp_scan_small(__popc(hit), lt, pre, tot);
+  uint32_t q = epos + pre;
+  if (hit & 0x0001u) w01 |= (uint32_t)esc[q++] << 7;
+  if (hit & 0x0010u) w01 |= (uint32_t)esc[q++] << 23;
+  if (hit & 0x0100u) w23 |= (uint32_t)esc[q++] << 7;
+  if (hit & 0x1000u) w23 |= (uint32_t)esc[q++] << 23;
+  epos += tot;
+}
+
+__device__ __forceinline__ float lo_f32(uint32_t w) { return __uint_as_float(w << 16); }
+__device__ __forceinline__ float hi_f32(uint32_t w) { return __uint_as_float(w & 0xFFFF0000u); }
+
+// ---------------------------------------------------------------------------------------------
+// R4 -> dense BF16
+// ---------------------------------------------------------------------------------------------
+constexpr int DEC_THREADS = 256;
+
+__global__ void __launch_bounds__(DEC_THREADS) r4_decode_kernel(bn_r4 w, int64_t N, int64_t K, int T, int64_t NB, int64_t RS, int64_t R0, uint16_t *__restrict__ out) {
+  extern __shared__ uint32_t lut[];
+  build_pair_lut(lut, w.table);
+  __syncthreads();
+  const uint32_t lane = lane_id(), lt = lanemask_lt();
+  const uint32_t lut_lane = smem_addr(lut) + lane * 4;
+  const int warps = DEC_THREADS / 32;
+  for (int64_t orow = (int64_t)blockIdx.x * warps + (threadIdx.x >> 5); orow < N; orow += (int64_t)gridDim.x * warps) {
+    const int64_t row = (orow / NB) * RS + R0 + orow % NB;
+    uint32_t epos = w.row_esc[row];
+    const uint8_t *raw = w.raw + row * K;
+    const uint16_t *codes = w.codes + row * T * 32;
+    const uint8_t *flags = w.flags + row * T;
+    uint2 *o = reinterpret_cast<uint2 *>(out + orow * K);
+    for (int t0 = 0; t0 < T; t0 += 32) {
+      const uint32_t fmask = __ballot_sync(BN_FULL, t0 + (int)lane < T && flags[t0 + lane] != 0);
+      const int tn = min(32, T - t0);
+#pragma unroll 4
+      for (int u = 0; u < tn; u++) {
+        const int t = t0 + u;
+        const bool in = t * BN_TILE + (int)lane * 4 < K;
+        uint32_t r = in ? ldg_stream_u32(raw + t * BN_TILE + lane * 4) : 0u;
+        uint32_t c = ldg_stream_u16(codes + t * 32 + lane);
+        uint32_t w01, w23;
+        decode4(r, c, lut_lane, w01, w23);
+        if ((fmask >> u) & 1u) apply_escapes(c, w.esc, epos, lt, w01, w23);
+        if (in) o[t * 32 + lane] = make_uint2(w01, w23);
+      }
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Fused decode + product: Y[m, r] = sum_k X[m, k] W[r, k]
+//   M   input rows held per pass (accumulators per weight row)
+//   RW  weight rows a warp works on at once (reuses the x registers)
+// x lives in shared memory as fp32, staged in chunks of KC tiles when M * K is large.
+// ---------------------------------------------------------------------------------------------
+constexpr int MV_THREADS = 512;  // launch bound; small matrices launch fewer warps per block
+
+struct RowsArgs {
+  bn_r4 w;
+  const uint16_t *x;
+  int64_t x_stride;
+  const uint32_t *xi, *ei;  // per-slot input row / expert (gather only)
+  int m;                    // input rows really present (<= M of the instantiation)
+  int64_t n;                // weight rows per slot
+  int64_t K;
+  int T;
+  int KC;  // tiles of x staged at a time
+  int64_t RS, R0, split;
+  uint16_t *y, *y2;
+  int64_t y_stride;
+};
+
+template <int M, int RW, bool GATHER>
+__global__ void __launch_bounds__(MV_THREADS) r4_rows_kernel(RowsArgs a) {
+  constexpr int U = 4;  // tiles whose loads are issued before any is consumed
+  extern __shared__ uint32_t smem[];
+  uint32_t *lut = smem;
+  float *xs = reinterpret_cast<float *>(smem + LUT_WORDS);  // [M][KC * 128]
+  const uint32_t lane = lane_id(), lt = lanemask_lt(), warp = threadIdx.x >> 5;
+  const uint32_t lut_lane = smem_addr(lut) + lane * 4;
+  const int warps = blockDim.x >> 5;
+  const int64_t K = a.K;
+  const int T = a.T, KC = a.KC;
+  const int xs_stride = KC * BN_TILE;
+
+  int64_t row0 = 0;  // storage row of output row 0
+  const uint16_t *x = a.x;
+  int64_t g = 0;
+  if (GATHER) {
+    g = blockIdx.y;
+    row0 = (int64_t)a.ei[g] * a.RS + a.R0;
+    x = a.x + (int64_t)a.xi[g] * a.x_stride;
+  }
+  build_pair_lut(lut, a.w.table);
+
+  const bool one_chunk = KC >= T;
+  const int64_t block_rows = (int64_t)warps * RW;
+  const int64_t first_rb = (int64_t)blockIdx.x * block_rows;
+  for (int64_t rb = first_rb; rb < a.n; rb += (int64_t)gridDim.x * block_rows) {
+    float acc[RW][M];
+    uint32_t epos[RW];
+    const uint8_t *raw_row[RW];
+    const uint16_t *code_row[RW];
+    const uint8_t *flag_row[RW];
+    bool live[RW];
+#pragma unroll
+    for (int i = 0; i < RW; i++) {
+      const int64_t r = rb + (int64_t)warp * RW + i;
+      live[i] = r < a.n;
+      const int64_t srow = row0 + (live[i] ? r : 0);
+      epos[i] = a.w.row_esc[srow];
+      raw_row[i] = a.w.raw + srow * K + lane * 4;
+      code_row[i] = a.w.codes + srow * T * 32 + lane;
+      flag_row[i] = a.w.flags + srow * T;
+#pragma unroll
+      for (int m = 0; m < M; m++) acc[i][m] = 0.0f;
+    }
+    for (int tc = 0; tc < T; tc += KC) {
+      // stage x[:, tc*128 ..) as fp32; absent rows and columns >= K hold zeros and are
+      // never multiplied into a real output (see `in` and the store predicate)
+      if (!one_chunk || rb == first_rb) {
+        __syncthreads();
+        for (int i = threadIdx.x; i < M * xs_stride; i += blockDim.x) {
+          const int m = i / xs_stride, col = i - m * xs_stride;
+          const int64_t k = (int64_t)tc * BN_TILE + col;
+          xs[i] = (m < a.m && k < K) ? __uint_as_float((uint32_t)x[m * a.x_stride + k] << 16) : 0.0f;
+        }
+        __syncthreads();
+      }
+      const int tend = min(T, tc + KC);
+      for (int t0 = tc; t0 < tend; t0 += 32) {
+        uint32_t fmask[RW], fany = 0;
+#pragma unroll
+        for (int i = 0; i < RW; i++) {
+          fmask[i] = __ballot_sync(BN_FULL, t0 + (int)lane < tend && flag_row[i][t0 + lane] != 0);
+          fany |= fmask[i];
+        }
+        const int tn = min(32, tend - t0);
+        for (int u0 = 0; u0 < tn; u0 += U) {
+          uint32_t r4[U][RW], c4[U][RW];
+#pragma unroll
+          for (int uu = 0; uu < U; uu++) {
+            const int t = t0 + u0 + uu;
+            const bool in = u0 + uu < tn && (int64_t)t * BN_TILE + lane * 4 < K;
+#pragma unroll
+            for (int i = 0; i < RW; i++) {
+              r4[uu][i] = in ? ldg_stream_u32(raw_row[i] + t * BN_TILE) : 0u;
+              c4[uu][i] = in ? ldg_stream_u16(code_row[i] + t * 32) : 0u;
+            }
+          }
+#pragma unroll
+          for (int uu = 0; uu < U; uu++) {
+            const int u = u0 + uu, t = t0 + u;
+            if (u >= tn) break;
+            const bool in = (int64_t)t * BN_TILE + lane * 4 < K;
+            float wf[RW][4];
+#pragma unroll
+            for (int i = 0; i < RW; i++) {
+              uint32_t w01, w23;
+              decode4(r4[uu][i], c4[uu][i], lut_lane, w01, w23);
+              if ((fany >> u) & 1u) {
+                if ((fmask[i] >> u) & 1u) apply_escapes(c4[uu][i], a.w.esc, epos[i], lt, w01, w23);
+              }
+              wf[i][0] = lo_f32(w01), wf[i][1] = hi_f32(w01), wf[i][2] = lo_f32(w23), wf[i][3] = hi_f32(w23);
+            }
+            if (in) {
+              const float *xt = xs + (t - tc) * BN_TILE + lane * 4;
+#pragma unroll
+              for (int m = 0; m < M; m++) {
+                const float4 xv = *reinterpret_cast<const float4 *>(xt + m * xs_stride);
+#pragma unroll
+                for (int i = 0; i < RW; i++) {
+                  float s = acc[i][m];
+                  s = __fmaf_rn(wf[i][0], xv.x, s);
+                  s = __fmaf_rn(wf[i][1], xv.y, s);
+                  s = __fmaf_rn(wf[i][2], xv.z, s);
+                  s = __fmaf_rn(wf[i][3], xv.w, s);
+                  acc[i][m] = s;
+                }
+              }
+            }
+          }
+        }
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < RW; i++) {
+      float mine = 0.0f;
+#pragma unroll
+      for (int m = 0; m < M; m++) {
+        float s = acc[i][m];
+#pragma unroll
+        for (int o = 16; o >= 1; o >>= 1) s = s + __shfl_xor_sync(BN_FULL, s, o);
+        if ((int)lane == m) mine = s;
+      }
+      const int64_t r = rb + (int64_t)warp * RW + i;
+      if (live[i] && (int)lane < a.m) {
+        const uint16_t v = f32_to_bf16_bits(mine);
+        if (GATHER) {
+          if (a.split > 0 && r >= a.split)
+            a.y2[g * (a.n - a.split) + (r - a.split)] = v;
+          else
+            a.y[g * (a.split > 0 ? a.split : a.n) + r] = v;
+        } else {
+          a.y[(int64_t)lane * a.y_stride + r] = v;
+        }
+      }
+    }
+  }
+}
+
+static int sm_count() {
+  static int n = 0;
+  if (!n) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    if (n <= 0) n = 148;
+  }
+  return n;
+}
+
+template <int M, int RW, bool GATHER>
+static int launch_rows(RowsArgs a, int64_t G, cudaStream_t s) {
+  // x chunk: whole K when it fits beside the table, else as many tiles as the budget holds
+  int kc = a.T;
+  const size_t budget = (M == 1 ? 192 : 96) * 1024;
+  if ((size_t)M * kc * BN_TILE * 4 > budget) kc = (int)(budget / ((size_t)M * BN_TILE * 4));
+  if (kc < 1) return fail(BN_ERR_ARG, "K too large for the fused rows kernel");
+  a.KC = kc;
+  const size_t smem = LUT_WORDS * 4 + (size_t)M * kc * BN_TILE * 4;
+  auto kern = r4_rows_kernel<M, RW, GATHER>;
+  BN_CUDA(allow_smem(kern, smem));
+  // few rows: narrower blocks so that every SM gets work
+  int threads = MV_THREADS;
+  while (threads > 128 && (a.n * G + (threads / 32) * RW - 1) / ((threads / 32) * RW) < 2 * (int64_t)sm_count()) threads >>= 1;
+  int per_sm = 1;
+  BN_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, threads, smem));
+  if (per_sm < 1) per_sm = 1;
+  const int64_t block_rows = (int64_t)(threads / 32) * RW;
+  int64_t blocks = (a.n + block_rows - 1) / block_rows;
+  const int64_t cap = (int64_t)sm_count() * per_sm;
+  if (blocks * G > cap) blocks = (cap + G - 1) / G;
+  dim3 grid((unsigned)blocks, (unsigned)G);
+  kern<<<grid, threads, smem, s>>>(a);
+  return launched("r4_rows_kernel");
+}
+
+static int check_r4(const bn_r4 *w) {
+  if (!w || !w->raw || !w->codes || !w->flags || !w->esc || !w->table || !w->row_esc) return fail(BN_ERR_ARG, "null R4 array");
+  return BN_OK;
+}
+
+}  // namespace bn
+
+using namespace bn;
+
+extern "C" int bn_r4_decode(const bn_r4 *w, int64_t N, int64_t K, int64_t NB, int64_t RS, int64_t R0, uint16_t *out, void *stream) {
+  if (int e = check_r4(w)) return e;
+  if (!out || N < 0 || K <= 0 || NB <= 0) return fail(BN_ERR_ARG, "bn_r4_decode: bad size or null output");
+  if (K % 4) return fail(BN_ERR_ARG, "R4 needs K % 4 == 0");
+  if (N == 0) return BN_OK;
+  const size_t smem = LUT_WORDS * 4;
+  BN_CUDA(allow_smem(r4_decode_kernel, smem));
+  const int warps = DEC_THREADS / 32;
+  int64_t blocks = (N + warps - 1) / warps;
+  if (blocks > (int64_t)sm_count() * 8) blocks = (int64_t)sm_count() * 8;
+  r4_decode_kernel<<<(unsigned)blocks, DEC_THREADS, smem, (cudaStream_t)stream>>>(*w, N, K, (int)tiles(K), NB, RS, R0, out);
+  return launched("r4_decode_kernel");
+}
+
+extern "C" int bn_r4_rows(const uint16_t *x, int64_t x_stride, const bn_r4 *w, int64_t M, int64_t N, int64_t K, uint16_t *y, int64_t y_stride, void *stream) {
+  if (int e = check_r4(w)) return e;
+  if (!x || !y || N < 0 || K <= 0 || M < 1 || M > 16) return fail(BN_ERR_ARG, "bn_r4_rows: bad size (1 <= M <= 16) or null pointer");
+  if (K % 4) return fail(BN_ERR_ARG, "R4 needs K % 4 == 0");
+  if (N == 0) return BN_OK;
+  RowsArgs a{};
+  a.w = *w, a.x = x, a.x_stride = x_stride, a.n = N, a.K = K, a.T = (int)tiles(K), a.y = y, a.y_stride = y_stride;
+  cudaStream_t s = (cudaStream_t)stream;
+  a.m = (int)M;
+  // the instantiation is the next power of two >= M: absent input rows are zeros in shared
+  // memory and are never stored, so the weights stream once whatever M
+  if (M == 1) return N >= 8192 ? launch_rows<1, 2, false>(a, 1, s) : launch_rows<1, 1, false>(a, 1, s);
+  if (M == 2) return launch_rows<2, 2, false>(a, 1, s);
+  if (M <= 4) return launch_rows<4, 2, false>(a, 1, s);
+  if (M <= 8) return launch_rows<8, 2, false>(a, 1, s);
+  return launch_rows<16, 2, false>(a, 1, s);
+}
+
+extern "C" int bn_r4_gather(const uint16_t *x, const bn_r4 *w, const uint32_t *xi, const uint32_t *ei, int64_t G, int64_t n, int64_t K, int64_t RS, int64_t R0, int64_t split, uint16_t *y, uint16_t *y2, void *stream) {
+  if (int e = check_r4(w)) return e;
+  if (!x || !xi || !ei || !y || G < 0 || n < 0 || K <= 0 || split < 0 || split >= (n > 0 ? n : 1)) return fail(BN_ERR_ARG, "bn_r4_gather: bad size or null pointer");
+  if (split > 0 && !y2) return fail(BN_ERR_ARG, "bn_r4_gather: split needs y2");
+  if (K % 4) return fail(BN_ERR_ARG, "R4 needs K % 4 == 0");
+  if (G == 0 || n == 0) return BN_OK;
+  if (G > 65535) return fail(BN_ERR_ARG, "bn_r4_gather: more than 65535 slots");
+  RowsArgs a{};
+  a.w = *w, a.x = x, a.x_stride = K, a.xi = xi, a.ei = ei, a.n = n, a.K = K, a.T = (int)tiles(K);
+  a.RS = RS, a.R0 = R0, a.split = split, a.y = y, a.y2 = y2, a.m = 1;
+  return launch_rows<1, 1, true>(a, G, (cudaStream_t)stream);
+}

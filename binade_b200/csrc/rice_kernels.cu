@@ -1,0 +1,312 @@
+// Format-2 (Rice) stream decoders. One warp owns a row (tiles of a row are chained: a tile's
+// length is only known once its planes are decoded); lane l owns weights 4l .. 4l+3 of every
+// tile, so a lane's four ranks are exactly one R4 lane word (or one uint32 of 8-bit ranks).
+//
+// Stream of one tile (n weights, meta = k | qmax << 2):
+//   low plane     n*k bits, bit b of weight i at i*k + b
+//   unary planes  j = 0 .. qmax-1: one bit per weight still alive (q >= j), set iff q > j
+// The bit offset of a lane inside a plane is the number of alive weights before it: a warp
+// prefix sum over per-lane alive counts, done with three ballots.
+#include "common.cuh"
+
+namespace bn {
+
+enum RiceMode { RICE_RANKS = 0, RICE_UNPACK = 1, RICE_R4 = 2 };
+
+struct RiceArgs {
+  const uint8_t *meta;
+  const uint32_t *bits;
+  uint64_t nwords;
+  const uint32_t *roff;
+  const uint8_t *table;
+  const uint8_t *raw;
+  int64_t R, K;
+  int T;
+  // outputs
+  uint32_t *ranks;   // RICE_RANKS: [R, T*32] four 8-bit ranks per word
+  uint32_t *rend;    // RICE_RANKS / RICE_UNPACK: word after each row's last bit
+  uint16_t *out;     // RICE_UNPACK: BF16 [R, K]
+  uint16_t *codes;   // RICE_R4
+  uint8_t *flags;    // RICE_R4
+  uint32_t *row_cnt; // RICE_R4
+  uint8_t *esc_tmp;  // RICE_R4 scratch
+  uint64_t esc_cap;
+  uint32_t *tmp_off;
+  uint32_t *counters;
+};
+
+// n <= 32 bits of the stream starting at bit `pos`; words outside [0, nwords) read as zero.
+__device__ __forceinline__ uint32_t read_bits(const uint32_t *__restrict__ bits, uint64_t nwords, uint64_t pos, uint32_t n) {
+  const uint64_t w = pos >> 5;
+  const uint32_t s = (uint32_t)pos & 31u;
+  uint32_t lo = w < nwords ? __ldg(bits + w) : 0u;
+  uint32_t hi = (s + n > 32u && w + 1 < nwords) ? __ldg(bits + w + 1) : 0u;
+  uint32_t v = __funnelshift_r(lo, hi, s);
+  return n >= 32u ? v : v & ((1u << n) - 1u);
+}
+
+constexpr int RICE_THREADS = 256;
+
+template <int MODE>
+__global__ void __launch_bounds__(RICE_THREADS) rice_kernel(RiceArgs a) {
+  __shared__ uint8_t tbl[256];
+  if (MODE != RICE_RANKS) {
+    if (threadIdx.x < 256) tbl[threadIdx.x] = a.table[threadIdx.x];
+    __syncthreads();
+  }
+  const uint32_t lane = lane_id(), lt = lanemask_lt();
+  const int warps = RICE_THREADS / 32;
+  const int T = a.T;
+  const int64_t K = a.K;
+  for (int64_t row = (int64_t)blockIdx.x * warps + (threadIdx.x >> 5); row < a.R; row += (int64_t)gridDim.x * warps) {
+    const uint32_t w0 = a.roff[row];
+    const uint64_t w_end = row + 1 < a.R ? (uint64_t)a.roff[row + 1] : a.nwords;
+    // pull the row's stream toward the SM: one 128-byte line per lane, up to 4 KB
+    {
+      const uint64_t p = (uint64_t)w0 + lane * 32u;
+      if (p < w_end && p < a.nwords) asm volatile("prefetch.global.L1 [%0];" ::"l"(a.bits + p));
+    }
+    uint64_t cur = (uint64_t)w0 * 32u;
+    uint32_t row_escapes = 0;
+    uint64_t esc_base = 0;
+    bool esc_room = false;
+    if (MODE == RICE_R4) {
+      // claim scratch for the most escapes the row's meta bytes allow: a tile can hold a rank
+      // >= 15 only if its largest representable rank (qmax << k | low bits) reaches 15
+      uint32_t bound = 0;
+      for (int t = lane; t < T; t += 32) {
+        const uint32_t m = a.meta[row * T + t], k = m & 3u, qmax = m >> 2;
+        if (((qmax << k) | ((1u << k) - 1u)) >= 15u) bound += (uint32_t)min((int64_t)BN_TILE, K - (int64_t)t * BN_TILE);
+      }
+#pragma unroll
+      for (int o = 16; o >= 1; o >>= 1) bound += __shfl_xor_sync(BN_FULL, bound, o);
+      unsigned long long base = 0;
+      if (lane == 0 && bound) base = atomicAdd(reinterpret_cast<unsigned long long *>(a.counters + 4), (unsigned long long)bound);
+      base = __shfl_sync(BN_FULL, base, 0);
+      esc_base = base;
+      esc_room = base + bound <= a.esc_cap;
+      if (lane == 0) a.tmp_off[row] = (uint32_t)base;
+    }
+    for (int t0 = 0; t0 < T; t0 += 32) {
+      const uint32_t my_meta = t0 + (int)lane < T ? a.meta[row * T + t0 + lane] : 0u;
+      uint32_t my_flag = 0;
+      const int tn = min(32, T - t0);
+      for (int u = 0; u < tn; u++) {
+        const int t = t0 + u;
+        const uint32_t m = __shfl_sync(BN_FULL, my_meta, u);
+        const uint32_t k = m & 3u, qmax = m >> 2;
+        const int n = (int)min((int64_t)BN_TILE, K - (int64_t)t * BN_TILE);
+        const uint32_t nv = (uint32_t)max(0, min(4, n - (int)lane * 4));
+        uint32_t lo = 0;
+        if (nv * k) lo = read_bits(a.bits, a.nwords, cur + lane * 4u * k, nv * k);
+        cur += (uint64_t)n * k;
+        uint32_t q4 = 0;  // one byte per weight
+        uint32_t alive = (1u << nv) - 1u;
+        for (uint32_t j = 0; j < qmax; j++) {
+          const uint32_t c = __popc(alive);
+          uint32_t pre, tot;
+          warp_scan_small(c, lt, pre, tot);
+          if (tot == 0) break;  // only a corrupt stream: the remaining planes are empty
+          if (tot == 1) {
+            // one weight left: its remaining planes are a run of ones closed by a zero (or by
+            // reaching qmax); count it in one go instead of one warp scan per plane
+            const uint32_t rem = qmax - j;
+            uint32_t used = 0;
+            if (c) {
+              uint32_t ones = 0;
+              for (uint32_t done = 0; done < rem; done += 32) {
+                const uint32_t take = min(32u, rem - done);
+                const uint32_t b = read_bits(a.bits, a.nwords, cur + done, take);
+                const uint32_t run = __ffs(~b) - 1;  // 32 when b is all ones (ffs(0) = 0 wraps)
+                if (run < take) { ones += run; break; }
+                ones += take;
+              }
+              used = min(ones + 1, rem);
+              q4 += ones << (8 * (__ffs(alive) - 1));
+            }
+            const uint32_t owner = __ffs(__ballot_sync(BN_FULL, c != 0)) - 1;
+            cur += __shfl_sync(BN_FULL, used, owner);
+            break;
+          }
+          uint32_t b = c ? read_bits(a.bits, a.nwords, cur + pre, c) : 0u;
+          uint32_t na = 0;
+#pragma unroll
+          for (int i = 0; i < 4; i++) {
+            if ((alive >> i) & 1u) {
+              const uint32_t v = b & 1u;
+              b >>= 1;
+              q4 += v << (8 * i);
+              na |= v << i;
+            }
+          }
+          alive = na;
+          cur += tot;
+        }
+        // ranks of the lane's four weights, one per byte: q << k | low bits
+        const uint32_t km = (1u << k) - 1u;
+        uint32_t r4 = 0;
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+          const uint32_t r = ((((q4 >> (8 * i)) & 0xFFu) << k) | ((lo >> (i * k)) & km)) & 0xFFu;
+          r4 |= r << (8 * i);
+        }
+        if (MODE == RICE_RANKS) {
+          a.ranks[(row * T + t) * 32 + lane] = r4;
+        } else if (MODE == RICE_UNPACK) {
+          const int64_t col = (int64_t)t * BN_TILE + lane * 4;
+          if (nv == 4 && (K & 3) == 0) {  // aligned: one 4-byte load, one 8-byte store
+            const uint32_t rw = ldg_stream_u32(a.raw + row * K + col);
+            uint32_t o[4];
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+              const uint32_t b = (rw >> (8 * i)) & 0xFFu, e = tbl[(r4 >> (8 * i)) & 0xFFu];
+              o[i] = ((b & 0x80u) << 8) | (e << 7) | (b & 0x7Fu);
+            }
+            *reinterpret_cast<uint2 *>(a.out + row * K + col) = make_uint2(o[0] | (o[1] << 16), o[2] | (o[3] << 16));
+          } else {
+            for (uint32_t i = 0; i < nv; i++) {
+              const uint32_t b = a.raw[row * K + col + i], e = tbl[(r4 >> (8 * i)) & 0xFFu];
+              a.out[row * K + col + i] = (uint16_t)(((b & 0x80u) << 8) | (e << 7) | (b & 0x7Fu));
+            }
+          }
+        } else {
+          uint32_t c16 = 0, hit = 0;
+#pragma unroll
+          for (int i = 0; i < 4; i++) {
+            const uint32_t r = (r4 >> (8 * i)) & 0xFFu;
+            c16 |= min(r, 15u) << (4 * i);
+            hit |= (r >= 15u ? 1u : 0u) << i;
+          }
+          a.codes[(row * T + t) * 32 + lane] = (uint16_t)c16;
+          const uint32_t any = __ballot_sync(BN_FULL, hit != 0);
+          if (any) {
+            uint32_t pre, tot;
+            warp_scan_small(__popc(hit), lt, pre, tot);
+            if (esc_room) {
+              uint64_t p = esc_base + row_escapes + pre;
+#pragma unroll
+              for (int i = 0; i < 4; i++)
+                if ((hit >> i) & 1u) a.esc_tmp[p++] = tbl[(r4 >> (8 * i)) & 0xFFu];
+            }
+            row_escapes += tot;
+            if ((int)lane == u) my_flag = 1;
+          }
+        }
+      }
+      if (MODE == RICE_R4 && t0 + (int)lane < T) a.flags[row * T + t0 + lane] = (uint8_t)my_flag;
+    }
+    if (lane == 0) {
+      const uint32_t rend = (uint32_t)((cur + 31u) >> 5);
+      if (MODE == RICE_R4) {
+        a.row_cnt[row] = row_escapes;
+        if (row_escapes) atomicAdd(a.counters + 2, row_escapes);
+        if ((uint64_t)rend != w_end) atomicMax(a.counters + 1, (uint32_t)(a.R - row));
+      } else {
+        a.rend[row] = rend;
+      }
+    }
+  }
+}
+
+// row_esc = exclusive prefix sum of row_cnt, by one block (load-time, R up to a few 10^5).
+__global__ void __launch_bounds__(1024) scan_rows_kernel(const uint32_t *row_cnt, int64_t R, uint32_t *row_esc) {
+  __shared__ uint32_t part[1024];
+  const int tid = threadIdx.x;
+  const int64_t per = (R + 1023) / 1024, lo = min(R, per * tid), hi = min(R, lo + per);
+  uint32_t s = 0;
+  for (int64_t i = lo; i < hi; i++) s += row_cnt[i];
+  part[tid] = s;
+  __syncthreads();
+  for (int o = 1; o < 1024; o <<= 1) {
+    const uint32_t v = tid >= o ? part[tid - o] : 0u;
+    __syncthreads();
+    part[tid] += v;
+    __syncthreads();
+  }
+  uint32_t run = part[tid] - s;
+  for (int64_t i = lo; i < hi; i++) {
+    const uint32_t c = row_cnt[i];  // read before the write: row_esc may alias row_cnt
+    row_esc[i] = run;
+    run += c;
+  }
+}
+
+// esc[row_esc[r] + i] = esc_tmp[tmp_off[r] + i], i < (escapes of row r); one warp per row.
+__global__ void __launch_bounds__(256) compact_esc_kernel(const uint32_t *__restrict__ row_esc, const uint8_t *__restrict__ esc_tmp, const uint32_t *__restrict__ tmp_off, int64_t R, uint8_t *__restrict__ esc, uint64_t esc_bytes) {
+  const uint32_t lane = lane_id();
+  for (int64_t row = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5); row < R; row += (int64_t)gridDim.x * 8) {
+    const uint64_t b = row_esc[row], e = row + 1 < R ? (uint64_t)row_esc[row + 1] : esc_bytes - 1;
+    const uint8_t *src = esc_tmp + tmp_off[row];
+    for (uint64_t i = lane; b + i < e; i += 32) esc[b + i] = src[i];
+  }
+  if (blockIdx.x == 0 && threadIdx.x == 0) esc[esc_bytes - 1] = 0;
+}
+
+static int rice_grid(int64_t R) {
+  int dev = 0, sms = 148;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  int64_t blocks = (R + RICE_THREADS / 32 - 1) / (RICE_THREADS / 32);
+  const int64_t cap = (int64_t)sms * 8;
+  return (int)(blocks < cap ? blocks : cap);
+}
+
+static int check_stream(const uint8_t *meta, const uint32_t *bits, const uint32_t *roff, int64_t R, int64_t K) {
+  if (!meta || !bits || !roff) return fail(BN_ERR_ARG, "null Rice stream array");
+  if (R < 0 || K <= 0) return fail(BN_ERR_ARG, "bad matrix size");
+  return BN_OK;
+}
+
+}  // namespace bn
+
+using namespace bn;
+
+extern "C" int bn_rice_ranks(const uint8_t *meta, const uint32_t *bits, uint64_t nwords, const uint32_t *roff, int64_t R, int64_t K, uint8_t *ranks, uint32_t *rend, void *stream) {
+  if (int e = check_stream(meta, bits, roff, R, K)) return e;
+  if (!ranks || !rend) return fail(BN_ERR_ARG, "bn_rice_ranks: null output");
+  if (R == 0) return BN_OK;
+  RiceArgs a{};
+  a.meta = meta, a.bits = bits, a.nwords = nwords, a.roff = roff, a.R = R, a.K = K, a.T = (int)tiles(K);
+  a.ranks = reinterpret_cast<uint32_t *>(ranks), a.rend = rend;
+  rice_kernel<RICE_RANKS><<<rice_grid(R), RICE_THREADS, 0, (cudaStream_t)stream>>>(a);
+  return launched("rice_kernel<ranks>");
+}
+
+extern "C" int bn_rice_unpack(const uint8_t *meta, const uint32_t *bits, uint64_t nwords, const uint32_t *roff, const uint8_t *table, const uint8_t *raw, int64_t R, int64_t K, uint16_t *out, uint32_t *rend, void *stream) {
+  if (int e = check_stream(meta, bits, roff, R, K)) return e;
+  if (!table || !raw || !out || !rend) return fail(BN_ERR_ARG, "bn_rice_unpack: null pointer");
+  if (R == 0) return BN_OK;
+  RiceArgs a{};
+  a.meta = meta, a.bits = bits, a.nwords = nwords, a.roff = roff, a.table = table, a.raw = raw, a.R = R, a.K = K, a.T = (int)tiles(K);
+  a.out = out, a.rend = rend;
+  rice_kernel<RICE_UNPACK><<<rice_grid(R), RICE_THREADS, 0, (cudaStream_t)stream>>>(a);
+  return launched("rice_kernel<unpack>");
+}
+
+extern "C" int bn_rice_to_r4(const uint8_t *meta, const uint32_t *bits, uint64_t nwords, const uint32_t *roff, const uint8_t *table, int64_t R, int64_t K, uint16_t *codes, uint8_t *flags, uint32_t *row_cnt, uint8_t *esc_tmp, uint64_t esc_cap, uint32_t *tmp_off, uint32_t *counters, void *stream) {
+  if (int e = check_stream(meta, bits, roff, R, K)) return e;
+  if (!table || !codes || !flags || !row_cnt || !tmp_off || !counters || (!esc_tmp && esc_cap)) return fail(BN_ERR_ARG, "bn_rice_to_r4: null pointer");
+  if (K % 4) return fail(BN_ERR_ARG, "R4 needs K % 4 == 0");
+  BN_CUDA(cudaMemsetAsync(counters, 0, 8 * sizeof(uint32_t), (cudaStream_t)stream));
+  if (R == 0) return BN_OK;
+  RiceArgs a{};
+  a.meta = meta, a.bits = bits, a.nwords = nwords, a.roff = roff, a.table = table, a.R = R, a.K = K, a.T = (int)tiles(K);
+  a.codes = codes, a.flags = flags, a.row_cnt = row_cnt, a.esc_tmp = esc_tmp, a.esc_cap = esc_cap, a.tmp_off = tmp_off, a.counters = counters;
+  rice_kernel<RICE_R4><<<rice_grid(R), RICE_THREADS, 0, (cudaStream_t)stream>>>(a);
+  return launched("rice_kernel<r4>");
+}
+
+extern "C" int bn_r4_finish(const uint32_t *row_cnt, const uint8_t *esc_tmp, const uint32_t *tmp_off, int64_t R, uint32_t *row_esc, uint8_t *esc, uint64_t esc_bytes, void *stream) {
+  if (!row_cnt || !tmp_off || !row_esc || !esc || esc_bytes < 1 || R < 0) return fail(BN_ERR_ARG, "bn_r4_finish: null pointer or empty esc");
+  if (!esc_tmp && esc_bytes > 1) return fail(BN_ERR_ARG, "bn_r4_finish: escapes without scratch");
+  cudaStream_t s = (cudaStream_t)stream;
+  if (R > 0) {
+    scan_rows_kernel<<<1, 1024, 0, s>>>(row_cnt, R, row_esc);
+    if (int e = launched("scan_rows_kernel")) return e;
+  }
+  int64_t blocks = (R + 7) / 8;
+  if (blocks > 2048) blocks = 2048;
+  if (blocks < 1) blocks = 1;
+  compact_esc_kernel<<<(unsigned)blocks, 256, 0, s>>>(row_esc, esc_tmp, tmp_off, R, esc, esc_bytes);
+  return launched("compact_esc_kernel");
+}

@@ -1,0 +1,152 @@
+"""Python face of the CUDA entry points (include/binade_b200.h) on torch CUDA tensors.
+
+Mirrors the reference's kernel wrappers (binade/mlx/cuda_kernels.py: rice_ranks, r4_matvec,
+r4_gather, r4_decode) with torch tensors in place of MLX arrays. Tensors are only carriers of
+device memory: every call passes raw pointers and the current CUDA stream to the C ABI.
+Nothing here runs without a CUDA device and the built library.
+"""
+
+from __future__ import annotations
+
+import ctypes
+
+import numpy as np
+import torch
+
+from .. import _native
+from ..format import TILE
+
+R4_KEYS = ("raw", "codes", "flags", "esc", "table", "row_esc")
+
+
+def require_cuda() -> torch.device:
+    if not torch.cuda.is_available():
+        raise RuntimeError("binade_b200 needs a CUDA device: its kernels have no CPU fallback")
+    return torch.device("cuda", torch.cuda.current_device())
+
+
+def to_device(a, dtype=None) -> torch.Tensor:
+    """numpy array or tensor -> contiguous CUDA tensor (uint16/uint32 travel as int16/int32)."""
+    dev = require_cuda()
+    if isinstance(a, np.ndarray):
+        if a.dtype == np.uint16:
+            a = a.view(np.int16)
+        elif a.dtype == np.uint32:
+            a = a.view(np.int32)
+        a = torch.from_numpy(np.ascontiguousarray(a))
+    t = a.to(dev, non_blocking=True).contiguous()
+    return t if dtype is None else t.to(dtype)
+
+
+def _p(t):
+    return None if t is None else ctypes.c_void_p(t.data_ptr())
+
+
+def _stream():
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _call(fn, *args):
+    return _native.call("cuda", fn, *args, _stream())
+
+
+def r4_struct(a: dict) -> _native.R4Struct:
+    return _native.R4Struct(*(a[k].data_ptr() for k in R4_KEYS))
+
+
+def rice_ranks(meta: torch.Tensor, bits: torch.Tensor, roff: torch.Tensor, K: int):
+    """(ranks uint8 [R, ceil(K/128)*128], rend int32-typed uint32 [R])."""
+    R, T = roff.numel(), -(-K // TILE)
+    if meta.numel() != R * T:
+        raise ValueError(f"{meta.numel()} tiles for {R} rows of {K}")
+    ranks = torch.empty((R, T * TILE), dtype=torch.uint8, device=meta.device)
+    rend = torch.empty(R, dtype=torch.int32, device=meta.device)
+    if bits.numel() == 0:
+        bits = torch.zeros(1, dtype=torch.int32, device=meta.device)
+        nwords = 0
+    else:
+        nwords = bits.numel()
+    _call("bn_rice_ranks", _p(meta), _p(bits), nwords, _p(roff), R, K, _p(ranks), _p(rend))
+    return ranks, rend
+
+
+def rice_unpack(meta, bits, roff, table, raw, R: int, K: int):
+    """BF16 rows [R, K] (bfloat16 tensor) and rend [R] from a Rice stream plus raw bytes."""
+    out = torch.empty((R, K), dtype=torch.bfloat16, device=raw.device)
+    rend = torch.empty(R, dtype=torch.int32, device=raw.device)
+    nwords = bits.numel()
+    if nwords == 0:
+        bits = torch.zeros(1, dtype=torch.int32, device=raw.device)
+    _call("bn_rice_unpack", _p(meta), _p(bits), nwords, _p(roff), _p(table), _p(raw), R, K, _p(out), _p(rend))
+    return out, rend
+
+
+def rice_to_r4(meta, bits, roff, table, R: int, K: int, esc_cap: int | None = None):
+    """The load-time expander: Rice arrays on the device -> (codes, flags, esc, row_esc, bad_row).
+
+    One host read of 32 bytes of counters per tensor (escape total, scratch claimed, first bad
+    row); the scratch is sized from the tile count and grown once if a tensor needs more."""
+    dev = meta.device
+    T = -(-K // TILE)
+    codes = torch.empty(R * T * 32, dtype=torch.int16, device=dev)
+    flags = torch.empty(R * T, dtype=torch.uint8, device=dev)
+    row_cnt = torch.empty(R, dtype=torch.int32, device=dev)
+    tmp_off = torch.empty(R, dtype=torch.int32, device=dev)
+    counters = torch.empty(8, dtype=torch.int32, device=dev)
+    nwords = bits.numel()
+    if nwords == 0:
+        bits = torch.zeros(1, dtype=torch.int32, device=dev)
+    cap = esc_cap if esc_cap is not None else max(4096, R * K // 8)
+    while True:
+        cap = min(cap, (1 << 32) - 1)
+        esc_tmp = torch.empty(cap, dtype=torch.uint8, device=dev)
+        _call("bn_rice_to_r4", _p(meta), _p(bits), nwords, _p(roff), _p(table), R, K, _p(codes), _p(flags), _p(row_cnt), _p(esc_tmp), cap, _p(tmp_off), _p(counters))
+        c = counters.cpu().numpy().view(np.uint32)
+        claimed = int(c[4]) | int(c[5]) << 32
+        if claimed <= cap:
+            break
+        if claimed >= 1 << 32:
+            raise ValueError("escape scratch of one call exceeds 4 GiB: expand the tensor in row chunks")
+        cap = claimed
+    n_esc = int(c[2])
+    bad_row = R - int(c[1]) if c[1] else -1
+    esc = torch.empty(n_esc + 1, dtype=torch.uint8, device=dev)
+    _call("bn_r4_finish", _p(row_cnt), _p(esc_tmp), _p(tmp_off), R, _p(row_cnt), _p(esc), n_esc + 1)
+    return codes, flags, esc, row_cnt, bad_row
+
+
+def r4_decode(a: dict, N: int, K: int, nb: int | None = None, rs: int | None = None, r0: int = 0) -> torch.Tensor:
+    """BF16 [N, K] from R4; output row r is storage row (r // nb) * rs + r0 + r % nb."""
+    out = torch.empty((N, K), dtype=torch.bfloat16, device=a["raw"].device)
+    nb = nb or max(N, 1)
+    _call("bn_r4_decode", ctypes.byref(r4_struct(a)), N, K, nb, rs or nb, r0, _p(out))
+    return out
+
+
+def r4_rows(a: dict, x: torch.Tensor, N: int, K: int) -> torch.Tensor:
+    """x [M, K] (1 <= M <= 16, bfloat16, contiguous rows) -> [M, N], fused decode."""
+    M = x.shape[0]
+    y = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
+    _call("bn_r4_rows", _p(x), x.stride(0), ctypes.byref(r4_struct(a)), M, N, K, _p(y), N)
+    return y
+
+
+def r4_matvec(a: dict, x: torch.Tensor, N: int, K: int) -> torch.Tensor:
+    """x [..., K] holding one row -> [..., N] (reference: r4_matvec, cuda_kernels.py:118-130)."""
+    y = torch.empty((*x.shape[:-1], N), dtype=torch.bfloat16, device=x.device)
+    _call("bn_r4_rows", _p(x), K, ctypes.byref(r4_struct(a)), 1, N, K, _p(y), N)
+    return y
+
+
+def r4_gather(a: dict, x: torch.Tensor, xi: torch.Tensor, ei: torch.Tensor, n: int, rs: int, r0: int, K: int, split: int | None = None, shape: tuple | None = None):
+    """[G, n] (or `shape`), or with split the pair [G, split], [G, n - split]
+    (reference: r4_gather, cuda_kernels.py:133-146). xi, ei: int32 tensors of G entries."""
+    G = ei.numel()
+    dev = x.device
+    if split:
+        y = torch.empty((G, split), dtype=torch.bfloat16, device=dev)
+        y2 = torch.empty((G, n - split), dtype=torch.bfloat16, device=dev)
+    else:
+        y, y2 = torch.empty(shape or (G, n), dtype=torch.bfloat16, device=dev), None
+    _call("bn_r4_gather", _p(x), ctypes.byref(r4_struct(a)), _p(xi), _p(ei), G, n, K, rs, r0, split or 0, _p(y), _p(y2))
+    return (y, y2) if split else y

@@ -1,0 +1,134 @@
+"""R4 runtime on CUDA: format-2 arrays from the file, 4-bit rank codes in GPU memory.
+
+Same roles and names as the reference's binade/mlx/r4.py, on torch:
+  transcode(module)   Rice arrays {raw, table, meta, bits, roff} -> R4 dict, on the GPU in one
+                      fused pass (reference: transcode + _rank_chunks, r4.py:119-175)
+  R4Linear(a)         the linear-layer hook: y = x @ W.T with W decoded inside the kernel
+  convert(model)      swap every BinadeLinear holder for an R4Linear in place (r4.py:375-410)
+
+Row counts: 1..16 input rows run the fused decode kernel (weights stream once, fp32 accumulation
+in the documented lane order); more rows rebuild the BF16 weight with the decode kernel and call
+torch.matmul, as the reference does for long prompts (r4.py:288).
+"""
+
+from __future__ import annotations
+
+import numpy as np
+import torch
+from torch import nn
+
+from ..format import TILE
+from . import kernels as ck
+
+FUSED_MAX_ROWS = 16  # input rows served by the fused decode kernel
+
+
+class BinadeLinear(nn.Module):
+    """Holder of one packed weight's file arrays (`weight` = dict of raw, table, meta, bits, roff,
+    numpy or torch) until `convert` turns it into an R4Linear. It cannot run."""
+
+    def __init__(self, weight: dict):
+        super().__init__()
+        self.weight = weight
+
+    def forward(self, x):
+        raise RuntimeError("packed weights run on the R4 runtime: call binade_b200.cuda.r4.convert(model)")
+
+
+def transcode(module) -> dict:
+    """R4 arrays for a format-2 module (anything with a `.weight` dict, or the dict itself).
+    Rows of K weights, K % 4 == 0 (raw bytes are read four at a time); a last tile with K % 128
+    weights is padded with code 0. Raises ValueError if a row's stream does not end where the
+    next one starts."""
+    w = module.weight if hasattr(module, "weight") else module
+    if "bits" not in w:
+        raise ValueError("only format 2 (Rice) arrays can be transcoded; format 1 is not implemented")
+    raw = ck.to_device(w["raw"])
+    K = raw.shape[-1]
+    R = raw.numel() // K if K else 0
+    if K % 4:
+        raise ValueError(f"R4 needs K % 4 == 0, got {K}")
+    T = -(-K // TILE)
+    meta, bits, roff, table = (ck.to_device(w[k]) for k in ("meta", "bits", "roff", "table"))
+    if meta.numel() != R * T or roff.numel() != R:
+        raise ValueError(f"{meta.numel()} tiles and {roff.numel()} row offsets for {R} x {K}")
+    codes, flags, esc, row_esc, bad = ck.rice_to_r4(meta, bits, roff, table, R, K)
+    if bad >= 0:
+        raise ValueError(f"Rice stream of row {bad} does not end where the next row starts")
+    return {"raw": raw.reshape(R, K), "table": table, "codes": codes, "flags": flags, "esc": esc, "row_esc": row_esc, "shape": tuple(raw.shape)}
+
+
+def r4_bytes(a: dict) -> int:
+    """Bytes a matvec streams: every R4 array (reference: scripts/matvec_bench.py:34-35)."""
+    return sum(a[k].numel() * a[k].element_size() for k in ck.R4_KEYS)
+
+
+class _R4:
+    """Shared R4 storage, the fused kernels and the BF16 rebuild."""
+
+    def _init_r4(self, a: dict):
+        self._a = a
+        self.N, self.K = a["raw"].shape
+        self.T = -(-self.K // TILE)
+
+    def _matvec(self, x: torch.Tensor) -> torch.Tensor:
+        """x [..., K] holding one row -> [..., N]."""
+        return ck.r4_matvec(self._a, x.contiguous(), self.N, self.K)
+
+    def _gather(self, x, xi, ei, n: int, rs: int, r0: int = 0, *, split: int | None = None, shape: tuple | None = None):
+        """[G, n] outputs (or `shape`): pair g multiplies input row xi[g] of x [.., K] by storage
+        rows ei[g] * rs + r0 .. + n. With split, the pair [G, split], [G, n - split]."""
+        return ck.r4_gather(self._a, x.contiguous(), xi.to(torch.int32), ei.reshape(-1).to(torch.int32), n, rs, r0, self.K, split, shape)
+
+    def dense(self, n: int | None = None, rs: int | None = None, r0: int = 0) -> torch.Tensor:
+        """The BF16 weight, rebuilt from R4. With n, rs, r0: rows r0 .. r0 + n - 1 of every block of
+        rs storage rows, as [N * n / rs, K]."""
+        if n is None:
+            return ck.r4_decode(self._a, self.N, self.K).reshape(self._a["shape"])
+        return ck.r4_decode(self._a, self.N // rs * n, self.K, n, rs, r0)
+
+    def _rows(self, x: torch.Tensor) -> torch.Tensor:
+        lead = x.shape[:-1]
+        M = x.numel() // self.K
+        if M == 1:
+            return self._matvec(x)
+        if M <= FUSED_MAX_ROWS:
+            return ck.r4_rows(self._a, x.reshape(M, self.K).contiguous(), self.N, self.K).reshape(*lead, self.N)
+        return x @ self.dense().reshape(self.N, self.K).T
+
+
+class R4Linear(nn.Module, _R4):
+    def __init__(self, a: dict):
+        nn.Module.__init__(self)
+        self._init_r4(a)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        return self._rows(x)
+
+
+def convert(model: nn.Module, log=None) -> int:
+    """Swap every BinadeLinear for an R4Linear in place; returns how many were converted. Each
+    holder's file arrays are dropped as soon as its R4 arrays exist."""
+    todo = [(parent, name) for parent in model.modules() for name, child in parent.named_children() if isinstance(child, BinadeLinear)]
+    for i, (parent, name) in enumerate(todo, 1):
+        holder = getattr(parent, name)
+        setattr(parent, name, R4Linear(transcode(holder)))
+        holder.weight = None
+        if log and (i % 50 == 0 or i == len(todo)):
+            log(f"R4 transcode {i}/{len(todo)}")
+    return len(todo)
+
+
+def holders(packed) -> dict:
+    """{tensor name: BinadeLinear} for every packed weight of an unpack.PackedModel (or a path to
+    a packed directory), file arrays read to host memory."""
+    from .. import st
+    from ..unpack import PackedModel
+
+    pm = packed if isinstance(packed, PackedModel) else PackedModel(packed)
+    out = {}
+    for name in pm.packed:
+        if f"{name}.bits" not in pm.infos:
+            raise ValueError(f"{name}: format 1 is not implemented")
+        out[name] = BinadeLinear({k: st.read(pm.infos[f"{name}.{k}"]) for k in ("raw", "table", "meta", "bits", "roff")})
+    return out

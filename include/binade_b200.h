@@ -1,0 +1,150 @@
+/*
+ * binade_b200 — C ABI of the B200 (sm_100a) implementation of Binade's data-parallel hot path.
+ *
+ * Two shared libraries export these symbols:
+ *   libbinade_b200.so       the CUDA entry points (section 2); links the CUDA runtime
+ *   libbinade_b200_host.so  the host-side codec used by the packer (section 3); no CUDA
+ *
+ * Conventions
+ *   - every entry point returns an int status: BN_OK or a BN_ERR_* code; bn_last_error()
+ *     returns a thread-local message for the last non-zero status of the calling thread;
+ *   - every pointer of section 2 is a DEVICE pointer owned by the caller (inputs are never
+ *     written; outputs must not alias inputs); the library allocates nothing unless stated;
+ *   - `stream` is a cudaStream_t passed as void* (NULL = the legacy default stream); calls only
+ *     enqueue work and return without synchronising;
+ *   - BF16 values travel as uint16_t bit patterns; all integers are little-endian;
+ *   - a matrix has R (or N) rows of K weights, T = ceil(K/128) tiles per row.
+ *
+ * Each declaration cites the interface of the reference project (GuyShafir/binade v0.1.2, paths
+ * relative to its root) that it replaces.
+ */
+#ifndef BINADE_B200_H
+#define BINADE_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ------------------------------------------------------------------ 1. status ------------- */
+#define BN_OK 0
+#define BN_ERR_ARG 1      /* null pointer, K % 4 != 0, size out of range ...                 */
+#define BN_ERR_CUDA 2     /* a CUDA runtime call or launch failed; see bn_last_error()       */
+#define BN_ERR_CAPACITY 3 /* an output or scratch buffer given by the caller is too small    */
+#define BN_ERR_STREAM 4   /* host codec: a Rice stream does not end where its meta says      */
+
+const char *bn_last_error(void);
+/* ABI version of the library: major * 100 + minor. */
+int bn_abi_version(void);
+
+/* The R4 in-memory layout of one matrix (binade/mlx/r4.py:143-175):
+ *   raw     [N*K]      sign<<7 | mantissa of every weight
+ *   codes   [N*T*32]   four 4-bit codes per uint16: nibble j of lane word l of tile t is
+ *                      min(rank, 15) of weight 128t + 4l + j; padding weights code 0
+ *   flags   [N*T]      non-zero iff the tile holds a code 15 (escape)
+ *   esc     [n_esc+1]  exponent bytes of the escaped weights, row-major order, one trailing 0
+ *   table   [256]      exponent by rank (only entries 0..14 are read by the kernels)
+ *   row_esc [N]        number of escapes before each row                                    */
+typedef struct bn_r4 {
+  const uint8_t *raw;
+  const uint16_t *codes;
+  const uint8_t *flags;
+  const uint8_t *esc;
+  const uint8_t *table;
+  const uint32_t *row_esc;
+} bn_r4;
+
+/* ------------------------------------------------------------------ 2. CUDA entry points -- */
+
+/* Rice stream -> 8-bit ranks. Replaces rice_ranks, binade/mlx/cuda_kernels.py:974-995
+ * (Metal twin binade/mlx/rice_kernel.py:71-98).
+ *   meta [R*T], bits [nwords], roff [R]  ->  ranks [R, T*128] (padding columns 0),
+ *   rend [R] = word after the row's last bit; the caller compares it with the next row's roff.
+ * Reads of `bits` are clamped to [0, nwords): a corrupt stream cannot read out of bounds. */
+int bn_rice_ranks(const uint8_t *meta, const uint32_t *bits, uint64_t nwords, const uint32_t *roff,
+                  int64_t R, int64_t K, uint8_t *ranks, uint32_t *rend, void *stream);
+
+/* Rice stream + raw bytes -> BF16 words [R,K], the decode of PackedModel.rows
+ * (binade/unpack.py:68-94: rice_ranks, table lookup and bf16.join in one pass). */
+int bn_rice_unpack(const uint8_t *meta, const uint32_t *bits, uint64_t nwords, const uint32_t *roff,
+                   const uint8_t *table, const uint8_t *raw, int64_t R, int64_t K, uint16_t *out,
+                   uint32_t *rend, void *stream);
+
+/* Load-time expander, Rice -> R4, step 1 of 2. Replaces transcode + _rank_chunks
+ * (binade/mlx/r4.py:119-175), which decode to 8-bit ranks, re-read them with elementwise ops
+ * and gather escapes on the host.
+ *   outputs  codes [R*T*32], flags [R*T], row_cnt [R] (escapes of each row)
+ *   scratch  esc_tmp [esc_cap] escape bytes, esc_cap < 2^32; each row claims, at tmp_off[r], room
+ *            for the most escapes its meta bytes allow (a tile can escape only if
+ *            qmax << k | (2^k - 1) >= 15) and writes its escapes there in order;
+ *            tmp_off [R]; counters: 8 x uint32, 8-byte aligned, zeroed by the call itself:
+ *              [1]    R - (first row whose stream does not end at the next row's roff, or at
+ *                     nwords for the last row); 0 = every row ends where it must
+ *              [2]    total number of escapes
+ *              [4..5] uint64: bytes of esc_tmp claimed
+ * When the claimed bytes exceed esc_cap some rows wrote no escape bytes: call again with an
+ * esc_tmp of at least that size (codes, flags, row_cnt and counters are complete either way). */
+int bn_rice_to_r4(const uint8_t *meta, const uint32_t *bits, uint64_t nwords, const uint32_t *roff,
+                  const uint8_t *table, int64_t R, int64_t K, uint16_t *codes, uint8_t *flags,
+                  uint32_t *row_cnt, uint8_t *esc_tmp, uint64_t esc_cap, uint32_t *tmp_off,
+                  uint32_t *counters, void *stream);
+
+/* Expander step 2: row_esc = exclusive prefix sum of row_cnt (may alias row_cnt), and the
+ * escape runs of esc_tmp compacted into row order: esc [n_esc + 1], last byte 0
+ * (binade/mlx/r4.py:164-173). esc must hold counters[2] + 1 bytes. */
+int bn_r4_finish(const uint32_t *row_cnt, const uint8_t *esc_tmp, const uint32_t *tmp_off, int64_t R,
+                 uint32_t *row_esc, uint8_t *esc, uint64_t esc_bytes, void *stream);
+
+/* R4 -> dense BF16 [N,K]; output row r is storage row (r / NB) * RS + R0 + r % NB.
+ * Replaces r4_decode, binade/mlx/cuda_kernels.py:897-916. */
+int bn_r4_decode(const bn_r4 *w, int64_t N, int64_t K, int64_t NB, int64_t RS, int64_t R0,
+                 uint16_t *out, void *stream);
+
+/* Fused R4-decode products Y [M,N] = X [M,K] . W^T for 1 <= M <= 16 input rows, fp32
+ * accumulation in a fixed order per output: 32 lanes, lane l owns weights 128t + 4l + j and adds
+ * their products (fused multiply-add) for t then j ascending; columns >= K are skipped; lanes
+ * combine with strides 16, 8, 4, 2, 1; one round-to-nearest-even to BF16. M = 1 replaces
+ * r4_matvec, binade/mlx/cuda_kernels.py:118-130 (same order for K % 128 == 0). The weights are
+ * read once whatever M. x_stride / y_stride: elements between rows of X / Y. */
+int bn_r4_rows(const uint16_t *x, int64_t x_stride, const bn_r4 *w, int64_t M, int64_t N, int64_t K,
+               uint16_t *y, int64_t y_stride, void *stream);
+
+/* G independent matvecs (the decode step of a mixture of experts). Slot g multiplies input row
+ * xi[g] of x [., K] by storage rows ei[g] * RS + R0 + r, r < n. With split == 0 results go to
+ * y [G, n]; with 0 < split < n, rows below split go to y [G, split] and the rest to
+ * y2 [G, n - split]. Replaces r4_gather, binade/mlx/cuda_kernels.py:133-146. */
+int bn_r4_gather(const uint16_t *x, const bn_r4 *w, const uint32_t *xi, const uint32_t *ei, int64_t G,
+                 int64_t n, int64_t K, int64_t RS, int64_t R0, int64_t split, uint16_t *y,
+                 uint16_t *y2, void *stream);
+
+/* ------------------------------------------------------------------ 3. host codec --------- */
+
+/* Last error message of the calling thread, for the host codec library. */
+const char *bn_host_last_error(void);
+
+/* BF16 words -> raw bytes, exponent histogram (binade/bf16.py:20-33 and the first pass of
+ * pack_tensor, binade/pack.py:74-75). hist [256] is ADDED to. raw may be NULL. */
+int bn_host_split_hist(const uint16_t *w, int64_t n, uint8_t *raw, int64_t *hist);
+
+/* Histogram -> (table, rank). binade/format.py:34-42. */
+int bn_host_rank_table(const int64_t *hist, uint8_t *table, uint8_t *rank);
+
+/* Format-2 (Rice) encoder over rows of BF16 words: binade/rice.py:57-125 fed with
+ * rank[bf16.exponent(w)] as pack_tensor does (binade/pack.py:80-83).
+ *   w [R*K], rank [256] -> meta [R*T], roff [R], words [cap_words].
+ * Returns in *nwords the stream length; when it exceeds cap_words (or words == NULL) nothing is
+ * written to `words` and the status is BN_ERR_CAPACITY, so a first call can size the buffer.
+ * `threads` <= 0 uses every available core. */
+int bn_host_rice_encode(const uint16_t *w, const uint8_t *rank, int64_t R, int64_t K, uint8_t *meta,
+                        uint32_t *roff, uint32_t *words, uint64_t cap_words, uint64_t *nwords,
+                        int threads);
+
+/* The same encoder fed with ready-made ranks [R*K] (encode_ranks, binade/rice.py:76-119). */
+int bn_host_rice_encode_ranks(const uint8_t *ranks, int64_t R, int64_t K, uint8_t *meta, uint32_t *roff,
+                              uint32_t *words, uint64_t cap_words, uint64_t *nwords, int threads);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* BINADE_B200_H */

@@ -1,0 +1,364 @@
+"""GPU parity: every CUDA entry point, called through the C ABI, against the CPU oracle.
+
+Bit-exact for the integer work (Rice decode, R4 expansion, dense decode); the fused products are
+compared bit for bit with the oracle's same-order fp32 sums and with a PyTorch fp32 reference
+that adds in the same order."""
+
+import numpy as np
+import pytest
+import torch
+
+from conftest import GOLDEN, golden
+from oracle import oracle as o
+
+pytestmark = pytest.mark.gpu
+
+CODEC = golden("codec_cases.npz")
+CASES = [c for c in CODEC if "exps" in CODEC[c]]
+
+
+def bf16_words(a: np.ndarray) -> np.ndarray:
+    v = np.ascontiguousarray(a, np.float32).view(np.uint32).astype(np.uint64)
+    return ((v + 0x7FFF + ((v >> 16) & 1)) >> 16).astype(np.uint16)
+
+
+def weights(rng, shape, scale=0.02, escapes=True):
+    """BF16 words: row-scaled normal values, some -0, a few rare large exponents (escapes)."""
+    w = rng.standard_normal(shape) * scale * np.exp(rng.standard_normal(shape[:-1] + (1,)))
+    u = bf16_words(w)
+    flat = u.reshape(-1)
+    flat[::997] = 0x8000
+    if escapes:
+        flat[5::199] = 0x3F80 | 0x4000
+        flat[11::311] = bf16_words(np.array([3.0e-9], np.float32))[0]
+    return u
+
+
+def words(t: torch.Tensor) -> np.ndarray:
+    return t.contiguous().view(torch.int16).cpu().numpy().view(np.uint16)
+
+
+def dev(a: np.ndarray) -> torch.Tensor:
+    from binade_b200.cuda import kernels as ck
+
+    return ck.to_device(a)
+
+
+def r4_on_device(a: dict) -> dict:
+    d = {k: dev(a[k]) for k in ("raw", "codes", "flags", "esc", "table", "row_esc")}
+    d["raw"] = d["raw"].reshape(a["shape"][-2] if len(a["shape"]) == 2 else -1, a["shape"][-1])
+    d["shape"] = a["shape"]
+    return d
+
+
+def packed_arrays(u: np.ndarray) -> dict:
+    from binade_b200 import pack
+
+    return pack.pack(u)
+
+
+def torch_same_order(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    """PyTorch fp32 reference of the documented order: x [M,K], w [N,K] bfloat16 -> [M,N] bfloat16.
+    Lane l owns columns 128t + 4l + j; per lane sequential fp32 adds over t then j; lanes combine
+    with strides 16, 8, 4, 2, 1; one rounding to BF16."""
+    M, K = x.shape
+    N = w.shape[0]
+    T = -(-K // 128)
+    xf = torch.zeros((M, T * 128), dtype=torch.float32, device=x.device)
+    wf = torch.zeros((N, T * 128), dtype=torch.float32, device=x.device)
+    xf[:, :K], wf[:, :K] = x.float(), w.float()
+    real = (torch.arange(T * 128, device=x.device) < K).view(T, 32, 4)
+    xf, wf = xf.view(M, 1, T, 32, 4), wf.view(1, N, T, 32, 4)
+    acc = torch.zeros((M, N, 32), dtype=torch.float32, device=x.device)
+    for t in range(T):
+        for j in range(4):
+            prod = wf[:, :, t, :, j] * xf[:, :, t, :, j]  # exact: two BF16 factors
+            acc = torch.where(real[t, :, j], acc + prod, acc)
+    for s in (16, 8, 4, 2, 1):
+        acc = acc[..., :s] + acc[..., s : 2 * s]
+    return acc[..., 0].to(torch.bfloat16)
+
+
+# ------------------------------------------------------------------------------ Rice decode
+@pytest.mark.parametrize("case", CASES)
+def test_rice_ranks_golden(case):
+    from binade_b200.cuda import kernels as ck
+
+    g = CODEC[case]
+    R, K = g["exps"].shape
+    ranks, rend = ck.rice_ranks(dev(g["meta"]), dev(g["bits"]), dev(g["roff"]), K)
+    got = ranks.cpu().numpy()
+    assert np.array_equal(got[:, :K], g["ranks"])
+    assert not got[:, K:].any()
+    assert np.array_equal(rend.cpu().numpy().view(np.uint32), (g["end"] + 31) >> 5)
+
+
+@pytest.mark.parametrize("R,K", [(1, 5), (40, 100), (24, 704), (64, 1000), (7, 256), (300, 3840), (33, 15360)])
+def test_rice_ranks_shapes(R, K):
+    from binade_b200 import rice
+    from binade_b200.cuda import kernels as ck
+
+    rng = np.random.default_rng(K)
+    ranks = np.minimum(rng.geometric(0.35, size=(R, K)) - 1, 255).astype(np.uint8)
+    ranks[::5, ::97] = rng.integers(0, 256, size=ranks[::5, ::97].shape)
+    meta, bits, roff = rice.encode_ranks(ranks)
+    ref, end = o.c_rice_decode_ranks(meta, bits, roff, K)
+    assert np.array_equal(ref, ranks)
+    got, rend = ck.rice_ranks(dev(meta), dev(bits), dev(roff), K)
+    got, rend = got.cpu().numpy(), rend.cpu().numpy().view(np.uint32)
+    assert np.array_equal(got[:, :K], ranks) and not got[:, K:].any()
+    assert np.array_equal(rend, (end + 31) >> 5)
+    assert np.array_equal(rend, np.append(roff[1:], bits.size))
+
+
+def test_rice_decode_and_errors():
+    from binade_b200 import rice
+
+    g = CODEC["geometric_20x1000"]
+    enc = rice.RiceEncoded(g["table"], g["meta"], g["bits"], g["roff"])
+    assert np.array_equal(rice.decode(enc, 20, 1000), g["exps"])
+    with pytest.raises(ValueError):
+        rice.decode(rice.RiceEncoded(g["table"], g["meta"], g["bits"][:-1], g["roff"]), 20, 1000)
+    with pytest.raises(ValueError):
+        rice.decode(enc, 19, 1000)
+
+
+def test_every_bf16_pattern_round_trips():
+    from binade_b200 import pack, unpack
+
+    w = np.random.default_rng(1).permutation(np.arange(1 << 16, dtype=np.uint32).astype(np.uint16)).reshape(256, 256)
+    assert np.array_equal(unpack.unpack(pack.pack(w)), w)
+
+
+@pytest.mark.parametrize("shape", [(96, 704), (7, 5), (3, 40, 100), (1, 1)])
+def test_pack_unpack_round_trip(shape):
+    from binade_b200 import pack, unpack
+
+    u = weights(np.random.default_rng(sum(shape)), shape)
+    p = pack.pack(u)
+    assert np.array_equal(unpack.unpack(p), u)
+    if u.size > 4:
+        bad = dict(p, bits=p["bits"][:-1])
+        with pytest.raises(ValueError):
+            unpack.unpack(bad)
+
+
+def test_packed_model_restores_every_tensor(tmp_path):
+    from binade_b200 import st
+    from binade_b200.unpack import PackedModel
+
+    pm = PackedModel(GOLDEN / "packed_model" / "packed")
+    orig = {i.name: i for i in st.list_tensors(GOLDEN / "packed_model" / "src")}
+    assert sorted(pm.names()) == sorted(orig)
+    assert set(pm.packed) == {"model.embed_tokens.weight", "model.layers.0.self_attn.q_proj.weight", "model.layers.0.experts.gate_up_proj", "lm_head.weight"}
+    for name, info in orig.items():
+        assert np.array_equal(pm.tensor(name), st.read(info)), name
+    rows = list(pm.rows("lm_head.weight", chunk=5000))
+    assert len(rows) > 1 and rows[0][0] == 0 and rows[-1][1] == 300
+
+
+# ------------------------------------------------------------------------------ Rice -> R4
+@pytest.mark.parametrize("case", list(golden("r4_layout.npz")))
+def test_transcode_golden_layout(case):
+    from binade_b200.cuda import r4
+
+    g = golden("r4_layout.npz")[case]
+    a = r4.transcode(packed_arrays(g["w"]))
+    assert np.array_equal(a["codes"].cpu().numpy().view(np.uint16), g["codes"])
+    assert np.array_equal(a["flags"].cpu().numpy(), g["flags"])
+    assert np.array_equal(a["esc"].cpu().numpy(), g["esc"])
+    assert np.array_equal(a["row_esc"].cpu().numpy().view(np.uint32), g["row_esc"])
+    assert np.array_equal(words(r4.R4Linear(a).dense()), g["w"])
+
+
+@pytest.mark.parametrize("N,K", [(64, 704), (160, 2112), (300, 260), (48, 100), (64, 128), (40, 4), (300, 3840), (17, 15360)])
+def test_transcode_matches_oracle(N, K):
+    from binade_b200.cuda import r4
+
+    u = weights(np.random.default_rng(K), (N, K))
+    want = o.pack_r4(u)
+    a = r4.transcode(packed_arrays(u))
+    for k, dt in (("codes", np.uint16), ("flags", np.uint8), ("esc", np.uint8), ("row_esc", np.uint32)):
+        got = a[k].cpu().numpy()
+        assert np.array_equal(got.view(dt) if got.dtype.itemsize == np.dtype(dt).itemsize else got, want[k]), k
+    assert np.array_equal(words(r4.R4Linear(a).dense()), u)
+    assert a["shape"] == (N, K) and r4.r4_bytes(a) == sum(want[k].nbytes for k in ("raw", "codes", "flags", "esc", "table", "row_esc"))
+
+
+def test_transcode_all_escapes_grows_scratch():
+    """Uniform exponents: nearly every weight escapes, far beyond the default scratch size."""
+    from binade_b200.cuda import r4
+
+    rng = np.random.default_rng(3)
+    u = rng.integers(0, 1 << 16, size=(64, 1024), dtype=np.uint16)
+    want = o.pack_r4(u)
+    a = r4.transcode(packed_arrays(u))
+    assert a["esc"].numel() - 1 > 64 * 1024 * 0.8
+    assert np.array_equal(a["esc"].cpu().numpy(), want["esc"])
+    assert np.array_equal(a["row_esc"].cpu().numpy().view(np.uint32), want["row_esc"])
+    assert np.array_equal(words(r4.R4Linear(a).dense()), u)
+
+
+def test_transcode_rejects_bad_input():
+    from binade_b200.cuda import r4
+
+    u = weights(np.random.default_rng(0), (8, 256))
+    p = packed_arrays(u)
+    with pytest.raises(ValueError):
+        r4.transcode(dict(p, bits=p["bits"][:-1]))
+    with pytest.raises(ValueError):
+        r4.transcode(packed_arrays(weights(np.random.default_rng(0), (8, 6))))
+    with pytest.raises(ValueError):
+        r4.transcode(dict(p, roff=p["roff"][:-1]))
+
+
+def test_dense_row_remap():
+    """dense(n, rs, r0): rows r0 .. r0+n-1 of every block of rs storage rows (expert halves)."""
+    from binade_b200.cuda import r4
+
+    E, n, K = 4, 24, 384
+    u = weights(np.random.default_rng(9), (E, 2 * n, K))
+    m = r4.R4Linear(r4.transcode(packed_arrays(u)))
+    assert np.array_equal(words(m.dense(n, 2 * n, 0)).reshape(E, n, K), u[:, :n])
+    assert np.array_equal(words(m.dense(n, 2 * n, n)).reshape(E, n, K), u[:, n:])
+    assert np.array_equal(words(m.dense()), u)
+
+
+# ------------------------------------------------------------------------------ fused products
+@pytest.mark.parametrize("N,K", [(64, 704), (160, 2112), (300, 260), (48, 100), (64, 128), (40, 4), (4096, 512), (520, 3840), (200, 15360)])
+def test_matvec_bit_exact(N, K):
+    from binade_b200.cuda import r4
+
+    rng = np.random.default_rng(N + K)
+    u = weights(rng, (N, K))
+    xw = bf16_words(rng.standard_normal((1, K)))
+    m = r4.R4Linear(r4.transcode(packed_arrays(u)))
+    x = dev(xw).view(torch.bfloat16)
+    got = m(x)
+    assert got.shape == (1, N) and got.dtype == torch.bfloat16
+    want = o.c_r4_matvec(o.pack_r4(u), xw[0], N, K)
+    assert np.array_equal(words(got)[0], want)
+    ref = torch_same_order(x, dev(u).view(torch.bfloat16))
+    assert np.array_equal(words(got), words(ref))
+
+
+def adversarial(R: int, K: int, seed: int = 0) -> np.ndarray:
+    """Rows whose sum with an all-ones input depends on the order: +2^25 first, then ones that
+    vanish against it (fp32 ulp at 2^25 is 4), then -2^25: 0 in the documented order. Row types
+    cycle: the pattern on one lane (columns 128j), on every 8th column, random values. The 2^25
+    exponent is rare, so these rows also exercise escapes."""
+    big = 2.0**25
+    w = np.zeros((R, K), np.float32)
+    last = 128 * ((K - 1) // 128)
+    w[0::3, 0], w[0::3, last] = big, -big
+    w[0::3, 128:last:128] = 1.0
+    w[1::3, 0], w[1::3, K - 8] = big, -big
+    w[1::3, 8 : K - 8 : 8] = 1.0
+    w[2::3] = np.random.default_rng(seed).standard_normal(w[2::3].shape) * 0.02
+    return bf16_words(w)
+
+
+@pytest.mark.parametrize("N,K", [(96, 704), (4096, 512), (512, 2048), (48, 2816)])
+def test_order_sensitive_rows(N, K):
+    from binade_b200.cuda import r4
+
+    u = adversarial(N, K)
+    m = r4.R4Linear(r4.transcode(packed_arrays(u)))
+    W = dev(u).view(torch.bfloat16)
+    for M in (1, 2, 3, 8, 15, 16):
+        x = torch.ones((M, K), dtype=torch.bfloat16, device="cuda")
+        got = m(x)
+        assert np.array_equal(words(got), words(torch_same_order(x, W))), M
+        assert np.array_equal(words(got), o.c_dense_rows(words(x), u)), M
+    y = words(m(torch.ones((1, K), dtype=torch.bfloat16, device="cuda")))[0]
+    exact = o.bf16_to_f32(u).astype(np.float64).sum(axis=1)
+    assert not y[0::3].any()  # lane pattern: exactly 0 in the documented order
+    assert np.any(o.bf16_to_f32(y[1::3]) != exact[1::3])  # another grouping rounds differently
+
+
+@pytest.mark.parametrize("M", [2, 4, 5, 8, 11, 16])
+def test_small_m_rows(M):
+    from binade_b200.cuda import r4
+
+    N, K = 333, 1664
+    rng = np.random.default_rng(M)
+    u = weights(rng, (N, K))
+    xw = bf16_words(rng.standard_normal((M, K)))
+    m = r4.R4Linear(r4.transcode(packed_arrays(u)))
+    got = m(dev(xw).view(torch.bfloat16).reshape(1, M, K))
+    assert got.shape == (1, M, N)
+    assert np.array_equal(words(got)[0], o.c_dense_rows(xw, u))
+
+
+def test_many_rows_rebuild_path():
+    from binade_b200.cuda import r4
+
+    N, K, M = 256, 512, 40
+    rng = np.random.default_rng(5)
+    u = weights(rng, (N, K))
+    m = r4.R4Linear(r4.transcode(packed_arrays(u)))
+    x = dev(bf16_words(rng.standard_normal((M, K)))).view(torch.bfloat16)
+    W = dev(u).view(torch.bfloat16)
+    assert torch.equal(m(x), x @ W.T)
+
+
+@pytest.mark.parametrize("E,N,K,topk", [(8, 176, 704, 4), (8, 704, 176, 4), (6, 96, 384, 2), (16, 64, 520, 8)])
+def test_gather(E, N, K, topk):
+    from binade_b200.cuda import r4
+
+    rng = np.random.default_rng(N * K)
+    u = weights(rng, (E, N, K))
+    m = r4.R4Linear(r4.transcode(packed_arrays(u)))
+    a = o.pack_r4(u.reshape(E * N, K))
+    sel = rng.choice(E, size=topk, replace=False).astype(np.uint32)
+    # one shared input row (gate/up), then one input row per selected expert (down)
+    for xi in (np.zeros(topk, np.uint32), np.arange(topk, dtype=np.uint32)):
+        xw = bf16_words(rng.standard_normal((int(xi.max()) + 1, K)))
+        got = m._gather(dev(xw).view(torch.bfloat16), dev(xi), dev(sel), N, N)
+        assert np.array_equal(words(got), o.c_r4_gather(a, xw, xi, sel, N, K, N))
+    # the upper half of fused rows, and the split form
+    half = N // 2
+    xw = bf16_words(rng.standard_normal((1, K)))
+    xi = np.zeros(topk, np.uint32)
+    want = o.c_r4_gather(a, xw, xi, sel, N, K, N)
+    got = m._gather(dev(xw).view(torch.bfloat16), dev(xi), dev(sel), N - half, N, half)
+    assert np.array_equal(words(got), want[:, half:])
+    lo, hi = m._gather(dev(xw).view(torch.bfloat16), dev(xi), dev(sel), N, N, split=half)
+    assert np.array_equal(words(lo), want[:, :half]) and np.array_equal(words(hi), want[:, half:])
+
+
+def test_order_sensitive_gather():
+    from binade_b200.cuda import r4
+
+    E, N, K, topk = 8, 48, 704, 4
+    u = adversarial(E * N, K).reshape(E, N, K)
+    m = r4.R4Linear(r4.transcode(packed_arrays(u)))
+    sel = np.array([5, 0, 7, 2], np.uint32)
+    got = m._gather(torch.ones((1, K), dtype=torch.bfloat16, device="cuda"), dev(np.zeros(topk, np.uint32)), dev(sel), N, N)
+    want = o.c_r4_gather(o.pack_r4(u.reshape(E * N, K)), np.full((1, K), 0x3F80, np.uint16), np.zeros(topk, np.uint32), sel, N, K, N)
+    assert np.array_equal(words(got), want)
+
+
+def test_convert_swaps_holders():
+    from binade_b200.cuda import r4
+
+    rng = np.random.default_rng(2)
+    u1, u2 = weights(rng, (128, 256)), weights(rng, (64, 128))
+
+    class Block(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.up = r4.BinadeLinear(packed_arrays(u1))
+            self.down = r4.BinadeLinear(packed_arrays(u2))
+            self.norm = torch.nn.LayerNorm(4)
+
+    model = torch.nn.Sequential(Block())
+    with pytest.raises(RuntimeError):
+        model[0].up(torch.zeros(1, 256))
+    assert r4.convert(model) == 2
+    assert isinstance(model[0].up, r4.R4Linear) and (model[0].up.N, model[0].up.K, model[0].up.T) == (128, 256, 2)
+    assert np.array_equal(words(model[0].down.dense()), u2)
+    hs = r4.holders(GOLDEN / "packed_model" / "packed")
+    assert set(hs) == {"model.embed_tokens.weight", "model.layers.0.self_attn.q_proj.weight", "model.layers.0.experts.gate_up_proj", "lm_head.weight"}
+    a = r4.transcode(hs["lm_head.weight"])
+    assert a["shape"] == (300, 256)
