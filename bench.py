@@ -228,12 +228,13 @@ def run_ours(args) -> dict | None:
         return out
 
     # ---- parity of this very workload against the oracle, on one small projection
-    if rank == 0:
+    if rank == 0 and not args.no_parity:
         from oracle import oracle as o
 
-        name, n, k = SHAPES[1]
+        j = min(range(len(SHAPES)), key=lambda i: SHAPES[i][1] * SHAPES[i][2])
+        name, n, k = SHAPES[j]
         want = o.c_r4_matvec(o.pack_r4(synthetic_weight(name, n, k, rank)), synthetic_input(k, rank), n, k)
-        got = layers[1][3][0]._matvec(xs[k]).view(torch.int16).cpu().numpy().view(np.uint16)
+        got = layers[j][3][0]._matvec(xs[k]).view(torch.int16).cpu().numpy().view(np.uint16)
         if not np.array_equal(got, want):
             raise SystemExit("bench: GPU matvec differs from the oracle; refusing to report a number")
 
@@ -283,17 +284,16 @@ def run_ours(args) -> dict | None:
     ms_per_step = ms / args.steps
     value = world * step_bytes / (ms_per_step * 1e-3) / 1e9
 
-    # ---- per shape: the matvec alone, rotating copies, graph-captured
-    per_shape = {}
-    for name, n, k, mods, nbytes in layers:
+    # ---- per shape: the matvec alone and cuBLAS BF16 GEMV on the pre-decoded weight, both
+    # rotating the same copies inside a CUDA graph
+    def graph_us(fn, iters=60):
         g = torch.cuda.CUDAGraph()
-        iters = 40
         with torch.cuda.stream(side):
-            mods[0]._matvec(xs[k])
+            fn(0)
             side.synchronize()
             with torch.cuda.graph(g, stream=side):
                 for i in range(iters):
-                    mods[i % copies]._matvec(xs[k])
+                    fn(i)
         torch.cuda.synchronize()
         g.replay()
         torch.cuda.synchronize()
@@ -302,20 +302,16 @@ def run_ours(args) -> dict | None:
         g.replay()
         e1.record()
         torch.cuda.synchronize()
-        us = e0.elapsed_time(e1) * 1e3 / iters
-        # BF16 baseline: cuBLAS GEMV on the pre-decoded weight, same rotation
+        return e0.elapsed_time(e1) * 1e3 / iters
+
+    per_shape = {}
+    for name, n, k, mods, nbytes in layers if not args.quick else []:
+        us = graph_us(lambda i: mods[i % copies]._matvec(xs[k]))
         dense = [m.dense() for m in mods]
-        for i in range(3):
-            torch.mv(dense[i % copies], xs[k])
-        torch.cuda.synchronize()
-        e0.record()
-        for i in range(iters):
-            torch.mv(dense[i % copies], xs[k])
-        e1.record()
-        torch.cuda.synchronize()
-        us_bf16 = e0.elapsed_time(e1) * 1e3 / iters
-        per_shape[name] = {"us": round(us, 2), "gbs": round(nbytes / us / 1e3, 1), "bf16_gemv_us": round(us_bf16, 2), "speedup_vs_bf16": round(us_bf16 / us, 3)}
-        del dense, g
+        outs = [torch.empty(n, dtype=torch.bfloat16, device=dev) for _ in range(copies)]
+        us_bf16 = graph_us(lambda i: torch.mv(dense[i % copies], xs[k], out=outs[i % copies]))
+        per_shape[name] = {"us": round(us, 2), "gbs": round(nbytes / us / 1e3, 1), "pct_of_8tbs": round(nbytes / us / 1e3 / NOMINAL_HBM_GBS * 100, 1), "bf16_gemv_us": round(us_bf16, 2), "speedup_vs_bf16": round(us_bf16 / us, 3)}
+        del dense, outs
 
     # ---- end to end through the public hook with host buffers
     k_list = sorted({k for _, _, k in SHAPES})
@@ -331,11 +327,11 @@ def run_ours(args) -> dict | None:
             h_y[j].copy_(y, non_blocking=True)
         torch.cuda.synchronize()
 
+    e2e_steps = 3 if args.quick else min(args.steps, 200)
     for i in range(3):
         e2e_step(i)
     if world > 1:
         dist.barrier()
-    e2e_steps = min(args.steps, 200)
     ev0.record()
     for i in range(e2e_steps):
         e2e_step(i)
@@ -365,7 +361,7 @@ def run_ours(args) -> dict | None:
         "pct_of_nominal_8tbs": round(100 * value / world / NOMINAL_HBM_GBS, 2),
         "bits_per_weight": {"file_format2": round(bits_file / numel, 3), "r4_in_memory": round(bits_r4 / numel, 3)},
         "shapes": per_shape,
-        "speedup_vs_bf16_gemv_per_token": round(sum(v["bf16_gemv_us"] for v in per_shape.values()) / sum(v["us"] for v in per_shape.values()), 3),
+        "speedup_vs_bf16_gemv_per_token": round(sum(v["bf16_gemv_us"] for v in per_shape.values()) / sum(v["us"] for v in per_shape.values()), 3) if per_shape else None,
         "expander": {"ms_per_layer": round(expand_ms, 3), "gbs": round(expand_bytes / expand_ms / 1e6, 1), "algorithmic_bytes": expand_bytes, "host_pack_s": round(host_pack_s, 2), "host_pack_cores": cpu_cores()},
         "roofline": {"bound": "hbm", "kernel": "r4_rows_kernel<M=1> (all 7 launches of a step)", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"], "peak_source": peaks["source"], "bytes_per_launch": per_launch_bytes, "traffic": args.traffic},
         "e2e": {"value": e2e_val, "unit": UNIT, "ms_per_step": e2e_ms, "h2d_bytes_per_step": sum(2 * k for k in k_list), "d2h_bytes_per_step": sum(2 * n for _, n, _ in SHAPES), "api": "R4Linear.__call__ on host-resident inputs, outputs copied back to pinned host memory"},
@@ -373,7 +369,7 @@ def run_ours(args) -> dict | None:
         "clocks": clocks.summary(),
     }  # fmt: skip
     # ---- CPU baseline on a bounded sample (rank 0, single GPU runs only)
-    if world == 1 and not args.no_cpu:
+    if world == 1 and not args.no_cpu and not args.quick:
         mats = cpu_r4_layer(0, names={"q", "k"})
         cxs = {k: synthetic_input(k, 0) for k in {m[2] for m in mats}}
         cpu_step(mats, cxs)
@@ -398,8 +394,14 @@ def main():
     ap.add_argument("--impl", default="ours", choices=("ours", "reference"))
     ap.add_argument("--copies", type=int, default=3, help="weight copies rotated between steps")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--shapes", default="", help="comma list of matrices to keep (default: all seven); for small profiling runs")
+    ap.add_argument("--quick", action="store_true", help="timed region only: skip the per-shape, end-to-end and CPU legs")
+    ap.add_argument("--no-parity", action="store_true", help="skip the oracle check (only for kernel experiments whose output is wrong on purpose)")
     ap.add_argument("--traffic", type=float, default=None, help="DRAM bytes per launch from an ncu capture, if known")
     args = ap.parse_args()
+    if args.shapes:
+        keep = set(args.shapes.split(","))
+        SHAPES[:] = [sh for sh in SHAPES if sh[0] in keep]
     if args.impl == "reference":
         if int(os.environ.get("RANK", 0)) != 0:
             return

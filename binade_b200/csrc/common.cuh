@@ -28,6 +28,9 @@ inline int launched(const char *what) {
   return e == cudaSuccess ? BN_OK : fail_cuda(e, what);
 }
 
+// Streaming batch-1 matvec (r4_stream.cu); -1 when the shape is outside its coverage.
+int stream_matvec(const bn_r4 *w, const uint16_t *x, int64_t N, int64_t K, uint16_t *y, cudaStream_t s);
+
 inline int64_t tiles(int64_t K) { return (K + BN_TILE - 1) / BN_TILE; }
 
 // Raises a kernel's dynamic shared memory limit once per (kernel, device).

@@ -323,6 +323,10 @@ extern "C" int bn_r4_rows(const uint16_t *x, int64_t x_stride, const bn_r4 *w, i
   a.m = (int)M;
   // the instantiation is the next power of two >= M: absent input rows are zeros in shared
   // memory and are never stored, so the weights stream once whatever M
+  if (M == 1 && x_stride >= 0) {
+    const int e = stream_matvec(w, x, N, K, y, s);
+    if (e >= 0) return e;
+  }
   if (M == 1) return N >= 8192 ? launch_rows<1, 2, false>(a, 1, s) : launch_rows<1, 1, false>(a, 1, s);
   if (M == 2) return launch_rows<2, 2, false>(a, 1, s);
   if (M <= 4) return launch_rows<4, 2, false>(a, 1, s);

@@ -118,6 +118,12 @@ int bn_r4_gather(const uint16_t *x, const bn_r4 *w, const uint32_t *xi, const ui
                  int64_t n, int64_t K, int64_t RS, int64_t R0, int64_t split, uint16_t *y,
                  uint16_t *y2, void *stream);
 
+/* Device-side status of the calling thread's current device: 0, or non-zero once a kernel of
+ * this library gave up a bounded wait (its output is then incomplete). Every wait inside the
+ * kernels is bounded, so a lost copy ends in this status instead of a hang. Synchronises with
+ * the device. No counterpart in the reference. */
+int bn_device_status(int *status);
+
 /* ------------------------------------------------------------------ 3. host codec --------- */
 
 /* Last error message of the calling thread, for the host codec library. */
