@@ -33,6 +33,7 @@ SHAPES = [("q", 4096, 3840), ("k", 2048, 3840), ("v", 2048, 3840), ("o", 3840, 4
 WORKLOAD = "config2: Rice->R4 expansion + batch-1 fused R4 matvec, 7 matrices of a 12B-class layer (q 4096x3840, k/v 2048x3840, o 3840x4096, gate/up 15360x3840, down 3840x15360), N(0,0.02) BF16 with 0.1% x64 outliers, x ~ N(0,1)"
 METRIC, UNIT = "r4_matvec_hbm_gbs", "GB/s"
 NOMINAL_HBM_GBS = 8000.0
+OUTLIERS = 1e-3  # fraction of weights scaled x64 (the benchmark's distribution); --outliers changes it for experiments
 
 
 def synthetic_weight(name: str, n: int, k: int, seed_base: int = 0) -> np.ndarray:
@@ -42,7 +43,7 @@ def synthetic_weight(name: str, n: int, k: int, seed_base: int = 0) -> np.ndarra
     seed = seed_base * 1000 + sum(ord(c) for c in name) + n + k
     g = torch.Generator().manual_seed(seed)
     w = torch.randn((n, k), generator=g) * 0.02
-    w = torch.where(torch.rand((n, k), generator=g) < 1e-3, w * 64, w)
+    w = torch.where(torch.rand((n, k), generator=g) < OUTLIERS, w * 64, w)
     return w.to(torch.bfloat16).view(torch.int16).numpy().view(np.uint16)
 
 
@@ -396,9 +397,11 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--shapes", default="", help="comma list of matrices to keep (default: all seven); for small profiling runs")
     ap.add_argument("--quick", action="store_true", help="timed region only: skip the per-shape, end-to-end and CPU legs")
+    ap.add_argument("--outliers", type=float, default=OUTLIERS, help="fraction of weights scaled x64 (default: the benchmark's 0.1 %%)")
     ap.add_argument("--no-parity", action="store_true", help="skip the oracle check (only for kernel experiments whose output is wrong on purpose)")
     ap.add_argument("--traffic", type=float, default=None, help="DRAM bytes per launch from an ncu capture, if known")
     args = ap.parse_args()
+    globals()["OUTLIERS"] = args.outliers
     if args.shapes:
         keep = set(args.shapes.split(","))
         SHAPES[:] = [sh for sh in SHAPES if sh[0] in keep]

@@ -5,19 +5,23 @@
 //
 //   stage   RW rows x KC tiles: raw [RW][KC*128] bytes, codes [RW][KC*64] bytes
 //   lane l  owns weights 128t + 4l + j of every tile (the documented summation order)
-//   x       whole vector as fp32 in shared memory; pair table (see r4_kernels.cu) per lane
+//   x       whole vector as BF16 in shared memory, multiplied with the mixed-precision
+//           fma.rn.f32.bf16 (exact widening of both factors, one rounding of the sum)
+//   table   pair table of r4_kernels.cu, entry i of lane l at i*256 + l*4, placed on a 64 KB
+//           boundary of the shared window so that a lookup address is one byte permute of the
+//           code word into a per-lane base
 //
 // Requires K % 16 == 0 (bulk copies need 16-byte aligned row segments) and an x vector that fits
-// shared memory beside the table and the rings; other shapes take the plain-load kernel.
+// shared memory; other shapes take the plain-load kernel.
 #include <stdlib.h>
 
 #include "common.cuh"
 
 namespace bn {
 
-constexpr int ST_KC = 8;             // tiles per stage
-constexpr int ST_LUT_BYTES = 256 * 256;  // entry i of lane l at i * 256 + l * 4
+constexpr uint32_t ST_LUT_BYTES = 256 * 256;
 constexpr uint32_t ST_SPIN_LIMIT = 1u << 24;
+constexpr uint32_t ST_BASE_MAX = 2048;  // the dynamic shared window starts below this address
 
 __device__ int g_stream_error;  // set when a bounded wait gives up; read by bn_device_status()
 
@@ -27,7 +31,7 @@ __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
 __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+__device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
@@ -36,25 +40,66 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
       : "=r"(ok)
       : "r"(bar), "r"(parity)
       : "memory");
-  return ok != 0;
+  return ok;
 }
-// Bounded wait: gives up after ST_SPIN_LIMIT polls and reports through g_stream_error.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+// Bounded wait: gives up after ST_SPIN_LIMIT polls and reports through g_stream_error. `token`
+// receives a value the compiler cannot see through; reads of the stage take it as an input.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, uint32_t &token) {
   for (uint32_t i = 0; i < ST_SPIN_LIMIT; i++)
-    if (mbar_try_wait(bar, parity)) return true;
+    if ((token = mbar_try_wait(bar, parity)) != 0) return true;
   atomicExch(&g_stream_error, 1);
   return false;
 }
 __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
 }
+// Shared-memory reads by 32-bit shared address (no generic-to-shared conversion per load).
+// The table and x never change once the block has staged them, so these two may be scheduled
+// freely; their addresses depend on values read after the stage's barrier wait.
+__device__ __forceinline__ uint32_t lut_read(uint32_t addr) {
+  uint32_t v;
+  asm("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ uint2 x_read(uint32_t addr) {
+  uint2 v;
+  asm("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr));
+  return v;
+}
+// Ring reads carry `token`, a value produced by the stage's barrier wait: the compiler can then
+// neither merge reads of two different stages nor move a read above its wait.
+template <int OFF>
+__device__ __forceinline__ uint32_t ring_u32(uint32_t addr, uint32_t token) {
+  uint32_t v;
+  asm("ld.shared.u32 %0, [%1+%2];" : "=r"(v) : "r"(addr), "n"(OFF), "r"(token));
+  return v;
+}
+template <int OFF>
+__device__ __forceinline__ uint32_t ring_u16(uint32_t addr, uint32_t token) {
+  uint16_t v;
+  asm("ld.shared.u16 %0, [%1+%2];" : "=h"(v) : "r"(addr), "n"(OFF), "r"(token));
+  return v;
+}
+// acc += w.lo * x.lo; acc += w.hi * x.hi with BF16 factors widened exactly (two fused ops).
+__device__ __forceinline__ float fma2_bf16(uint32_t w, uint32_t x, float acc) {
+  asm("{\n\t.reg .b16 wl, wh, xl, xh;\n\t"
+      "mov.b32 {wl, wh}, %1;\n\t"
+      "mov.b32 {xl, xh}, %2;\n\t"
+      "fma.rn.f32.bf16 %0, wl, xl, %0;\n\t"
+      "fma.rn.f32.bf16 %0, wh, xh, %0;\n\t}"
+      : "+f"(acc)
+      : "r"(w), "r"(x));
+  return acc;
+}
+
 struct StreamArgs {
   bn_r4 w;
   const uint16_t *x;
   uint16_t *y;
   int64_t N, K;
   int T;
-  int stages;  // ring depth per warp
+  int stages;     // ring depth per warp
+  uint32_t smem;  // dynamic shared memory of the launch, bytes
 };
 
 // Escapes of one flagged lane word, in weight order across the warp: OR-masks for the two
@@ -82,133 +127,172 @@ __device__ __noinline__ uint3 escape_patch(uint32_t c, const uint8_t *__restrict
   return make_uint3(o01, o23, tot);
 }
 
-// One stage (nt <= ST_KC tiles) of RWG rows: decode and accumulate. `stage` points at this
-// lane's raw bytes of row 0 (rows ST_KC*128 apart), `codes` at its code word of row 0 (rows
-// ST_KC*64 apart); xs is this lane's slice of x for the stage's first tile; lut is this lane's
-// column of the pair table. The tile loop is unrolled by two only: the whole hot loop must fit
-// the instruction cache.
-template <int RWG>
-__device__ __forceinline__ void consume_stage(const uint8_t *stage, const uint8_t *codes, const float *xs, const uint8_t *lut, int nt, int klim, const uint32_t (&fbits)[RWG], uint32_t fany, const uint8_t *__restrict__ esc, uint32_t (&epos)[RWG], float (&acc)[RWG]) {
-  constexpr uint32_t RAW_ROW = ST_KC * 128, CODE_ROW = ST_KC * 64;
-#pragma unroll 2
-  for (int u = 0; u < nt; u++) {
-    const float4 xv = *reinterpret_cast<const float4 *>(xs + u * BN_TILE);
-    uint32_t w01[RWG], w23[RWG], c4[RWG];
-#pragma unroll
-    for (int i = 0; i < RWG; i++) {
-      const uint32_t r4 = *reinterpret_cast<const uint32_t *>(stage + i * RAW_ROW + u * 128);
-      c4[i] = *reinterpret_cast<const uint16_t *>(codes + i * CODE_ROW + u * 64);
-      const uint32_t e01 = *reinterpret_cast<const uint32_t *>(lut + (c4[i] & 0xFFu) * 256u);
-      const uint32_t e23 = *reinterpret_cast<const uint32_t *>(lut + (c4[i] & 0xFF00u));
-      w01[i] = (__byte_perm(r4, 0u, 0x1100) & 0x807F807Fu) | e01;
-      w23[i] = (__byte_perm(r4, 0u, 0x3322) & 0x807F807Fu) | e23;
-    }
-    if ((fany >> u) & 1u) {
-#pragma unroll
-      for (int i = 0; i < RWG; i++)
-        if ((fbits[i] >> u) & 1u) {
-          const uint3 p = escape_patch(c4[i], esc, epos[i]);
-          w01[i] |= p.x, w23[i] |= p.y, epos[i] += p.z;
-        }
-    }
-    if (u * BN_TILE < klim) {
-#pragma unroll
-      for (int i = 0; i < RWG; i++) {
-        float s = acc[i];
-        s = __fmaf_rn(__uint_as_float(w01[i] << 16), xv.x, s);
-        s = __fmaf_rn(__uint_as_float(w01[i] & 0xFFFF0000u), xv.y, s);
-        s = __fmaf_rn(__uint_as_float(w23[i] << 16), xv.z, s);
-        s = __fmaf_rn(__uint_as_float(w23[i] & 0xFFFF0000u), xv.w, s);
-        acc[i] = s;
-      }
-    }
+// Four weights of row I of a stage as two BF16x2 words (escapes not yet applied).
+template <int I, uint32_t RAW_ROW, uint32_t CODE_ROW>
+__device__ __forceinline__ void load_word(uint32_t raw, uint32_t codes, uint32_t lut, uint32_t token, uint32_t &c4, uint32_t &w01, uint32_t &w23) {
+  const uint32_t r4 = ring_u32<I * RAW_ROW>(raw, token);
+  c4 = ring_u16<I * CODE_ROW>(codes, token);
+  const uint32_t e01 = lut_read(__byte_perm(c4, lut, 0x7604));  // lut + code byte 0 * 256
+  const uint32_t e23 = lut_read(__byte_perm(c4, lut, 0x7614));  // lut + code byte 1 * 256
+  w01 = (__byte_perm(r4, 0u, 0x1100) & 0x807F807Fu) | e01;
+  w23 = (__byte_perm(r4, 0u, 0x3322) & 0x807F807Fu) | e23;
+}
+
+template <int RWG, uint32_t RAW_ROW, uint32_t CODE_ROW, int I = 0>
+__device__ __forceinline__ void clean_tile(uint32_t raw, uint32_t codes, uint32_t lut, uint32_t token, uint2 xv, float (&acc)[RWG]) {
+  if constexpr (I < RWG) {
+    uint32_t c4, w01, w23;
+    load_word<I, RAW_ROW, CODE_ROW>(raw, codes, lut, token, c4, w01, w23);
+    acc[I] = fma2_bf16(w23, xv.y, fma2_bf16(w01, xv.x, acc[I]));
+    clean_tile<RWG, RAW_ROW, CODE_ROW, I + 1>(raw, codes, lut, token, xv, acc);
   }
 }
 
-// WARPS: streaming warps per block; RW: rows walked together (a warp's last rows % RW rows are
-// walked one at a time)
-template <int WARPS, int RW>
+// A tile that needs care: some row holds escapes (bit u of fbits[i]), or the tile is the row's
+// partial last tile and this lane's columns may not exist (`in`).
+template <int RWG, uint32_t RAW_ROW, uint32_t CODE_ROW, int I = 0>
+__device__ __forceinline__ void careful_tile(uint32_t raw, uint32_t codes, uint32_t lut, uint32_t token, uint2 xv, int u, bool in, const uint32_t (&fbits)[RWG], const uint8_t *__restrict__ esc, uint32_t (&epos)[RWG], float (&acc)[RWG]) {
+  if constexpr (I < RWG) {
+    uint32_t c4, w01, w23;
+    load_word<I, RAW_ROW, CODE_ROW>(raw, codes, lut, token, c4, w01, w23);
+    if ((fbits[I] >> u) & 1u) {
+      const uint3 p = escape_patch(c4, esc, epos[I]);
+      w01 |= p.x, w23 |= p.y, epos[I] += p.z;
+    }
+    const float s = fma2_bf16(w23, xv.y, fma2_bf16(w01, xv.x, acc[I]));
+    acc[I] = in ? s : acc[I];
+    careful_tile<RWG, RAW_ROW, CODE_ROW, I + 1>(raw, codes, lut, token, xv, u, in, fbits, esc, epos, acc);
+  }
+}
+
+// One stage (nt tiles) of RWG rows: decode and accumulate.
+//   raw    shared address of this lane's raw bytes of row 0, tile 0 (rows RAW_ROW, tiles 128 apart)
+//   codes  shared address of this lane's code word of row 0, tile 0 (rows CODE_ROW, tiles 64 apart)
+//   xs     shared address of this lane's four BF16 inputs of the first tile (tiles 256 apart)
+//   lut    shared address of this lane's column of the pair table (bits 8..15 clear)
+//   care   bit u set: tile u needs the careful path (an escape in some row, or a partial tile)
+//   partial  bit u set: tile u is the row's partial last tile; lane_in_partial: this lane's
+//          columns exist in it
+// Runs of clean tiles go through a loop without any per-tile test, unrolled by two only: the hot
+// loop must stay within the instruction cache.
+template <int RWG, uint32_t RAW_ROW, uint32_t CODE_ROW>
+__device__ __forceinline__ void consume_stage(uint32_t raw, uint32_t codes, uint32_t xs, uint32_t lut, uint32_t token, int nt, uint32_t partial, bool lane_in_partial, const uint32_t (&fbits)[RWG], uint32_t care, const uint8_t *__restrict__ esc, uint32_t (&epos)[RWG], float (&acc)[RWG]) {
+  const uint32_t stops = care | (1u << nt);  // sentinel after the last tile
+  int u = 0;
+  while (true) {
+    const int run = __ffs(stops >> u) - 1;
+#pragma unroll 2
+    for (int k = 0; k < run; k++) {
+      clean_tile<RWG, RAW_ROW, CODE_ROW>(raw, codes, lut, token, x_read(xs), acc);
+      raw += 128, codes += 64, xs += 256;
+    }
+    u += run;
+    if (u >= nt) break;
+    careful_tile<RWG, RAW_ROW, CODE_ROW>(raw, codes, lut, token, x_read(xs), u, lane_in_partial || !((partial >> u) & 1u), fbits, esc, epos, acc);
+    raw += 128, codes += 64, xs += 256;
+    u++;
+  }
+}
+
+// WARPS: streaming warps per block (one block per SM); RW: rows walked together (a warp's last
+// rows % RW rows are walked one at a time); KC: tiles per stage.
+//
+// Shared window, by absolute shared address (base = start of the dynamic allocation):
+//   [base, 64K)    x as BF16 [T*128] | mbarriers | rings of the first warps
+//   [64K, 128K)    pair table
+//   [128K, end)    rings of the remaining warps
+template <int WARPS, int RW, int KC>
 __global__ void __launch_bounds__(WARPS * 32, 1) r4_stream_kernel(StreamArgs a) {
   extern __shared__ __align__(128) uint8_t smem_raw[];
+  static_assert(32 % KC == 0, "a stage must not straddle a 32-tile flag word");
   constexpr int THREADS = WARPS * 32;
+  constexpr uint32_t RAW_ROW = KC * 128, CODE_ROW = KC * 64;
+  constexpr uint32_t RAW_STAGE = RW * RAW_ROW, STAGE = RAW_STAGE + RW * CODE_ROW;
+  constexpr uint32_t STAGE_MASK = (1u << KC) - 1u;
   const uint32_t lane = lane_id(), warp = threadIdx.x >> 5;
   const int64_t K = a.K;
   const int T = a.T, S = a.stages;
-  const int Tpad = T * BN_TILE;
-  // shared memory map: pair table | x fp32 [T*128] | per-warp rings | mbarriers
-  constexpr uint32_t RAW_ROW = ST_KC * 128, CODE_ROW = ST_KC * 64;
-  constexpr uint32_t RAW_STAGE = RW * RAW_ROW, STAGE = RAW_STAGE + RW * CODE_ROW;
-  uint8_t *const p_lut = smem_raw;
-  float *const p_x = reinterpret_cast<float *>(smem_raw + ST_LUT_BYTES);
-  uint8_t *const p_ring = smem_raw + ST_LUT_BYTES + (size_t)Tpad * 4 + (size_t)warp * S * STAGE;
-  const uint32_t s_ring = smem_addr(p_ring);
-  const uint32_t s_bar = smem_addr(smem_raw) + ST_LUT_BYTES + (uint32_t)Tpad * 4 + WARPS * (uint32_t)S * STAGE + warp * (uint32_t)S * 8;
+  const uint32_t base = smem_addr(smem_raw);
+  const uint32_t x_at = (base + 15u) & ~15u;
+  const uint32_t bar_at = x_at + (uint32_t)T * 256u;
+  const uint32_t pool_a = (bar_at + WARPS * (uint32_t)S * 8u + 127u) & ~127u;
+  const uint32_t ring_bytes = (uint32_t)S * STAGE;
+  const uint32_t in_a = pool_a < 65536u ? (65536u - pool_a) / ring_bytes : 0u;  // warps with rings below the table
+  const uint32_t s_ring = warp < in_a ? pool_a + warp * ring_bytes : 131072u + (warp - in_a) * ring_bytes;
+  const uint32_t need_end = in_a >= WARPS ? 131072u : 131072u + (WARPS - in_a) * ring_bytes;
+  if (base > ST_BASE_MAX || need_end > base + a.smem) {  // the host sized the window for another layout
+    if (threadIdx.x == 0) atomicExch(&g_stream_error, 2);
+    return;
+  }
+  const uint32_t s_bar = bar_at + warp * (uint32_t)S * 8u;
 
   // this warp's rows: nfull groups of RW rows, then the remaining rows one per group
   const int64_t workers = (int64_t)gridDim.x * WARPS, me = (int64_t)blockIdx.x * WARPS + warp;
   const int64_t r_begin = a.N * me / workers, r_end = a.N * (me + 1) / workers;
   const int nrows = (int)(r_end - r_begin);
   const int nfull = nrows / RW, ngroups = nfull + (nrows - nfull * RW);
-  const int nchunks = (T + ST_KC - 1) / ST_KC;
+  const int nchunks = (T + KC - 1) / KC, last_chunk = nchunks - 1;
+  const int nt_last = T - last_chunk * KC;  // tiles of a row's last stage
+  auto group_row = [&](int g) { return g < nfull ? g * RW : nfull * RW + (g - nfull); };
 
   if (lane == 0)
     for (int s = 0; s < S; s++) mbar_init(s_bar + s * 8, 1);
   asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   __syncwarp();
 
-  // producer side: next (group, chunk) to fetch and the ring slot it goes to
+  // Producer side. Lanes 0..RW-1 copy the raw bytes of rows 0..RW-1 of a group, lanes 16..16+RW-1
+  // their code words. A lane's source pointer simply runs on through its row; at the end of a
+  // group of RW rows it skips the rows its neighbours copied.
+  const bool raw_lane = lane < 16;
+  const uint32_t my_row = lane & 15u;
+  const uint32_t my_step = raw_lane ? RAW_ROW : CODE_ROW;
+  const uint32_t my_last = raw_lane ? (uint32_t)(K - (int64_t)last_chunk * KC * BN_TILE) : (uint32_t)nt_last * 64u;
+  const uint32_t my_off = raw_lane ? my_row * RAW_ROW : RAW_STAGE + my_row * CODE_ROW;
+  const uint32_t row_bytes = raw_lane ? (uint32_t)K : (uint32_t)T * 64u;
+  const uint32_t tx_full = RAW_ROW + CODE_ROW;
+  const uint32_t tx_last = (uint32_t)(K - (int64_t)last_chunk * KC * BN_TILE) + (uint32_t)nt_last * 64u;
   int pg = 0, pc = 0, ps = 0;
+  const uint8_t *src = (raw_lane ? a.w.raw : reinterpret_cast<const uint8_t *>(a.w.codes)) + (r_begin + (int64_t)min(my_row, (uint32_t)max(nrows - 1, 0))) * row_bytes;
   auto issue = [&]() {
     if (pg >= ngroups) return;
-    const int r0 = pg < nfull ? pg * RW : nfull * RW + (pg - nfull);
-    const int nlive = pg < nfull ? RW : 1;
-    const int t0 = pc * ST_KC, nt = min(ST_KC, T - t0);
-    const uint32_t raw_bytes = (uint32_t)min((int64_t)nt * BN_TILE, K - (int64_t)t0 * BN_TILE), code_bytes = (uint32_t)nt * 64u;
-    const uint32_t slot = s_ring + (uint32_t)ps * STAGE, bar = s_bar + (uint32_t)ps * 8;
-    if (lane == 0) mbar_expect_tx(bar, (uint32_t)nlive * (raw_bytes + code_bytes));
-    __syncwarp();
-    const int64_t row = r_begin + r0;
-    if ((int)lane < nlive) {
-      bulk_g2s(slot + lane * RAW_ROW, a.w.raw + (row + lane) * K + (int64_t)t0 * BN_TILE, raw_bytes, bar);
-    } else if ((int)lane >= 16 && (int)lane < 16 + nlive) {
-      const uint32_t i = lane - 16;
-      bulk_g2s(slot + RAW_STAGE + i * CODE_ROW, a.w.codes + ((row + i) * T + t0) * 32, code_bytes, bar);
+    const bool last = pc == last_chunk, wide_g = pg < nfull;
+    const uint32_t bytes = last ? my_last : my_step;
+    const uint32_t bar = s_bar + (uint32_t)ps * 8u;
+    if (lane == 0) mbar_expect_tx(bar, (last ? tx_last : tx_full) * (wide_g ? RW : 1));
+    if (my_row < (wide_g ? (uint32_t)RW : 1u)) bulk_g2s(s_ring + (uint32_t)ps * STAGE + my_off, src, bytes, bar);
+    src += bytes;
+    if (last) {
+      pc = 0, pg++;
+      if (wide_g) src += (size_t)(RW - 1) * row_bytes;
+    } else {
+      pc++;
     }
-    if (++pc == nchunks) pc = 0, pg++;
-    if (++ps == S) ps = 0;
+    ps = ps + 1 == S ? 0 : ps + 1;
   };
   for (int s = 0; s < S; s++) issue();
 
-  // while the first stages fly: pair table and x into shared memory (whole block)
+  // while the first stages fly: x and the pair table into shared memory (whole block)
   {
-    __shared__ uint32_t t16[16];
-    if (threadIdx.x < 16) t16[threadIdx.x] = threadIdx.x == 15 ? 0u : (uint32_t)a.w.table[threadIdx.x];
-    // x: 8 BF16 values (16 bytes) per load, every load of the block in flight at once
     const uint4 *x8 = reinterpret_cast<const uint4 *>(a.x);
-    for (int i = threadIdx.x; i < Tpad / 8; i += THREADS) {
-      uint4 v = make_uint4(0, 0, 0, 0);
-      if ((int64_t)i * 8 < K) v = __ldg(x8 + i);  // K % 16 == 0: a group of 8 is all in or all out
-      float4 lo, hi;
-      lo.x = __uint_as_float(v.x << 16), lo.y = __uint_as_float(v.x & 0xFFFF0000u), lo.z = __uint_as_float(v.y << 16), lo.w = __uint_as_float(v.y & 0xFFFF0000u);
-      hi.x = __uint_as_float(v.z << 16), hi.y = __uint_as_float(v.z & 0xFFFF0000u), hi.z = __uint_as_float(v.w << 16), hi.w = __uint_as_float(v.w & 0xFFFF0000u);
-      reinterpret_cast<float4 *>(p_x)[2 * i] = lo;
-      reinterpret_cast<float4 *>(p_x)[2 * i + 1] = hi;
-    }
-    __syncthreads();
-    uint32_t *lut = reinterpret_cast<uint32_t *>(p_lut);
+    uint4 *dst = reinterpret_cast<uint4 *>(smem_raw + (x_at - base));
+    for (int i = threadIdx.x; i < T * 16; i += THREADS) dst[i] = (int64_t)i * 8 < K ? __ldg(x8 + i) : make_uint4(0, 0, 0, 0);  // K % 16 == 0
+    uint32_t *lut = reinterpret_cast<uint32_t *>(smem_raw + (65536u - base));
     for (uint32_t i = threadIdx.x; i < 256 * 32; i += THREADS) {
-      const uint32_t code = i >> 5, l = i & 31;
-      lut[code * 64 + l] = (t16[code & 15] << 7) | (t16[code >> 4] << 23);
+      const uint32_t code = i >> 5, l = i & 31, c0 = code & 15, c1 = code >> 4;
+      const uint32_t e0 = c0 == 15 ? 0u : __ldg(a.w.table + c0), e1 = c1 == 15 ? 0u : __ldg(a.w.table + c1);
+      lut[code * 64 + l] = (e0 << 7) | (e1 << 23);
     }
     __syncthreads();
   }
 
-  const uint8_t *lut_lane = p_lut + lane * 4;
+  const uint32_t lut_lane = 65536u + lane * 4;
+  // in a row's partial last tile (K % 128 != 0) only the lanes below K % 128 hold weights
+  const uint32_t partial_bit = (K & 127) ? 1u << (nt_last - 1) : 0u;
+  const bool lane_in_partial = (int64_t)lane * 4 < (K & 127);
   int cs = 0;           // consumer slot
   uint32_t phases = 0;  // bit s: parity to wait for on slot s
   // flag bytes (one 32-tile group per row at a time) and escape cursors are fetched one step
   // ahead of their use, so their global-memory latency hides behind the previous tiles
-  auto group_row = [&](int g) { return g < nfull ? g * RW : nfull * RW + (g - nfull); };
   uint32_t pf_flag[RW], pf_epos[RW];
   auto prefetch_flags = [&](int g, int f) {
     const int r0 = group_row(g), live = g < nfull ? RW : 1;
@@ -233,8 +317,9 @@ __global__ void __launch_bounds__(WARPS * 32, 1) r4_stream_kernel(StreamArgs a) 
 #pragma unroll
     for (int i = 0; i < RW; i++) acc[i] = 0.0f, epos[i] = pf_epos[i], fmask[i] = 0u;
     if (g + 1 < ngroups) prefetch_epos(g + 1);
+    uint32_t xs = x_at + lane * 8;
     for (int c = 0; c < nchunks; c++) {
-      const int t0 = c * ST_KC, nt = min(ST_KC, T - t0);
+      const int t0 = c * KC;
       if ((t0 & 31) == 0) {
         const int f = t0 >> 5;
 #pragma unroll
@@ -245,29 +330,35 @@ __global__ void __launch_bounds__(WARPS * 32, 1) r4_stream_kernel(StreamArgs a) 
         if (f + 1 < fgroups) prefetch_flags(g, f + 1);
         else if (g + 1 < ngroups) prefetch_flags(g + 1, 0);
       }
-      if (!mbar_wait(s_bar + (uint32_t)cs * 8, (phases >> cs) & 1u)) return;  // gave up: status flag is set
+      uint32_t token;
+      if (!mbar_wait(s_bar + (uint32_t)cs * 8, (phases >> cs) & 1u, token)) return;  // gave up: status flag is set
       phases ^= 1u << cs;
-      const uint8_t *stage = p_ring + (size_t)cs * STAGE + lane * 4;
-      const uint8_t *codes = p_ring + (size_t)cs * STAGE + RAW_STAGE + lane * 2;
-      const float *xs = p_x + (size_t)t0 * BN_TILE + lane * 4;
-      const int klim = (int)min((int64_t)ST_KC * BN_TILE, K - (int64_t)t0 * BN_TILE) - (int)lane * 4;  // columns left for this lane
+      const uint32_t raw = s_ring + (uint32_t)cs * STAGE + lane * 4;
+      const uint32_t codes = s_ring + (uint32_t)cs * STAGE + RAW_STAGE + lane * 2;
+      const bool last = c == last_chunk;
+      const int nt = last ? nt_last : KC;
+      const uint32_t partial = last ? partial_bit : 0u;
       if (wide) {
-        uint32_t fbits[RW], fany = 0;
+        uint32_t fbits[RW], care = partial;
 #pragma unroll
         for (int i = 0; i < RW; i++) {
-          fbits[i] = (fmask[i] >> (t0 & 31)) & ((1u << ST_KC) - 1u);
-          fany |= fbits[i];
+          fbits[i] = (fmask[i] >> (t0 & 31)) & STAGE_MASK;
+          care |= fbits[i];
         }
-        consume_stage<RW>(stage, codes, xs, lut_lane, nt, klim, fbits, fany, a.w.esc, epos, acc);
+        consume_stage<RW, RAW_ROW, CODE_ROW>(raw, codes, xs, lut_lane, token, nt, partial, lane_in_partial, fbits, care, a.w.esc, epos, acc);
       } else {
-        uint32_t fb1[1] = {(fmask[0] >> (t0 & 31)) & ((1u << ST_KC) - 1u)}, ep1[1] = {epos[0]};
+        uint32_t fb1[1] = {(fmask[0] >> (t0 & 31)) & STAGE_MASK}, ep1[1] = {epos[0]};
         float ac1[1] = {acc[0]};
-        consume_stage<1>(stage, codes, xs, lut_lane, nt, klim, fb1, fb1[0], a.w.esc, ep1, ac1);
+        consume_stage<1, RAW_ROW, CODE_ROW>(raw, codes, xs, lut_lane, token, nt, partial, lane_in_partial, fb1, fb1[0] | partial, a.w.esc, ep1, ac1);
         epos[0] = ep1[0], acc[0] = ac1[0];
       }
+      xs += KC * 256;
+      // every read of the slot feeds an accumulator: pin them before the slot is refilled
+#pragma unroll
+      for (int i = 0; i < RW; i++) asm volatile("" ::"f"(acc[i]) : "memory");
       __syncwarp();
       issue();  // refill the slot just drained
-      if (++cs == S) cs = 0;
+      cs = cs + 1 == S ? 0 : cs + 1;
     }
     float mine = 0.0f;
 #pragma unroll
@@ -292,31 +383,45 @@ static int stream_sms() {
   return n;
 }
 
-template <int WARPS, int RW>
+constexpr uint32_t ST_SMEM_MAX = 227 * 1024;  // dynamic shared memory one block may ask for
+
+// Ring depth that fits the shared window when the dynamic allocation starts at `base` (mirrors
+// the kernel's layout arithmetic); 0 if not even two stages per warp fit.
+static int stream_stages(int warps, uint32_t stage, int T, uint32_t base) {
+  for (int S = 6; S >= 2; S--) {
+    const uint32_t x_at = (base + 15u) & ~15u, bar_at = x_at + (uint32_t)T * 256u;
+    const uint32_t pool_a = (bar_at + (uint32_t)warps * S * 8u + 127u) & ~127u, ring = S * stage;
+    if (pool_a > 65536u) return 0;
+    const uint32_t in_a = (65536u - pool_a) / ring;
+    const uint32_t end = in_a >= (uint32_t)warps ? 131072u : 131072u + ((uint32_t)warps - in_a) * ring;
+    if (end <= ST_SMEM_MAX) return S;  // the window ends at base + ST_SMEM_MAX >= ST_SMEM_MAX
+  }
+  return 0;
+}
+
+template <int WARPS, int RW, int KC>
 static int launch_stream(StreamArgs a, cudaStream_t s) {
-  const size_t fixed = ST_LUT_BYTES + (size_t)a.T * BN_TILE * 4 + 64;
-  const size_t stage = (size_t)RW * ST_KC * 192;
-  const size_t limit = 227 * 1024;
-  if (fixed + WARPS * 2 * (stage + 8) > limit) return -1;  // does not fit: caller falls back
-  int stages = (int)((limit - fixed) / (WARPS * (stage + 8)));
-  if (stages > 6) stages = 6;
+  // worst case of the two extremes of the window's start; the kernel re-derives the layout
+  // from the real start and refuses to run if it does not fit
+  const int stages = min(stream_stages(WARPS, RW * KC * 192, a.T, 0), stream_stages(WARPS, RW * KC * 192, a.T, ST_BASE_MAX));
+  if (stages < 2) return -1;  // does not fit: caller falls back
   a.stages = stages;
-  const size_t smem = fixed + (size_t)WARPS * stages * (stage + 8);
-  auto kern = r4_stream_kernel<WARPS, RW>;
-  BN_CUDA(allow_smem(kern, smem));
+  a.smem = ST_SMEM_MAX;
+  auto kern = r4_stream_kernel<WARPS, RW, KC>;
+  BN_CUDA(allow_smem(kern, a.smem));
   int64_t blocks = stream_sms();
   const int64_t need = (a.N + WARPS - 1) / WARPS;
   if (blocks > need) blocks = need;
-  kern<<<(unsigned)blocks, WARPS * 32, smem, s>>>(a);
+  kern<<<(unsigned)blocks, WARPS * 32, a.smem, s>>>(a);
   return launched("r4_stream_kernel");
 }
 
-// Streaming warps per block: 8, or 12 with BINADE_B200_STREAM_WARPS=12 (an experiment knob).
-static int stream_warps() {
-  static int n = 0;
-  if (!n) {
-    const char *e = getenv("BINADE_B200_STREAM_WARPS");
-    n = (e && atoi(e) == 12) ? 12 : 8;
+// Kernel shape: 0 (default) or an experiment selected with BINADE_B200_STREAM_SHAPE.
+static int stream_shape() {
+  static int n = -1;
+  if (n < 0) {
+    const char *e = getenv("BINADE_B200_STREAM_SHAPE");
+    n = e ? atoi(e) : 0;
   }
   return n;
 }
@@ -324,16 +429,19 @@ static int stream_warps() {
 // Returns -1 when the shape is outside what the streaming kernel covers.
 int stream_matvec(const bn_r4 *w, const uint16_t *x, int64_t N, int64_t K, uint16_t *y, cudaStream_t s) {
   const int64_t T = tiles(K);
-  if (K % 16 || N < 1) return -1;
+  if (K % 16 || N < 1 || T > 200) return -1;
   StreamArgs a{};
   a.w = *w, a.x = x, a.y = y, a.N = N, a.K = K, a.T = (int)T;
-  const bool wide = N / ((int64_t)stream_sms() * 8) >= 8;  // enough rows per warp to walk 4 at a time
-  if (!wide) return launch_stream<8, 2>(a, s);
-  if (stream_warps() == 12) {
-    const int e = launch_stream<12, 4>(a, s);
-    if (e >= 0) return e;
+  int e = -1;
+  switch (stream_shape()) {
+    case 1: e = launch_stream<8, 4, 8>(a, s); break;
+    case 2: e = launch_stream<12, 4, 8>(a, s); break;
+    case 3: e = launch_stream<16, 2, 8>(a, s); break;
+    case 4: e = launch_stream<16, 4, 4>(a, s); break;
+    default: e = launch_stream<16, 2, 8>(a, s); break;
   }
-  return launch_stream<8, 4>(a, s);
+  if (e == -1) e = launch_stream<8, 4, 4>(a, s);
+  return e;
 }
 
 }  // namespace bn
@@ -343,4 +451,3 @@ extern "C" int bn_device_status(int *status) {
   BN_CUDA(cudaMemcpyFromSymbol(status, bn::g_stream_error, sizeof(int)));
   return BN_OK;
 }
-
