@@ -96,7 +96,7 @@ def rice_to_r4(meta, bits, roff, table, R: int, K: int, esc_cap: int | None = No
     nwords = bits.numel()
     if nwords == 0:
         bits = torch.zeros(1, dtype=torch.int32, device=dev)
-    cap = esc_cap if esc_cap is not None else max(4096, R * K // 8)
+    cap = esc_cap if esc_cap is not None else 4096 + R * K // 4  # rows claim an upper bound, about 1/7 of the weights on real data
     while True:
         cap = min(cap, (1 << 32) - 1)
         esc_tmp = torch.empty(cap, dtype=torch.uint8, device=dev)
