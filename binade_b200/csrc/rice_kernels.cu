@@ -310,3 +310,90 @@ extern "C" int bn_r4_finish(const uint32_t *row_cnt, const uint8_t *esc_tmp, con
   compact_esc_kernel<<<(unsigned)blocks, 256, 0, s>>>(row_esc, esc_tmp, tmp_off, R, esc, esc_bytes);
   return launched("compact_esc_kernel");
 }
+
+
+namespace bn {
+
+// ---------------------------------------------------------------------------------------------
+// Expander that allocates nothing: bn_rice_to_r4_static.
+//
+// Some hosts of this library cannot call cudaMalloc where they load weights: a plugin running
+// inside a framework whose allocator owns the whole device (a second allocator would fragment or
+// exhaust it), code that loads layers on a stream while another stream is being captured into a
+// CUDA graph (an allocation there is an error), or a service with a fixed memory budget audited at
+// start-up. For them the scratch of the two-step expander lives in this fixed device array, which
+// every GPU that loads the library holds until the process exits.
+// ---------------------------------------------------------------------------------------------
+constexpr int64_t STATIC_MAX_ROWS = 65536;              // rows per call
+constexpr int64_t STATIC_MAX_WEIGHTS = 16ll << 20;      // R * K per call: escape scratch for the worst case
+constexpr size_t STATIC_COUNTERS_AT = 0;                // 8 x uint32, padded to 256 bytes
+constexpr size_t STATIC_TMP_OFF_AT = 256;               // uint32 [STATIC_MAX_ROWS]
+constexpr size_t STATIC_ESC_AT = STATIC_TMP_OFF_AT + (size_t)STATIC_MAX_ROWS * 4;
+constexpr size_t STATIC_BYTES = STATIC_ESC_AT + (size_t)STATIC_MAX_WEIGHTS;  // 16.25 MiB + 256 B
+
+static __device__ __align__(256) unsigned char g_static_scratch[STATIC_BYTES];
+
+// Escape runs -> row order, sizes read on the device: n_esc = counters[2]; at most esc_cap - 1
+// escape bytes are written, then the closing 0. info = {n_esc, R - first bad row (0: none),
+// 1 if esc_cap was too small (esc is then cut short), 0}.
+__global__ void __launch_bounds__(256) compact_esc_static_kernel(const uint32_t *__restrict__ row_esc, const uint8_t *__restrict__ esc_tmp, const uint32_t *__restrict__ tmp_off, const uint32_t *__restrict__ counters, int64_t R, uint8_t *__restrict__ esc, uint64_t esc_cap, uint32_t *__restrict__ info) {
+  const uint64_t n_esc = counters[2], room = esc_cap - 1;
+  const uint32_t lane = lane_id();
+  for (int64_t row = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5); row < R; row += (int64_t)gridDim.x * 8) {
+    const uint64_t b = row_esc[row], e = row + 1 < R ? (uint64_t)row_esc[row + 1] : n_esc;
+    const uint8_t *src = esc_tmp + tmp_off[row];
+    for (uint64_t i = lane; b + i < e && b + i < room; i += 32) esc[b + i] = src[i];
+  }
+  if (blockIdx.x == 0 && threadIdx.x == 0) {
+    esc[n_esc < room ? n_esc : room] = 0;
+    info[0] = (uint32_t)n_esc, info[1] = counters[1], info[2] = n_esc > room ? 1u : 0u, info[3] = 0u;
+  }
+}
+
+// The scratch array's device address on the current device, looked up once per device.
+static int static_scratch(unsigned char **out) {
+  static unsigned char *ptr[64] = {nullptr};
+  int dev = 0;
+  BN_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return fail(BN_ERR_ARG, "bn_rice_to_r4_static: device index out of range");
+  if (!ptr[dev]) {
+    // g_static_scratch names the array on the host side only; kernels need its device address
+    void *p = nullptr;
+    BN_CUDA(cudaGetSymbolAddress(&p, g_static_scratch));
+    ptr[dev] = static_cast<unsigned char *>(p);
+  }
+  *out = ptr[dev];
+  return BN_OK;
+}
+
+}  // namespace bn
+
+extern "C" int bn_rice_to_r4_static(const uint8_t *meta, const uint32_t *bits, uint64_t nwords, const uint32_t *roff, const uint8_t *table, int64_t R, int64_t K, uint16_t *codes, uint8_t *flags, uint32_t *row_esc, uint8_t *esc, uint64_t esc_cap, uint32_t *info, void *stream) {
+  using namespace bn;
+  if (int e = check_stream(meta, bits, roff, R, K)) return e;
+  if (!table || !codes || !flags || !row_esc || !esc || !info || esc_cap < 1) return fail(BN_ERR_ARG, "bn_rice_to_r4_static: null pointer or empty esc");
+  if (K % 4) return fail(BN_ERR_ARG, "R4 needs K % 4 == 0");
+  if (R > STATIC_MAX_ROWS || R * K > STATIC_MAX_WEIGHTS) return fail(BN_ERR_CAPACITY, "bn_rice_to_r4_static: at most 65536 rows and 16 Mi weights per call (expand larger tensors in row chunks, or use bn_rice_to_r4 with caller scratch)");
+  unsigned char *scratch = nullptr;
+  if (int e = static_scratch(&scratch)) return e;
+  cudaStream_t s = (cudaStream_t)stream;
+  uint32_t *counters = reinterpret_cast<uint32_t *>(scratch + STATIC_COUNTERS_AT);
+  uint32_t *tmp_off = reinterpret_cast<uint32_t *>(scratch + STATIC_TMP_OFF_AT);
+  uint8_t *esc_tmp = scratch + STATIC_ESC_AT;
+  // the array keeps the previous call's contents: the counters must start at zero
+  BN_CUDA(cudaMemsetAsync(counters, 0, 8 * sizeof(uint32_t), s));
+  if (R > 0) {
+    RiceArgs a{};
+    a.meta = meta, a.bits = bits, a.nwords = nwords, a.roff = roff, a.table = table, a.R = R, a.K = K, a.T = (int)tiles(K);
+    a.codes = codes, a.flags = flags, a.row_cnt = row_esc, a.esc_tmp = esc_tmp, a.esc_cap = (uint64_t)STATIC_MAX_WEIGHTS, a.tmp_off = tmp_off, a.counters = counters;
+    rice_kernel<RICE_R4><<<rice_grid(R), RICE_THREADS, 0, s>>>(a);
+    if (int e = launched("rice_kernel<r4>")) return e;
+    scan_rows_kernel<<<1, 1024, 0, s>>>(row_esc, R, row_esc);
+    if (int e = launched("scan_rows_kernel")) return e;
+  }
+  int64_t blocks = (R + 7) / 8;
+  if (blocks > 2048) blocks = 2048;
+  if (blocks < 1) blocks = 1;
+  compact_esc_static_kernel<<<(unsigned)blocks, 256, 0, s>>>(row_esc, esc_tmp, tmp_off, counters, R, esc, esc_cap, info);
+  return launched("compact_esc_static_kernel");
+}

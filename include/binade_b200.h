@@ -96,6 +96,26 @@ int bn_rice_to_r4(const uint8_t *meta, const uint32_t *bits, uint64_t nwords, co
 int bn_r4_finish(const uint32_t *row_cnt, const uint8_t *esc_tmp, const uint32_t *tmp_off, int64_t R,
                  uint32_t *row_esc, uint8_t *esc, uint64_t esc_bytes, void *stream);
 
+/* The whole expander (both steps above) for callers that must not allocate device memory while
+ * they load weights: a plugin inside a framework whose own allocator has taken the device, a
+ * loader running next to a stream capture (where cudaMalloc is an error), a service whose memory
+ * budget is fixed at start-up. This entry point has no counterpart in the reference. It calls no
+ * cudaMalloc/cudaFree and no allocating library routine: its scratch is a fixed 16.25 MiB device
+ * array inside the library, held by every GPU that loads the library until the process exits.
+ *   limits   R <= 65536 rows and R * K <= 16 Mi weights per call (BN_ERR_CAPACITY beyond: expand
+ *            a larger tensor in row chunks, or use bn_rice_to_r4 with scratch of your own)
+ *   outputs  codes [R*T*32], flags [R*T], row_esc [R], esc [esc_cap] (escape bytes + a closing
+ *            0), info: 4 x uint32 on the device = {number of escapes, R - first bad row (0 = every
+ *            row ends where it must), 1 if esc_cap < escapes + 1 (esc is then cut short), 0}
+ * The first call on a device looks up the array's device address (cudaGetSymbolAddress, with that
+ * device current); make that first call before any stream capture begins. All calls share the
+ * one array and it keeps the last call's contents (the call clears the counters it needs at
+ * zero): two calls whose kernels overlap on the GPU, on different streams or from different
+ * threads, race; run them one after the other. */
+int bn_rice_to_r4_static(const uint8_t *meta, const uint32_t *bits, uint64_t nwords, const uint32_t *roff,
+                         const uint8_t *table, int64_t R, int64_t K, uint16_t *codes, uint8_t *flags,
+                         uint32_t *row_esc, uint8_t *esc, uint64_t esc_cap, uint32_t *info, void *stream);
+
 /* R4 -> dense BF16 [N,K]; output row r is storage row (r / NB) * RS + R0 + r % NB.
  * Replaces r4_decode, binade/mlx/cuda_kernels.py:897-916. */
 int bn_r4_decode(const bn_r4 *w, int64_t N, int64_t K, int64_t NB, int64_t RS, int64_t R0,
