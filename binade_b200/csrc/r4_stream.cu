@@ -438,6 +438,9 @@ int stream_matvec(const bn_r4 *w, const uint16_t *x, int64_t N, int64_t K, uint1
     case 2: e = launch_stream<12, 4, 8>(a, s); break;
     case 3: e = launch_stream<16, 2, 8>(a, s); break;
     case 4: e = launch_stream<16, 4, 4>(a, s); break;
+    case 5: e = launch_stream<20, 2, 8>(a, s); break;
+    case 6: e = launch_stream<24, 2, 8>(a, s); break;
+    case 7: e = launch_stream<24, 2, 4>(a, s); break;
     default: e = launch_stream<16, 2, 8>(a, s); break;
   }
   if (e == -1) e = launch_stream<8, 4, 4>(a, s);
