@@ -13,8 +13,6 @@
 //
 // Requires K % 16 == 0 (bulk copies need 16-byte aligned row segments) and an x vector that fits
 // shared memory; other shapes take the plain-load kernel.
-#include <stdlib.h>
-
 #include "common.cuh"
 
 namespace bn {
@@ -54,20 +52,9 @@ __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void *src, uint32_t
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
 }
 // Shared-memory reads by 32-bit shared address (no generic-to-shared conversion per load).
-// The table and x never change once the block has staged them, so these two may be scheduled
-// freely; their addresses depend on values read after the stage's barrier wait.
-__device__ __forceinline__ uint32_t lut_read(uint32_t addr) {
-  uint32_t v;
-  asm("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
-  return v;
-}
-__device__ __forceinline__ uint2 x_read(uint32_t addr) {
-  uint2 v;
-  asm("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr));
-  return v;
-}
-// Ring reads carry `token`, a value produced by the stage's barrier wait: the compiler can then
-// neither merge reads of two different stages nor move a read above its wait.
+// Each takes `token`, a value the compiler cannot see through, produced by the stage's barrier
+// wait: reads of two different stages cannot be merged, and no read moves above the wait (nor,
+// for x and the table, above the block-wide barrier that publishes them, which precedes it).
 template <int OFF>
 __device__ __forceinline__ uint32_t ring_u32(uint32_t addr, uint32_t token) {
   uint32_t v;
@@ -78,6 +65,17 @@ template <int OFF>
 __device__ __forceinline__ uint32_t ring_u16(uint32_t addr, uint32_t token) {
   uint16_t v;
   asm("ld.shared.u16 %0, [%1+%2];" : "=h"(v) : "r"(addr), "n"(OFF), "r"(token));
+  return v;
+}
+__device__ __forceinline__ uint32_t lut_read(uint32_t addr, uint32_t token) {
+  uint32_t v;
+  asm("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr), "r"(token));
+  return v;
+}
+template <int OFF>
+__device__ __forceinline__ uint2 x_read(uint32_t addr, uint32_t token) {
+  uint2 v;
+  asm("ld.shared.v2.u32 {%0, %1}, [%2+%3];" : "=r"(v.x), "=r"(v.y) : "r"(addr), "n"(OFF), "r"(token));
   return v;
 }
 // acc += w.lo * x.lo; acc += w.hi * x.hi with BF16 factors widened exactly (two fused ops).
@@ -102,95 +100,108 @@ struct StreamArgs {
   uint32_t smem;  // dynamic shared memory of the launch, bytes
 };
 
-// Escapes of one flagged lane word, in weight order across the warp: OR-masks for the two
-// BF16x2 words (exponent bits of the code-15 weights, from the row's escape cursor) and the
-// tile's escape count. Nearly every flagged tile holds its escapes in a single lane: that lane
-// reads them straight from the cursor and the warp learns the count with one shuffle; otherwise
-// a ballot scan orders the lanes. Out of line on purpose: flagged tiles are rare and the hot
-// loop has to stay within the instruction cache. Whole warp calls it.
-__device__ __noinline__ uint3 escape_patch(uint32_t c, const uint8_t *__restrict__ esc, uint32_t epos) {
-  const uint32_t hit = c & (c >> 1) & (c >> 2) & (c >> 3) & 0x1111u;  // bit 4j: code j == 15
-  const uint32_t lanes = __ballot_sync(BN_FULL, hit != 0);
-  uint32_t q = epos, tot;
-  if ((lanes & (lanes - 1)) == 0) {  // zero or one lane
-    tot = __shfl_sync(BN_FULL, (uint32_t)__popc(hit), lanes ? __ffs(lanes) - 1 : 0);
-  } else {
-    uint32_t pre;
-    warp_scan_small(__popc(hit), lanemask_lt(), pre, tot);
-    q += pre;
-  }
-  uint32_t o01 = 0, o23 = 0;
+// Escapes of one flagged lane word, in weight order across the warp: exponent bits of its
+// code-15 weights are OR-ed into the two BF16x2 words from the row's escape cursor, which then
+// moves on by the tile's escape count. Nearly every flagged tile holds its escapes in a single
+// lane: that lane reads them straight from the cursor and one shuffle tells the warp the count;
+// the general case (several lanes) is a ballot scan kept out of line. Whole warp calls it.
+__device__ __noinline__ uint3 escape_scan(uint32_t hit, const uint8_t *__restrict__ esc, uint32_t epos) {
+  uint32_t pre, tot;
+  warp_scan_small(__popc(hit), lanemask_lt(), pre, tot);
+  uint32_t q = epos + pre, o01 = 0, o23 = 0;
   if (hit & 0x0001u) o01 |= (uint32_t)esc[q++] << 7;
   if (hit & 0x0010u) o01 |= (uint32_t)esc[q++] << 23;
   if (hit & 0x0100u) o23 |= (uint32_t)esc[q++] << 7;
   if (hit & 0x1000u) o23 |= (uint32_t)esc[q++] << 23;
   return make_uint3(o01, o23, tot);
 }
-
-// Four weights of row I of a stage as two BF16x2 words (escapes not yet applied).
-template <int I, uint32_t RAW_ROW, uint32_t CODE_ROW>
-__device__ __forceinline__ void load_word(uint32_t raw, uint32_t codes, uint32_t lut, uint32_t token, uint32_t &c4, uint32_t &w01, uint32_t &w23) {
-  const uint32_t r4 = ring_u32<I * RAW_ROW>(raw, token);
-  c4 = ring_u16<I * CODE_ROW>(codes, token);
-  const uint32_t e01 = lut_read(__byte_perm(c4, lut, 0x7604));  // lut + code byte 0 * 256
-  const uint32_t e23 = lut_read(__byte_perm(c4, lut, 0x7614));  // lut + code byte 1 * 256
-  w01 = (__byte_perm(r4, 0u, 0x1100) & 0x807F807Fu) | e01;
-  w23 = (__byte_perm(r4, 0u, 0x3322) & 0x807F807Fu) | e23;
-}
-
-template <int RWG, uint32_t RAW_ROW, uint32_t CODE_ROW, int I = 0>
-__device__ __forceinline__ void clean_tile(uint32_t raw, uint32_t codes, uint32_t lut, uint32_t token, uint2 xv, float (&acc)[RWG]) {
-  if constexpr (I < RWG) {
-    uint32_t c4, w01, w23;
-    load_word<I, RAW_ROW, CODE_ROW>(raw, codes, lut, token, c4, w01, w23);
-    acc[I] = fma2_bf16(w23, xv.y, fma2_bf16(w01, xv.x, acc[I]));
-    clean_tile<RWG, RAW_ROW, CODE_ROW, I + 1>(raw, codes, lut, token, xv, acc);
+__device__ __forceinline__ void escape_patch(uint32_t c, const uint8_t *__restrict__ esc, uint32_t &epos, uint32_t &w01, uint32_t &w23) {
+  const uint32_t hit = c & (c >> 1) & (c >> 2) & (c >> 3) & 0x1111u;  // bit 4j: code j == 15
+  const uint32_t lanes = __ballot_sync(BN_FULL, hit != 0);
+  if ((lanes & (lanes - 1)) == 0) {  // one lane (or none)
+    if (hit) {
+      uint32_t q = epos;
+      if (hit & 0x0001u) w01 |= (uint32_t)esc[q++] << 7;
+      if (hit & 0x0010u) w01 |= (uint32_t)esc[q++] << 23;
+      if (hit & 0x0100u) w23 |= (uint32_t)esc[q++] << 7;
+      if (hit & 0x1000u) w23 |= (uint32_t)esc[q] << 23;
+    }
+    epos += __shfl_sync(BN_FULL, (uint32_t)__popc(hit), __ffs(lanes | 0x80000000u) - 1);
+  } else {
+    const uint3 p = escape_scan(hit, esc, epos);
+    w01 |= p.x, w23 |= p.y, epos += p.z;
   }
 }
 
-// A tile that needs care: some row holds escapes (bit u of fbits[i]), or the tile is the row's
-// partial last tile and this lane's columns may not exist (`in`).
+// Decode + accumulate of lane word (row I, tile U) of a block, all offsets immediate.
+template <int I, int U, uint32_t RAW_ROW, uint32_t CODE_ROW>
+__device__ __forceinline__ float word_fma(uint32_t raw, uint32_t codes, uint32_t lut, uint32_t token, uint2 xv, float acc) {
+  const uint32_t r4 = ring_u32<I * RAW_ROW + U * 128>(raw, token);
+  const uint32_t c4 = ring_u16<I * CODE_ROW + U * 64>(codes, token);
+  const uint32_t e01 = lut_read(__byte_perm(c4, lut, 0x7604), token);  // lut + code byte 0 * 256
+  const uint32_t e23 = lut_read(__byte_perm(c4, lut, 0x7614), token);  // lut + code byte 1 * 256
+  const uint32_t w01 = (__byte_perm(r4, 0u, 0x1100) & 0x807F807Fu) | e01;
+  const uint32_t w23 = (__byte_perm(r4, 0u, 0x3322) & 0x807F807Fu) | e23;
+  return fma2_bf16(w23, xv.y, fma2_bf16(w01, xv.x, acc));
+}
+
+// NT tiles x RWG rows, straight-line: no loop, no test, every offset an immediate.
+template <int RWG, int NT, uint32_t RAW_ROW, uint32_t CODE_ROW, int U = 0>
+__device__ __forceinline__ void block_fma(uint32_t raw, uint32_t codes, uint32_t xs, uint32_t lut, uint32_t token, float (&acc)[RWG]) {
+  if constexpr (U < NT) {
+    const uint2 xv = x_read<U * 256>(xs, token);
+    acc[0] = word_fma<0, U, RAW_ROW, CODE_ROW>(raw, codes, lut, token, xv, acc[0]);
+    if constexpr (RWG > 1) acc[1] = word_fma<1, U, RAW_ROW, CODE_ROW>(raw, codes, lut, token, xv, acc[1]);
+    if constexpr (RWG > 2) acc[2] = word_fma<2, U, RAW_ROW, CODE_ROW>(raw, codes, lut, token, xv, acc[2]);
+    if constexpr (RWG > 3) acc[3] = word_fma<3, U, RAW_ROW, CODE_ROW>(raw, codes, lut, token, xv, acc[3]);
+    block_fma<RWG, NT, RAW_ROW, CODE_ROW, U + 1>(raw, codes, xs, lut, token, acc);
+  }
+}
+
+// One tile of RWG rows with every check: escapes where fbits says so, lanes outside a partial
+// tile masked. `u`: the tile's bit in fbits.
 template <int RWG, uint32_t RAW_ROW, uint32_t CODE_ROW, int I = 0>
 __device__ __forceinline__ void careful_tile(uint32_t raw, uint32_t codes, uint32_t lut, uint32_t token, uint2 xv, int u, bool in, const uint32_t (&fbits)[RWG], const uint8_t *__restrict__ esc, uint32_t (&epos)[RWG], float (&acc)[RWG]) {
   if constexpr (I < RWG) {
-    uint32_t c4, w01, w23;
-    load_word<I, RAW_ROW, CODE_ROW>(raw, codes, lut, token, c4, w01, w23);
-    if ((fbits[I] >> u) & 1u) {
-      const uint3 p = escape_patch(c4, esc, epos[I]);
-      w01 |= p.x, w23 |= p.y, epos[I] += p.z;
-    }
+    const uint32_t r4 = ring_u32<I * RAW_ROW>(raw, token);
+    const uint32_t c4 = ring_u16<I * CODE_ROW>(codes, token);
+    uint32_t w01 = (__byte_perm(r4, 0u, 0x1100) & 0x807F807Fu) | lut_read(__byte_perm(c4, lut, 0x7604), token);
+    uint32_t w23 = (__byte_perm(r4, 0u, 0x3322) & 0x807F807Fu) | lut_read(__byte_perm(c4, lut, 0x7614), token);
+    if ((fbits[I] >> u) & 1u) escape_patch(c4, esc, epos[I], w01, w23);
     const float s = fma2_bf16(w23, xv.y, fma2_bf16(w01, xv.x, acc[I]));
     acc[I] = in ? s : acc[I];
     careful_tile<RWG, RAW_ROW, CODE_ROW, I + 1>(raw, codes, lut, token, xv, u, in, fbits, esc, epos, acc);
   }
 }
 
-// One stage (nt tiles) of RWG rows: decode and accumulate.
-//   raw    shared address of this lane's raw bytes of row 0, tile 0 (rows RAW_ROW, tiles 128 apart)
-//   codes  shared address of this lane's code word of row 0, tile 0 (rows CODE_ROW, tiles 64 apart)
-//   xs     shared address of this lane's four BF16 inputs of the first tile (tiles 256 apart)
-//   lut    shared address of this lane's column of the pair table (bits 8..15 clear)
-//   care   bit u set: tile u needs the careful path (an escape in some row, or a partial tile)
-//   partial  bit u set: tile u is the row's partial last tile; lane_in_partial: this lane's
-//          columns exist in it
-// Runs of clean tiles go through a loop without any per-tile test, unrolled by two only: the hot
-// loop must stay within the instruction cache.
-template <int RWG, uint32_t RAW_ROW, uint32_t CODE_ROW>
-__device__ __forceinline__ void consume_stage(uint32_t raw, uint32_t codes, uint32_t xs, uint32_t lut, uint32_t token, int nt, uint32_t partial, bool lane_in_partial, const uint32_t (&fbits)[RWG], uint32_t care, const uint8_t *__restrict__ esc, uint32_t (&epos)[RWG], float (&acc)[RWG]) {
-  const uint32_t stops = care | (1u << nt);  // sentinel after the last tile
-  int u = 0;
-  while (true) {
-    const int run = __ffs(stops >> u) - 1;
-#pragma unroll 2
-    for (int k = 0; k < run; k++) {
-      clean_tile<RWG, RAW_ROW, CODE_ROW>(raw, codes, lut, token, x_read(xs), acc);
-      raw += 128, codes += 64, xs += 256;
+// One stage (nt tiles) of RWG rows, in blocks of BT tiles. A full block without a flagged tile
+// (and not holding a row's partial last tile) runs as one straight line of code: no loop, no test,
+// every offset an immediate. Any other block goes tile by tile with every check.
+//   fbits[i]  bit u: tile u of row i holds escapes
+//   partial   the stage's last tile is a row's partial last tile; lanes without
+//             `lane_in_partial` hold no weight in it
+template <int RWG, int KC, uint32_t RAW_ROW, uint32_t CODE_ROW>
+__device__ __forceinline__ void consume_stage(uint32_t raw, uint32_t codes, uint32_t xs, uint32_t lut, uint32_t token, int nt, bool partial, bool lane_in_partial, const uint32_t (&fbits)[RWG], const uint8_t *__restrict__ esc, uint32_t (&epos)[RWG], float (&acc)[RWG]) {
+  constexpr int BT = KC < 4 ? KC : (RWG >= 4 ? 2 : 4);
+  constexpr int NB = (KC + BT - 1) / BT;
+  uint32_t any = 0;
+#pragma unroll
+  for (int i = 0; i < RWG; i++) any |= fbits[i];
+#pragma unroll
+  for (int b = 0; b < NB; b++) {
+    const int left = nt - b * BT;
+    if (left <= 0) break;
+    const uint32_t braw = raw + b * BT * 128, bcodes = codes + b * BT * 64, bxs = xs + b * BT * 256;
+    const bool tail = partial && left <= BT;  // this block holds the partial tile
+    if (left >= BT && !tail && !((any >> (b * BT)) & ((1u << BT) - 1u))) {
+      block_fma<RWG, BT, RAW_ROW, CODE_ROW>(braw, bcodes, bxs, lut, token, acc);
+    } else {
+      const int n = left < BT ? left : BT;
+      for (int k = 0; k < n; k++) {
+        const bool in = lane_in_partial || !(tail && k == n - 1);
+        careful_tile<RWG, RAW_ROW, CODE_ROW>(braw + k * 128, bcodes + k * 64, lut, token, x_read<0>(bxs + k * 256, token), b * BT + k, in, fbits, esc, epos, acc);
+      }
     }
-    u += run;
-    if (u >= nt) break;
-    careful_tile<RWG, RAW_ROW, CODE_ROW>(raw, codes, lut, token, x_read(xs), u, lane_in_partial || !((partial >> u) & 1u), fbits, esc, epos, acc);
-    raw += 128, codes += 64, xs += 256;
-    u++;
   }
 }
 
@@ -287,7 +298,7 @@ __global__ void __launch_bounds__(WARPS * 32, 1) r4_stream_kernel(StreamArgs a) 
 
   const uint32_t lut_lane = 65536u + lane * 4;
   // in a row's partial last tile (K % 128 != 0) only the lanes below K % 128 hold weights
-  const uint32_t partial_bit = (K & 127) ? 1u << (nt_last - 1) : 0u;
+  const bool has_partial = (K & 127) != 0;
   const bool lane_in_partial = (int64_t)lane * 4 < (K & 127);
   int cs = 0;           // consumer slot
   uint32_t phases = 0;  // bit s: parity to wait for on slot s
@@ -337,19 +348,16 @@ __global__ void __launch_bounds__(WARPS * 32, 1) r4_stream_kernel(StreamArgs a) 
       const uint32_t codes = s_ring + (uint32_t)cs * STAGE + RAW_STAGE + lane * 2;
       const bool last = c == last_chunk;
       const int nt = last ? nt_last : KC;
-      const uint32_t partial = last ? partial_bit : 0u;
+      const bool partial = last && has_partial;
       if (wide) {
-        uint32_t fbits[RW], care = partial;
+        uint32_t fbits[RW];
 #pragma unroll
-        for (int i = 0; i < RW; i++) {
-          fbits[i] = (fmask[i] >> (t0 & 31)) & STAGE_MASK;
-          care |= fbits[i];
-        }
-        consume_stage<RW, RAW_ROW, CODE_ROW>(raw, codes, xs, lut_lane, token, nt, partial, lane_in_partial, fbits, care, a.w.esc, epos, acc);
+        for (int i = 0; i < RW; i++) fbits[i] = (fmask[i] >> (t0 & 31)) & STAGE_MASK;
+        consume_stage<RW, KC, RAW_ROW, CODE_ROW>(raw, codes, xs, lut_lane, token, nt, partial, lane_in_partial, fbits, a.w.esc, epos, acc);
       } else {
         uint32_t fb1[1] = {(fmask[0] >> (t0 & 31)) & STAGE_MASK}, ep1[1] = {epos[0]};
         float ac1[1] = {acc[0]};
-        consume_stage<1, RAW_ROW, CODE_ROW>(raw, codes, xs, lut_lane, token, nt, partial, lane_in_partial, fb1, fb1[0] | partial, a.w.esc, ep1, ac1);
+        consume_stage<1, KC, RAW_ROW, CODE_ROW>(raw, codes, xs, lut_lane, token, nt, partial, lane_in_partial, fb1, a.w.esc, ep1, ac1);
         epos[0] = ep1[0], acc[0] = ac1[0];
       }
       xs += KC * 256;
@@ -416,34 +424,18 @@ static int launch_stream(StreamArgs a, cudaStream_t s) {
   return launched("r4_stream_kernel");
 }
 
-// Kernel shape: 0 (default) or an experiment selected with BINADE_B200_STREAM_SHAPE.
-static int stream_shape() {
-  static int n = -1;
-  if (n < 0) {
-    const char *e = getenv("BINADE_B200_STREAM_SHAPE");
-    n = e ? atoi(e) : 0;
-  }
-  return n;
-}
-
-// Returns -1 when the shape is outside what the streaming kernel covers.
+// Returns -1 when the shape is outside what the streaming kernel covers. More resident warps
+// hide more of the decode's dependent-issue latency, so the widest block whose rings still fit
+// the shared window next to x is taken (24 warps for K = 3840, 20 for K = 15360).
 int stream_matvec(const bn_r4 *w, const uint16_t *x, int64_t N, int64_t K, uint16_t *y, cudaStream_t s) {
   const int64_t T = tiles(K);
   if (K % 16 || N < 1 || T > 200) return -1;
   StreamArgs a{};
   a.w = *w, a.x = x, a.y = y, a.N = N, a.K = K, a.T = (int)T;
-  int e = -1;
-  switch (stream_shape()) {
-    case 1: e = launch_stream<8, 4, 8>(a, s); break;
-    case 2: e = launch_stream<12, 4, 8>(a, s); break;
-    case 3: e = launch_stream<16, 2, 8>(a, s); break;
-    case 4: e = launch_stream<16, 4, 4>(a, s); break;
-    case 5: e = launch_stream<20, 2, 8>(a, s); break;
-    case 6: e = launch_stream<24, 2, 8>(a, s); break;
-    case 7: e = launch_stream<24, 2, 4>(a, s); break;
-    default: e = launch_stream<16, 2, 8>(a, s); break;
-  }
-  if (e == -1) e = launch_stream<8, 4, 4>(a, s);
+  int e = launch_stream<24, 2, 8>(a, s);
+  if (e == -1) e = launch_stream<20, 2, 8>(a, s);
+  if (e == -1) e = launch_stream<16, 2, 8>(a, s);
+  if (e == -1) e = launch_stream<8, 2, 8>(a, s);
   return e;
 }
 
