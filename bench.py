@@ -217,16 +217,15 @@ def run_ours(args) -> dict | None:
         del d, p, u
     step_bytes = sum(l[4] for l in layers)
     xs = {k: ck.to_device(synthetic_input(k, rank)).view(torch.bfloat16) for k in {k for _, _, k in SHAPES}}
-    gathered = {n: torch.empty(world * n, dtype=torch.bfloat16, device=dev) for _, n, _ in SHAPES} if world > 1 else None
+    if world > 1:
+        # every rank's matrices are its row shard of a world-times taller layer: the public
+        # sharded hook multiplies locally and all-gathers the slices (NCCL) in rank order
+        from binade_b200.cuda.dist import RowShardedLinear
+
+        layers = [(name, n, k, [RowShardedLinear(m, world * n) for m in mods], nbytes) for name, n, k, mods, nbytes in layers]
 
     def step(i: int):
-        out = []
-        for name, n, k, mods, _ in layers:
-            y = mods[i % copies]._matvec(xs[k])
-            if world > 1:
-                dist.all_gather_into_tensor(gathered[n], y)
-            out.append(y)
-        return out
+        return [mods[i % copies](xs[k]) for _, _, k, mods, _ in layers]
 
     # ---- parity of this very workload against the oracle, on one small projection
     if rank == 0 and not args.no_parity:
@@ -235,7 +234,7 @@ def run_ours(args) -> dict | None:
         j = min(range(len(SHAPES)), key=lambda i: SHAPES[i][1] * SHAPES[i][2])
         name, n, k = SHAPES[j]
         want = o.c_r4_matvec(o.pack_r4(synthetic_weight(name, n, k, rank)), synthetic_input(k, rank), n, k)
-        got = layers[j][3][0]._matvec(xs[k]).view(torch.int16).cpu().numpy().view(np.uint16)
+        got = layers[j][3][0](xs[k])[:n].contiguous().view(torch.int16).cpu().numpy().view(np.uint16)
         if not np.array_equal(got, want):
             raise SystemExit("bench: GPU matvec differs from the oracle; refusing to report a number")
 
@@ -307,8 +306,9 @@ def run_ours(args) -> dict | None:
 
     per_shape = {}
     for name, n, k, mods, nbytes in layers if not args.quick else []:
-        us = graph_us(lambda i: mods[i % copies]._matvec(xs[k]))
-        dense = [m.dense() for m in mods]
+        local = [m.local if world > 1 else m for m in mods]
+        us = graph_us(lambda i: local[i % copies]._matvec(xs[k]))
+        dense = [m.dense() for m in local]
         outs = [torch.empty(n, dtype=torch.bfloat16, device=dev) for _ in range(copies)]
         us_bf16 = graph_us(lambda i: torch.mv(dense[i % copies], xs[k], out=outs[i % copies]))
         per_shape[name] = {"us": round(us, 2), "gbs": round(nbytes / us / 1e3, 1), "pct_of_8tbs": round(nbytes / us / 1e3 / NOMINAL_HBM_GBS * 100, 1), "bf16_gemv_us": round(us_bf16, 2), "speedup_vs_bf16": round(us_bf16 / us, 3)}
@@ -323,9 +323,7 @@ def run_ours(args) -> dict | None:
         dx = {k: h_x[k].to(dev, non_blocking=True) for k in k_list}
         for j, (name, n, k, mods, _) in enumerate(layers):
             y = mods[i % copies](dx[k])
-            if world > 1:
-                dist.all_gather_into_tensor(gathered[n], y)
-            h_y[j].copy_(y, non_blocking=True)
+            h_y[j].copy_(y[:n] if world > 1 else y, non_blocking=True)
         torch.cuda.synchronize()
 
     e2e_steps = 3 if args.quick else min(args.steps, 200)

@@ -1,0 +1,109 @@
+"""Row sharding across ranks, on CPU: the cuts (index arithmetic) against the oracle, and the
+gather wiring with two gloo ranks (the local product is the oracle here: the CUDA kernels cannot
+run without a GPU, and the sharded module only adds the cut and the collective around them)."""
+
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+import torch.multiprocessing as mp
+
+from binade_b200 import pack
+from binade_b200.cuda import dist as bd
+from oracle import oracle as o
+
+
+def _weights(shape, seed=0):
+    rng = np.random.default_rng(seed)
+    w = rng.standard_normal(shape).astype(np.float32) * 0.02
+    w[rng.random(shape) < 5e-3] *= 64
+    return (w.view(np.uint32) >> 16).astype(np.uint16)
+
+
+def test_row_range_covers_rows_once():
+    for N in (0, 1, 7, 8, 100, 4097):
+        for world in (1, 2, 3, 8):
+            spans = [bd.row_range(N, r, world) for r in range(world)]
+            assert spans[0][0] == 0 and spans[-1][1] == N
+            assert all(a[1] == b[0] for a, b in zip(spans, spans[1:]))
+            assert max(b - a for a, b in spans) - min(b - a for a, b in spans) <= 1
+    with pytest.raises(ValueError):
+        bd.row_range(8, 2, 2)
+
+
+@pytest.mark.parametrize("N,K,world", [(37, 704, 2), (64, 256, 4), (10, 100, 3), (5, 128, 8)])
+def test_shard_packed_decodes_to_its_rows(N, K, world):
+    u = _weights((N, K), seed=N)
+    p = pack.pack(u)
+    got = []
+    for rank in range(world):
+        s = bd.shard_packed(p, rank, world)
+        r0, r1 = bd.row_range(N, rank, world)
+        assert s["shape"] == (r1 - r0, K) and s["meta"].size == (r1 - r0) * -(-K // 128)
+        if r1 > r0:
+            ranks, end = o.c_rice_decode_ranks(s["meta"], s["bits"], s["roff"], K)
+            nxt = np.append(s["roff"][1:].astype(np.int64), s["bits"].size)
+            assert np.array_equal((end + 31) >> 5, nxt)
+            got.append(o.np_join(s["raw"], s["table"][ranks]))
+    assert np.array_equal(np.concatenate(got), u)
+
+
+@pytest.mark.parametrize("N,K,world", [(37, 704, 2), (64, 256, 4), (9, 128, 8)])
+def test_shard_r4_matches_oracle_rows(N, K, world):
+    u = _weights((N, K), seed=K)
+    a = o.pack_r4(u)
+    _, table, ranks = o.c_ranks_of(u)  # the tensor's own table: a shard keeps it
+    t = {k: torch.from_numpy(v.view(np.int16) if v.dtype == np.uint16 else v.view(np.int32) if v.dtype == np.uint32 else v) for k, v in a.items() if k != "shape"}
+    t["raw"] = t["raw"].reshape(N, K)
+    pieces = []
+    for rank in range(world):
+        s = bd.shard_r4(t, rank, world)
+        r0, r1 = bd.row_range(N, rank, world)
+        want = o.c_r4_transcode(ranks[r0:r1], table) if r1 > r0 else None
+        if want is None:
+            assert s["raw"].shape[0] == 0 and s["esc"].numel() == 1
+            continue
+        assert np.array_equal(s["codes"].numpy().view(np.uint16), want["codes"])
+        assert np.array_equal(s["flags"].numpy(), want["flags"])
+        assert np.array_equal(s["esc"].numpy(), want["esc"])
+        assert np.array_equal(s["row_esc"].numpy().view(np.uint32), want["row_esc"])
+        pieces.append(s["raw"].numpy())
+    assert np.array_equal(np.concatenate(pieces), a["raw"].reshape(N, K))
+
+
+def _free_port() -> int:
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _rank_main(rank: int, world: int, port: int, N: int, K: int, out_dir: str):
+    import torch.distributed as dist
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    u = _weights((N, K), seed=3)
+    x = _weights((1, K), seed=4)
+    shard = bd.shard_packed(pack.pack(u), rank, world)
+    ranks, _ = o.c_rice_decode_ranks(shard["meta"], shard["bits"], shard["roff"], K)
+    w_local = o.np_join(shard["raw"], shard["table"][ranks])
+
+    def local(xt):  # stands for R4Linear(transcode(shard)) on this rank's GPU
+        y = o.c_dense_rows(xt.view(torch.int16).numpy().view(np.uint16).reshape(-1, K), w_local)
+        return torch.from_numpy(y.view(np.int16)).view(torch.bfloat16).reshape(*xt.shape[:-1], -1)
+
+    m = bd.RowShardedLinear(local, N)
+    y = m(torch.from_numpy(x.view(np.int16)).view(torch.bfloat16))
+    np.save(os.path.join(out_dir, f"y{rank}.npy"), y.view(torch.int16).numpy().view(np.uint16))
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("N", [64, 37])
+def test_row_sharded_linear_two_gloo_ranks(tmp_path, N):
+    K, world = 256, 2
+    mp.spawn(_rank_main, args=(world, _free_port(), N, K, str(tmp_path)), nprocs=world, join=True)
+    want = o.c_dense_rows(_weights((1, K), seed=4), _weights((N, K), seed=3))
+    for rank in range(world):
+        assert np.array_equal(np.load(tmp_path / f"y{rank}.npy"), want), rank

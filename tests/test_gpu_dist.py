@@ -1,0 +1,53 @@
+"""Row-sharded linear on two GPUs (NCCL): gathered output equals the single-GPU product bit for
+bit. Skipped on a box with one GPU."""
+
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+import torch.multiprocessing as mp
+
+pytestmark = pytest.mark.gpu
+
+
+def _rank_main(rank: int, world: int, port: int, N: int, K: int, out_dir: str):
+    import torch.distributed as dist
+
+    from binade_b200 import pack
+    from binade_b200.cuda import dist as bd
+    from binade_b200.cuda import kernels as ck
+    from binade_b200.cuda import r4
+    from test_gpu_parity import bf16_words, weights
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    rng = np.random.default_rng(5)
+    u = weights(rng, (N, K), escapes=False)
+    u.reshape(-1)[7::211] = 0x5F80  # rare exponent: escapes, finite sums
+    xw = bf16_words(rng.standard_normal((1, K)))
+    p = pack.pack(u)
+    x = ck.to_device(xw).view(torch.bfloat16)
+    local = r4.R4Linear(r4.transcode(bd.shard_packed(p, rank, world)))
+    y = bd.RowShardedLinear(local, N)(x)
+    cut = r4.R4Linear(bd.shard_r4(r4.transcode(p), rank, world))  # the same rows, cut after expansion
+    y2 = bd.RowShardedLinear(cut, N)(x)
+    full = r4.R4Linear(r4.transcode(p))(x)
+    ok = torch.equal(y.view(torch.int16), full.view(torch.int16)) and torch.equal(y2.view(torch.int16), full.view(torch.int16))
+    with open(os.path.join(out_dir, f"ok{rank}"), "w") as f:
+        f.write("1" if ok else "0")
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("N,K", [(512, 3840), (301, 704)])
+def test_row_sharded_linear_two_gpus(tmp_path, N, K):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    mp.spawn(_rank_main, args=(2, port, N, K, str(tmp_path)), nprocs=2, join=True)
+    assert [(tmp_path / f"ok{r}").read_text() for r in range(2)] == ["1", "1"]
