@@ -147,6 +147,9 @@ def run_reference(args) -> dict:
     reference project has no CPU matvec (its CPU code is the numpy codec) and its GPU kernels
     need MLX, which this box lacks, so the C port of its kernel semantics stands in. Each step
     covers the same fraction of every matrix's rows, sized so the run ends within about a minute."""
+    from oracle import oracle as o
+
+    threads = o.set_threads(cpu_cores())  # a multi-process launcher caps OMP_NUM_THREADS at 1
     mats = cpu_r4_layer(0)
     xs = {k: synthetic_input(k, 0) for k in {k for _, _, k in SHAPES}}
     t0 = time.perf_counter()
@@ -160,7 +163,7 @@ def run_reference(args) -> dict:
         done += cpu_step(mats, xs, frac)
     dt = time.perf_counter() - t0
     val = done / dt / 1e9
-    base = {"value": val, "unit": UNIT, "cores": cpu_cores(), "kind": "port", "sample": f"every step: the first {frac:.4f} of the rows of each of the 7 matrices, C oracle with OpenMP over rows"}
+    base = {"value": val, "unit": UNIT, "cores": threads, "kind": "port", "sample": f"every step: the first {frac:.4f} of the rows of each of the 7 matrices, C oracle with OpenMP over rows"}
     return {
         "impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16 weights (R4 coded), fp32 accumulate",
@@ -184,9 +187,16 @@ def run_ours(args) -> dict | None:
     if world > 1:
         import torch.distributed as dist
 
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+        import datetime
+
+        # a short timeout: a rank that dies or falls out of step ends the run instead of holding the GPUs
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local), timeout=datetime.timedelta(seconds=120))
     dev = torch.device("cuda", local)
     copies = args.copies
+    t_start = time.perf_counter()
+
+    def note(msg: str):  # progress on stderr: a stalled run shows where it stopped
+        print(f"[bench rank {rank} +{time.perf_counter() - t_start:6.1f}s] {msg}", file=sys.stderr, flush=True)
 
     # ---- build: host Rice encode (product packer), device expand (timed), R4 resident
     layers, expand_ms, expand_bytes, host_pack_s, bits_file, bits_r4 = [], 0.0, 0, 0.0, 0, 0
@@ -216,6 +226,7 @@ def run_ours(args) -> dict | None:
         layers.append((name, n, k, mods, r4.r4_bytes(a) + 2 * k + 2 * n))
         del d, p, u
     step_bytes = sum(l[4] for l in layers)
+    note(f"{len(layers)} matrices packed, expanded and resident")
     xs = {k: ck.to_device(synthetic_input(k, rank)).view(torch.bfloat16) for k in {k for _, _, k in SHAPES}}
     if world > 1:
         # every rank's matrices are its row shard of a world-times taller layer: the public
@@ -234,10 +245,12 @@ def run_ours(args) -> dict | None:
         j = min(range(len(SHAPES)), key=lambda i: SHAPES[i][1] * SHAPES[i][2])
         name, n, k = SHAPES[j]
         want = o.c_r4_matvec(o.pack_r4(synthetic_weight(name, n, k, rank)), synthetic_input(k, rank), n, k)
-        got = layers[j][3][0](xs[k])[:n].contiguous().view(torch.int16).cpu().numpy().view(np.uint16)
+        m0 = layers[j][3][0]
+        got = (m0.local if world > 1 else m0)(xs[k]).view(torch.int16).cpu().numpy().view(np.uint16)  # no collective: only rank 0 checks
         if not np.array_equal(got, want):
             raise SystemExit("bench: GPU matvec differs from the oracle; refusing to report a number")
 
+    note("parity checked")
     # ---- timed region: W warm-up steps, then exactly K steps as replays of a CUDA graph that
     # holds one step per weight copy (plus a shorter graph for K % copies)
     for i in range(max(args.warmup, 3)):
@@ -259,9 +272,11 @@ def run_ours(args) -> dict | None:
         torch.cuda.synchronize()
         return g
 
+    note("warm-up done")
     full, rem = divmod(args.steps, copies)
     g_full = capture(copies) if full else None
     g_rem = capture(rem) if rem else None
+    note("graphs captured")
     if world > 1:
         dist.barrier()
     torch.cuda.synchronize()
@@ -282,6 +297,7 @@ def run_ours(args) -> dict | None:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms = float(t.item())
     ms_per_step = ms / args.steps
+    note(f"timed region done: {ms_per_step * 1e3:.1f} us per step")
     value = world * step_bytes / (ms_per_step * 1e-3) / 1e9
 
     # ---- per shape: the matvec alone and cuBLAS BF16 GEMV on the pre-decoded weight, both
@@ -314,6 +330,7 @@ def run_ours(args) -> dict | None:
         per_shape[name] = {"us": round(us, 2), "gbs": round(nbytes / us / 1e3, 1), "pct_of_8tbs": round(nbytes / us / 1e3 / NOMINAL_HBM_GBS * 100, 1), "bf16_gemv_us": round(us_bf16, 2), "speedup_vs_bf16": round(us_bf16 / us, 3)}
         del dense, outs
 
+    note("per-shape timings done")
     # ---- end to end through the public hook with host buffers
     k_list = sorted({k for _, _, k in SHAPES})
     h_x = {k: torch.from_numpy(synthetic_input(k, rank).view(np.int16)).view(torch.bfloat16).pin_memory() for k in k_list}
@@ -342,10 +359,9 @@ def run_ours(args) -> dict | None:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         e2e_ms = float(t.item())
     e2e_val = world * step_bytes / (e2e_ms * 1e-3) / 1e9
+    note("end-to-end leg done")
 
     if rank != 0:
-        if world > 1:
-            dist.destroy_process_group()
         return None
 
     peaks = measured_peaks()
@@ -369,6 +385,9 @@ def run_ours(args) -> dict | None:
     }  # fmt: skip
     # ---- CPU baseline on a bounded sample (rank 0, single GPU runs only)
     if world == 1 and not args.no_cpu and not args.quick:
+        from oracle import oracle as o
+
+        threads = o.set_threads(cpu_cores())
         mats = cpu_r4_layer(0, names={"q", "k"})
         cxs = {k: synthetic_input(k, 0) for k in {m[2] for m in mats}}
         cpu_step(mats, cxs)
@@ -377,11 +396,9 @@ def run_ours(args) -> dict | None:
             cpu_step(mats, cxs)
             n_rep += 1
         dt = (time.perf_counter() - t0) / n_rep
-        result["cpu_baseline"] = {"value": sum(m[4] for m in mats) / dt / 1e9, "unit": UNIT, "cores": cpu_cores(), "kind": "port", "sample": f"q and k projections only (2 of 7 matvecs), {n_rep} repetitions, C oracle with OpenMP"}
+        result["cpu_baseline"] = {"value": sum(m[4] for m in mats) / dt / 1e9, "unit": UNIT, "cores": threads, "kind": "port", "sample": f"q and k projections only (2 of 7 matvecs), {n_rep} repetitions, C oracle with OpenMP"}
     else:
         result["cpu_baseline"] = None
-    if world > 1:
-        dist.destroy_process_group()
     return result
 
 
@@ -410,7 +427,17 @@ def main():
         return
     out = run_ours(args)
     if out is not None:
-        print(json.dumps(out))
+        print(json.dumps(out), flush=True)
+    if int(os.environ.get("WORLD_SIZE", 1)) > 1:
+        # Leave together and at once: tearing the NCCL communicator down while captured graphs
+        # still hold its kernels has been seen to block; the result line is already out.
+        import torch
+        import torch.distributed as dist
+
+        torch.cuda.synchronize()
+        dist.barrier()
+        sys.stderr.flush()
+        os._exit(0)
 
 
 if __name__ == "__main__":

@@ -265,6 +265,11 @@ def _i(v):
     return ctypes.c_int64(int(v))
 
 
+def set_threads(n: int) -> int:
+    """OpenMP threads of the C oracle's row loops; returns the count in effect."""
+    return int(lib().bo_set_threads(ctypes.c_int(n)))
+
+
 def c_rank_table(hist):
     table, rank = np.zeros(256, np.uint8), np.zeros(256, np.uint8)
     lib().bo_rank_table(_p(np.ascontiguousarray(hist, np.int64)), _p(table), _p(rank))
