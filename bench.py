@@ -361,6 +361,30 @@ def run_ours(args) -> dict | None:
     e2e_val = world * step_bytes / (e2e_ms * 1e-3) / 1e9
     note("end-to-end leg done")
 
+    # ---- whole-model decode: Llama-3.1-8B-shaped synthetic decoder, greedy, batch 1
+    decode = None
+    if not args.quick and not args.no_decode:
+        from binade_b200.cuda.llama import Decoder, LlamaShape
+
+        shape = LlamaShape()
+        prompt = torch.randint(0, shape.vocab, (40,), device=dev, generator=torch.Generator(device=dev).manual_seed(1))
+        decode = {"model": "Llama-3.1-8B-shaped synthetic decoder (32 layers, hidden 4096, FFN 14336, GQA 32/8 x 128, vocab 128256), N(0,0.02) BF16 weights, 40-token random prompt + 256 greedy tokens, one CUDA graph per token, linears row-sharded over the ranks"}
+        seqs = {}
+        for kind in ("r4", "bf16"):
+            model = Decoder(shape, kind=kind, rank=rank, world=world)
+            toks, secs = model.generate(prompt, 256)
+            if world > 1:
+                t = torch.tensor([secs], device=dev)
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+                secs = float(t.item())
+            seqs[kind] = toks
+            decode[f"{kind}_tok_s"] = round(256 / secs, 1)
+            decode[f"{kind}_weight_gb_per_token_per_gpu"] = round(model.linear_bytes() / 1e9, 3)
+            del model
+            torch.cuda.empty_cache()
+        decode["r4_vs_bf16"] = round(decode["r4_tok_s"] / decode["bf16_tok_s"], 3)
+        decode["tokens_equal_until"] = int((seqs["r4"] != seqs["bf16"]).to(torch.int64).cumsum(0).eq(0).sum().item())
+        note(f"decode leg done: R4 {decode['r4_tok_s']} tok/s, BF16 {decode['bf16_tok_s']} tok/s")
     if rank != 0:
         return None
 
@@ -381,6 +405,7 @@ def run_ours(args) -> dict | None:
         "roofline": {"bound": "hbm", "kernel": "r4_rows_kernel<M=1> (all 7 launches of a step)", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"], "peak_source": peaks["source"], "bytes_per_launch": per_launch_bytes, "traffic": args.traffic},
         "e2e": {"value": e2e_val, "unit": UNIT, "ms_per_step": e2e_ms, "h2d_bytes_per_step": sum(2 * k for k in k_list), "d2h_bytes_per_step": sum(2 * n for _, n, _ in SHAPES), "api": "R4Linear.__call__ on host-resident inputs, outputs copied back to pinned host memory"},
         "gpu_launches": launches,
+        "decode": decode,
         "clocks": clocks.summary(),
     }  # fmt: skip
     # ---- CPU baseline on a bounded sample (rank 0, single GPU runs only)
@@ -410,6 +435,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=("ours", "reference"))
     ap.add_argument("--copies", type=int, default=3, help="weight copies rotated between steps")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-decode", action="store_true", help="skip the whole-model decode leg")
     ap.add_argument("--shapes", default="", help="comma list of matrices to keep (default: all seven); for small profiling runs")
     ap.add_argument("--quick", action="store_true", help="timed region only: skip the per-shape, end-to-end and CPU legs")
     ap.add_argument("--outliers", type=float, default=OUTLIERS, help="fraction of weights scaled x64 (default: the benchmark's 0.1 %%)")

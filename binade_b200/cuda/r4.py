@@ -58,6 +58,41 @@ def transcode(module) -> dict:
     return {"raw": raw.reshape(R, K), "table": table, "codes": codes, "flags": flags, "esc": esc, "row_esc": row_esc, "shape": tuple(raw.shape)}
 
 
+def from_dense(w: torch.Tensor) -> dict:
+    """R4 arrays straight from a BF16 weight [.., K] already on the GPU (K % 4 == 0), without
+    going through a file: exponent histogram -> rank table -> 4-bit codes, flags and escapes with
+    torch ops on the device (the histogram alone crosses to the host). Gives the arrays that
+    packing the tensor and expanding it (pack.pack + transcode) would give; meant for synthetic
+    models and tests, where Rice-encoding billions of weights on the host first serves nothing."""
+    from ..format import rank_table
+
+    if w.dtype != torch.bfloat16 or not w.is_cuda:
+        raise ValueError("from_dense takes a bfloat16 tensor on a CUDA device")
+    shape = tuple(w.shape)
+    K = shape[-1]
+    if K % 4:
+        raise ValueError(f"R4 needs K % 4 == 0, got {K}")
+    u = w.contiguous().view(torch.int16).reshape(-1, K)
+    R, T = u.shape[0], -(-K // TILE)
+    exps = ((u.to(torch.int32) >> 7) & 0xFF).to(torch.uint8)
+    raw = (((u.to(torch.int32) >> 8) & 0x80) | (u.to(torch.int32) & 0x7F)).to(torch.uint8)
+    hist = torch.bincount(exps.reshape(-1).to(torch.int64), minlength=256).cpu().numpy()
+    table, rank = rank_table(hist)
+    ranks = ck.to_device(rank)[exps.to(torch.int64)]  # uint8 [R, K]
+    del exps
+    if K != T * TILE:
+        ranks = torch.nn.functional.pad(ranks, (0, T * TILE - K))
+    hit = ranks >= 15
+    table_t = ck.to_device(table)
+    esc = torch.cat([table_t[ranks[hit].to(torch.int64)], torch.zeros(1, dtype=torch.uint8, device=w.device)])
+    per_row = hit.sum(dim=1)
+    row_esc = (torch.cumsum(per_row, 0) - per_row).to(torch.int32)
+    flags = hit.view(R, T, TILE).any(dim=2).to(torch.uint8).reshape(-1)
+    q = torch.clamp(ranks, max=15).to(torch.int32).view(R, T * 32, 4)
+    codes = (q[..., 0] | (q[..., 1] << 4) | (q[..., 2] << 8) | (q[..., 3] << 12)).to(torch.int16).reshape(-1)
+    return {"raw": raw, "table": table_t, "codes": codes, "flags": flags, "esc": esc, "row_esc": row_esc, "shape": shape}
+
+
 def r4_bytes(a: dict) -> int:
     """Bytes a matvec streams: every R4 array (reference: scripts/matvec_bench.py:34-35)."""
     return sum(a[k].numel() * a[k].element_size() for k in ck.R4_KEYS)

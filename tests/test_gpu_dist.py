@@ -51,3 +51,32 @@ def test_row_sharded_linear_two_gpus(tmp_path, N, K):
         port = s.getsockname()[1]
     mp.spawn(_rank_main, args=(2, port, N, K, str(tmp_path)), nprocs=2, join=True)
     assert [(tmp_path / f"ok{r}").read_text() for r in range(2)] == ["1", "1"]
+
+
+def _decoder_main(rank: int, world: int, port: int, out_dir: str):
+    import torch.distributed as dist
+
+    from binade_b200.cuda.llama import Decoder
+    from test_gpu_decoder import tiny
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    prompt = torch.randint(0, 512, (6,), device="cuda", generator=torch.Generator(device="cuda").manual_seed(1))
+    sharded, _ = Decoder(tiny(), kind="r4", rank=rank, world=world).generate(prompt, 12, use_graph=True)
+    single, _ = Decoder(tiny(), kind="r4").generate(prompt, 12, use_graph=True)
+    with open(os.path.join(out_dir, f"ok{rank}"), "w") as f:
+        f.write("1" if torch.equal(sharded, single) else "0")
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_row_sharded_decoder_two_gpus(tmp_path):
+    """Row sharding keeps every output's summation order: greedy tokens equal the 1-GPU run."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    mp.spawn(_decoder_main, args=(2, port, str(tmp_path)), nprocs=2, join=True)
+    assert [(tmp_path / f"ok{r}").read_text() for r in range(2)] == ["1", "1"]
