@@ -385,6 +385,11 @@ def run_ours(args) -> dict | None:
         decode["r4_vs_bf16"] = round(decode["r4_tok_s"] / decode["bf16_tok_s"], 3)
         decode["tokens_equal_until"] = int((seqs["r4"] != seqs["bf16"]).to(torch.int64).cumsum(0).eq(0).sum().item())
         note(f"decode leg done: R4 {decode['r4_tok_s']} tok/s, BF16 {decode['bf16_tok_s']} tok/s")
+    # ---- the other two configurations, single GPU only (no collective in them)
+    prefill = moe_leg = None
+    if world == 1 and not args.quick:
+        prefill, moe_leg = prefill_leg(torch, dev, graph_us), moe_path_leg(torch, dev, graph_us)
+        note("prefill and MoE legs done")
     if rank != 0:
         return None
 
@@ -406,6 +411,8 @@ def run_ours(args) -> dict | None:
         "e2e": {"value": e2e_val, "unit": UNIT, "ms_per_step": e2e_ms, "h2d_bytes_per_step": sum(2 * k for k in k_list), "d2h_bytes_per_step": sum(2 * n for _, n, _ in SHAPES), "api": "R4Linear.__call__ on host-resident inputs, outputs copied back to pinned host memory"},
         "gpu_launches": launches,
         "decode": decode,
+        "prefill_gate_15360x3840": prefill,
+        "moe_128x(704x2816)": moe_leg,
         "clocks": clocks.summary(),
     }  # fmt: skip
     # ---- CPU baseline on a bounded sample (rank 0, single GPU runs only)
@@ -425,6 +432,49 @@ def run_ours(args) -> dict | None:
     else:
         result["cpu_baseline"] = None
     return result
+
+
+def prefill_leg(torch, dev, graph_us) -> dict:
+    """Fused decode products for short prompts on the gate projection (15360 x 3840): M rows of
+    N(0,1) inputs; 1..16 rows run the fused kernel (weights stream once), more rows rebuild the
+    BF16 weight and call cuBLAS; against cuBLAS on the pre-decoded weight."""
+    from binade_b200.cuda import kernels as ck
+    from binade_b200.cuda import r4
+
+    n, k = 15360, 3840
+    w = ck.to_device(synthetic_weight("gate", n, k)).view(torch.bfloat16)
+    m = r4.R4Linear(r4.from_dense(w))
+    out = {}
+    for M in (2, 8, 16, 32, 128, 2048):
+        x = torch.randn((M, k), device=dev, generator=torch.Generator(device=dev).manual_seed(M)).to(torch.bfloat16)
+        us = graph_us(lambda i: m(x), iters=10)
+        us_ref = graph_us(lambda i: torch.matmul(x, w.T), iters=10)
+        out[str(M)] = {"us": round(us, 1), "cublas_bf16_us": round(us_ref, 1), "vs_cublas": round(us_ref / us, 3), "path": "fused rows" if M <= r4.FUSED_MAX_ROWS else "rebuild + cuBLAS"}
+        if r4.FUSED_MAX_ROWS < M <= 16:
+            out[str(M)]["fused_rows_us"] = round(graph_us(lambda i: m.fused_rows(x), iters=10), 1)
+    return out
+
+
+def moe_path_leg(torch, dev, graph_us) -> dict:
+    """Expert path of a 26B-A4B-style layer: 128 experts, top-8 of uniform random logits, hidden
+    2816, expert FFN 704, token batches 1/8/64; fused gate+up gather, SwiGLU, down gather."""
+    from binade_b200.cuda import moe, r4
+
+    E, n, D = 128, 704, 2816
+    g = torch.Generator(device=dev).manual_seed(5)
+    gu = (torch.randn((E, 2 * n, D), device=dev, generator=g) * 0.02).to(torch.bfloat16)
+    dn = (torch.randn((E, D, n), device=dev, generator=g) * 0.02).to(torch.bfloat16)
+    layer = moe.R4SwitchGLU(r4.R4Linear(r4.from_dense(gu)), r4.R4Linear(r4.from_dense(dn)))
+    per_expert = (r4.r4_bytes(layer._gu._a) + r4.r4_bytes(layer._down._a)) / E
+    del gu, dn
+    out = {}
+    for B in (1, 8, 64):
+        x = torch.randn((B, D), device=dev, generator=g).to(torch.bfloat16)
+        idx = torch.topk(torch.softmax(torch.rand((B, E), device=dev, generator=g), dim=-1), 8, dim=-1).indices
+        us = graph_us(lambda i: layer(x, idx), iters=10)
+        active = int(torch.unique(idx).numel())
+        out[str(B)] = {"us": round(us, 1), "slots": B * 8, "active_experts": active, "gbs_of_slot_bytes": round(B * 8 * per_expert / us / 1e3, 1), "gbs_of_distinct_expert_bytes": round(active * per_expert / us / 1e3, 1)}
+    return out
 
 
 def main():

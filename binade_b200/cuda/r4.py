@@ -6,9 +6,10 @@ Same roles and names as the reference's binade/mlx/r4.py, on torch:
   R4Linear(a)         the linear-layer hook: y = x @ W.T with W decoded inside the kernel
   convert(model)      swap every BinadeLinear holder for an R4Linear in place (r4.py:375-410)
 
-Row counts: 1..16 input rows run the fused decode kernel (weights stream once, fp32 accumulation
-in the documented lane order); more rows rebuild the BF16 weight with the decode kernel and call
-torch.matmul, as the reference does for long prompts (r4.py:288).
+Row counts: 1..FUSED_MAX_ROWS input rows run the fused decode kernel (weights stream once, fp32
+accumulation in the documented lane order; `fused_rows` forces it up to 16 rows); more rows
+rebuild the BF16 weight with the decode kernel and call torch.matmul, as the reference does for
+long prompts (r4.py:288).
 """
 
 from __future__ import annotations
@@ -20,7 +21,7 @@ from torch import nn
 from ..format import TILE
 from . import kernels as ck
 
-FUSED_MAX_ROWS = 16  # input rows served by the fused decode kernel
+FUSED_MAX_ROWS = 2  # input rows served by the fused decode kernel; beyond, rebuilding BF16 and calling cuBLAS is faster on B200 (measured on 15360 x 3840: fused 52 / 148 / 252 us at 2 / 8 / 16 rows, rebuild 93 us)
 
 
 class BinadeLinear(nn.Module):
@@ -122,13 +123,18 @@ class _R4:
             return ck.r4_decode(self._a, self.N, self.K).reshape(self._a["shape"])
         return ck.r4_decode(self._a, self.N // rs * n, self.K, n, rs, r0)
 
+    def fused_rows(self, x: torch.Tensor) -> torch.Tensor:
+        """x [..., K] with 1..16 rows -> [..., N] through the fused decode kernel, every output in
+        the documented summation order (the same bits as the one-row kernel gives row by row)."""
+        M = x.numel() // self.K
+        return ck.r4_rows(self._a, x.reshape(M, self.K).contiguous(), self.N, self.K).reshape(*x.shape[:-1], self.N)
+
     def _rows(self, x: torch.Tensor) -> torch.Tensor:
-        lead = x.shape[:-1]
         M = x.numel() // self.K
         if M == 1:
             return self._matvec(x)
         if M <= FUSED_MAX_ROWS:
-            return ck.r4_rows(self._a, x.reshape(M, self.K).contiguous(), self.N, self.K).reshape(*lead, self.N)
+            return self.fused_rows(x)
         return x @ self.dense().reshape(self.N, self.K).T
 
 

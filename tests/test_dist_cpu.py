@@ -107,3 +107,37 @@ def test_row_sharded_linear_two_gloo_ranks(tmp_path, N):
     want = o.c_dense_rows(_weights((1, K), seed=4), _weights((N, K), seed=3))
     for rank in range(world):
         assert np.array_equal(np.load(tmp_path / f"y{rank}.npy"), want), rank
+
+
+def _ep_main(rank: int, world: int, port: int, out_dir: str):
+    import torch.distributed as dist
+
+    from binade_b200.cuda import moe
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    E, D, tokens, k = 8, 16, 5, 3
+    g = torch.Generator().manual_seed(9)
+    x = torch.randn((tokens, D), generator=g).to(torch.bfloat16)
+    idx = torch.stack([torch.randperm(E, generator=g)[:k] for _ in range(tokens)])
+    table = torch.randn((E, D), generator=torch.Generator().manual_seed(3)).to(torch.bfloat16)  # a toy "expert": y = x * table[e]
+
+    def local_slots(xf, xi, ei_local):  # stands for R4SwitchGLU.slots over this rank's experts
+        return xf[xi.long()] * table[ei_local.long() + rank * (E // world)]
+
+    y = moe.ExpertParallelGLU(local_slots, E, D, rank, world)(x, idx)
+    torch.save(y, os.path.join(out_dir, f"y{rank}.pt"))
+    dist.destroy_process_group()
+
+
+def test_expert_parallel_two_gloo_ranks(tmp_path):
+    """Every slot is computed by the rank owning its expert and reaches every rank in place."""
+    mp.spawn(_ep_main, args=(2, _free_port(), str(tmp_path)), nprocs=2, join=True)
+    E, D, tokens, k = 8, 16, 5, 3
+    g = torch.Generator().manual_seed(9)
+    x = torch.randn((tokens, D), generator=g).to(torch.bfloat16)
+    idx = torch.stack([torch.randperm(E, generator=g)[:k] for _ in range(tokens)])
+    table = torch.randn((E, D), generator=torch.Generator().manual_seed(3)).to(torch.bfloat16)
+    want = x[:, None, :] * table[idx]
+    for r in range(2):
+        assert torch.equal(torch.load(tmp_path / f"y{r}.pt"), want), r

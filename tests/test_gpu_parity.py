@@ -260,7 +260,7 @@ def test_order_sensitive_rows(N, K):
     W = dev(u).view(torch.bfloat16)
     for M in (1, 2, 3, 8, 15, 16):
         x = torch.ones((M, K), dtype=torch.bfloat16, device="cuda")
-        got = m(x)
+        got = m.fused_rows(x)
         assert np.array_equal(words(got), words(torch_same_order(x, W))), M
         assert np.array_equal(words(got), o.c_dense_rows(words(x), u)), M
     y = words(m(torch.ones((1, K), dtype=torch.bfloat16, device="cuda")))[0]
@@ -278,7 +278,7 @@ def test_small_m_rows(M):
     u = weights(rng, (N, K))
     xw = bf16_words(rng.standard_normal((M, K)))
     m = r4.R4Linear(r4.transcode(packed_arrays(u)))
-    got = m(dev(xw).view(torch.bfloat16).reshape(1, M, K))
+    got = m.fused_rows(dev(xw).view(torch.bfloat16).reshape(1, M, K))
     assert got.shape == (1, M, N)
     assert np.array_equal(words(got)[0], o.c_dense_rows(xw, u))
 
@@ -367,3 +367,28 @@ def test_zz_device_status_is_clean():
     st = ctypes.c_int(-1)
     _native.call("cuda", "bn_device_status", ctypes.byref(st))
     assert st.value == 0
+
+
+def test_switch_glu_matches_oracle():
+    """MoE decode step: fused gate/up gather, SwiGLU, down gather, against the oracle's products."""
+    from binade_b200.cuda import moe, r4
+
+    E, n, D, tokens, k = 8, 96, 256, 3, 4
+    rng = np.random.default_rng(21)
+    gu, dn = weights(rng, (E, 2 * n, D)), weights(rng, (E, D, n), escapes=False)
+    gu.reshape(-1)[::997] = 0x3C00  # keep gate/up finite: no Inf patterns in this test
+    gu.reshape(-1)[5::199] = 0x5F80
+    m = moe.R4SwitchGLU(r4.R4Linear(r4.transcode(packed_arrays(gu))), r4.R4Linear(r4.transcode(packed_arrays(dn))))
+    assert (m.E, m.n, m.D) == (E, n, D)
+    xw = bf16_words(rng.standard_normal((tokens, D)) * 0.1)
+    idx = np.stack([rng.choice(E, size=k, replace=False) for _ in range(tokens)]).astype(np.int64)
+    y = m(dev(xw).view(torch.bfloat16), torch.from_numpy(idx).cuda())
+    assert y.shape == (tokens, k, D)
+    a_gu, a_dn = o.pack_r4(gu.reshape(E * 2 * n, D)), o.pack_r4(dn.reshape(E * D, n))
+    ei = idx.reshape(-1).astype(np.uint32)
+    xi = (np.arange(ei.size) // k).astype(np.uint32)
+    both = o.c_r4_gather(a_gu, xw, xi, ei, 2 * n, D, 2 * n)
+    gate, up = torch.from_numpy(both[:, :n].view(np.int16).copy()).view(torch.bfloat16), torch.from_numpy(both[:, n:].view(np.int16).copy()).view(torch.bfloat16)
+    h = words(moe.swiglu(up, gate))
+    want = o.c_r4_gather(a_dn, h, np.arange(ei.size, dtype=np.uint32), ei, D, n, D)
+    assert np.array_equal(words(y).reshape(-1, D), want)
