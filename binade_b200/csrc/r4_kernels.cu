@@ -341,6 +341,10 @@ extern "C" int bn_r4_gather(const uint16_t *x, const bn_r4 *w, const uint32_t *x
   if (K % 4) return fail(BN_ERR_ARG, "R4 needs K % 4 == 0");
   if (G == 0 || n == 0) return BN_OK;
   if (G > 65535) return fail(BN_ERR_ARG, "bn_r4_gather: more than 65535 slots");
+  {
+    const int e = stream_gather(w, x, xi, ei, G, n, K, RS, R0, split, y, y2, (cudaStream_t)stream);
+    if (e >= 0) return e;
+  }
   RowsArgs a{};
   a.w = *w, a.x = x, a.x_stride = K, a.xi = xi, a.ei = ei, a.n = n, a.K = K, a.T = (int)tiles(K);
   a.RS = RS, a.R0 = R0, a.split = split, a.y = y, a.y2 = y2, a.m = 1;

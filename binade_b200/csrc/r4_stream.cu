@@ -98,6 +98,11 @@ struct StreamArgs {
   int T;
   int stages;     // ring depth per warp
   uint32_t smem;  // dynamic shared memory of the launch, bytes
+  // expert gather (blockIdx.y = slot g): rows ei[g] * RS + R0 .. + N, input row xi[g]; outputs
+  // y [G, N], or with 0 < split < N: y [G, split] and y2 [G, N - split]. ei == nullptr: plain.
+  const uint32_t *xi, *ei;
+  int64_t RS, R0, split;
+  uint16_t *y2;
 };
 
 // Escapes of one flagged lane word, in weight order across the warp: exponent bits of its
@@ -239,8 +244,11 @@ __global__ void __launch_bounds__(WARPS * 32, 1) r4_stream_kernel(StreamArgs a) 
 
   // this warp's rows: nfull groups of RW rows, then the remaining rows one per group
   const int64_t workers = (int64_t)gridDim.x * WARPS, me = (int64_t)blockIdx.x * WARPS + warp;
-  const int64_t r_begin = a.N * me / workers, r_end = a.N * (me + 1) / workers;
-  const int nrows = (int)(r_end - r_begin);
+  const int64_t o_begin = a.N * me / workers, o_end = a.N * (me + 1) / workers;  // output rows of this warp
+  const int64_t slot = blockIdx.y;
+  const int64_t row0 = a.ei ? (int64_t)a.ei[slot] * a.RS + a.R0 : 0;  // storage row of output row 0
+  const int64_t r_begin = row0 + o_begin;
+  const int nrows = (int)(o_end - o_begin);
   const int nfull = nrows / RW, ngroups = nfull + (nrows - nfull * RW);
   const int nchunks = (T + KC - 1) / KC, last_chunk = nchunks - 1;
   const int nt_last = T - last_chunk * KC;  // tiles of a row's last stage
@@ -284,7 +292,7 @@ __global__ void __launch_bounds__(WARPS * 32, 1) r4_stream_kernel(StreamArgs a) 
 
   // while the first stages fly: x and the pair table into shared memory (whole block)
   {
-    const uint4 *x8 = reinterpret_cast<const uint4 *>(a.x);
+    const uint4 *x8 = reinterpret_cast<const uint4 *>(a.x + (a.ei ? (int64_t)a.xi[slot] * K : 0));
     uint4 *dst = reinterpret_cast<uint4 *>(smem_raw + (x_at - base));
     for (int i = threadIdx.x; i < T * 16; i += THREADS) dst[i] = (int64_t)i * 8 < K ? __ldg(x8 + i) : make_uint4(0, 0, 0, 0);  // K % 16 == 0
     uint32_t *lut = reinterpret_cast<uint32_t *>(smem_raw + (65536u - base));
@@ -376,7 +384,12 @@ __global__ void __launch_bounds__(WARPS * 32, 1) r4_stream_kernel(StreamArgs a) 
       for (int o = 16; o >= 1; o >>= 1) s = s + __shfl_xor_sync(BN_FULL, s, o);
       if ((int)lane == i) mine = s;
     }
-    if ((int)lane < (wide ? RW : 1)) a.y[row + lane] = f32_to_bf16_bits(mine);
+    if ((int)lane < (wide ? RW : 1)) {
+      const int64_t r = row - row0 + lane;  // output row within the slot
+      const uint16_t v = f32_to_bf16_bits(mine);
+      if (a.split > 0 && r >= a.split) a.y2[slot * (a.N - a.split) + (r - a.split)] = v;
+      else a.y[slot * (a.split > 0 ? a.split : a.N) + r] = v;
+    }
   }
 }
 
@@ -408,7 +421,7 @@ static int stream_stages(int warps, uint32_t stage, int T, uint32_t base) {
 }
 
 template <int WARPS, int RW, int KC>
-static int launch_stream(StreamArgs a, cudaStream_t s) {
+static int launch_stream(StreamArgs a, cudaStream_t s, int64_t slots = 1) {
   // worst case of the two extremes of the window's start; the kernel re-derives the layout
   // from the real start and refuses to run if it does not fit
   const int stages = min(stream_stages(WARPS, RW * KC * 192, a.T, 0), stream_stages(WARPS, RW * KC * 192, a.T, ST_BASE_MAX));
@@ -417,10 +430,10 @@ static int launch_stream(StreamArgs a, cudaStream_t s) {
   a.smem = ST_SMEM_MAX;
   auto kern = r4_stream_kernel<WARPS, RW, KC>;
   BN_CUDA(allow_smem(kern, a.smem));
-  int64_t blocks = stream_sms();
+  int64_t blocks = (stream_sms() + slots - 1) / slots;  // blocks per slot: about one block per SM in all
   const int64_t need = (a.N + WARPS - 1) / WARPS;
   if (blocks > need) blocks = need;
-  kern<<<(unsigned)blocks, WARPS * 32, a.smem, s>>>(a);
+  kern<<<dim3((unsigned)blocks, (unsigned)slots), WARPS * 32, a.smem, s>>>(a);
   return launched("r4_stream_kernel");
 }
 
@@ -436,6 +449,20 @@ int stream_matvec(const bn_r4 *w, const uint16_t *x, int64_t N, int64_t K, uint1
   if (e == -1) e = launch_stream<20, 2, 8>(a, s);
   if (e == -1) e = launch_stream<16, 2, 8>(a, s);
   if (e == -1) e = launch_stream<8, 2, 8>(a, s);
+  return e;
+}
+
+// Expert gather through the streaming kernel; -1 when the shape is outside its coverage.
+int stream_gather(const bn_r4 *w, const uint16_t *x, const uint32_t *xi, const uint32_t *ei, int64_t G, int64_t n, int64_t K, int64_t RS, int64_t R0, int64_t split, uint16_t *y, uint16_t *y2, cudaStream_t s) {
+  const int64_t T = tiles(K);
+  if (K % 16 || n < 1 || T > 200 || G < 1 || G > 65535) return -1;
+  StreamArgs a{};
+  a.w = *w, a.x = x, a.y = y, a.y2 = y2, a.N = n, a.K = K, a.T = (int)T;
+  a.xi = xi, a.ei = ei, a.RS = RS, a.R0 = R0, a.split = split;
+  int e = launch_stream<24, 2, 8>(a, s, G);
+  if (e == -1) e = launch_stream<20, 2, 8>(a, s, G);
+  if (e == -1) e = launch_stream<16, 2, 8>(a, s, G);
+  if (e == -1) e = launch_stream<8, 2, 8>(a, s, G);
   return e;
 }
 
