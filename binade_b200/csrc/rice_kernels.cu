@@ -45,13 +45,39 @@ __device__ __forceinline__ uint32_t read_bits(const uint32_t *__restrict__ bits,
   return n >= 32u ? v : v & ((1u << n) - 1u);
 }
 
+// The same on a row: `row` points at the row's first word, `pos` counts bits from there, and
+// `avail` words may be read (all 32-bit arithmetic: a row's stream is far below 2^32 bits).
+__device__ __forceinline__ uint32_t row_bits(const uint32_t *__restrict__ row, uint32_t avail, uint32_t pos, uint32_t n) {
+  const uint32_t w = pos >> 5, s = pos & 31u;
+  uint32_t lo = w < avail ? __ldg(row + w) : 0u;
+  uint32_t hi = (s + n > 32u && w + 1 < avail) ? __ldg(row + w + 1) : 0u;
+  uint32_t v = __funnelshift_r(lo, hi, s);
+  return n >= 32u ? v : v & ((1u << n) - 1u);
+}
+
+// Exclusive prefix over lanes and warp total of a per-lane count in 0..7: three ballots for the
+// prefix, one warp reduction for the total. All 32 lanes must call.
+__device__ __forceinline__ void warp_scan_count(uint32_t cnt, uint32_t lt, uint32_t &pre, uint32_t &tot) {
+  const uint32_t b0 = __ballot_sync(BN_FULL, cnt & 1u), b1 = __ballot_sync(BN_FULL, cnt & 2u), b2 = __ballot_sync(BN_FULL, cnt & 4u);
+  pre = __popc(b0 & lt) + 2 * __popc(b1 & lt) + 4 * __popc(b2 & lt);
+  tot = __reduce_add_sync(BN_FULL, cnt);
+}
+
 constexpr int RICE_THREADS = 256;
 
 template <int MODE>
 __global__ void __launch_bounds__(RICE_THREADS) rice_kernel(RiceArgs a) {
   __shared__ uint8_t tbl[256];
-  if (MODE != RICE_RANKS) {
-    if (threadIdx.x < 256) tbl[threadIdx.x] = a.table[threadIdx.x];
+  // deposit table: entry alive | bits << 4 spreads the low bits of `bits`, in order, over the
+  // set positions of the 4-bit mask `alive` (a 4-bit pdep)
+  __shared__ uint8_t deposit[256];
+  {
+    const uint32_t al = threadIdx.x & 15u;
+    uint32_t b = threadIdx.x >> 4, out = 0;
+    for (int i = 0; i < 4; i++)
+      if ((al >> i) & 1u) out |= (b & 1u) << i, b >>= 1;
+    deposit[threadIdx.x] = (uint8_t)out;
+    if (MODE != RICE_RANKS) tbl[threadIdx.x] = a.table[threadIdx.x];
     __syncthreads();
   }
   const uint32_t lane = lane_id(), lt = lanemask_lt();
@@ -66,7 +92,9 @@ __global__ void __launch_bounds__(RICE_THREADS) rice_kernel(RiceArgs a) {
       const uint64_t p = (uint64_t)w0 + lane * 32u;
       if (p < w_end && p < a.nwords) asm volatile("prefetch.global.L1 [%0];" ::"l"(a.bits + p));
     }
-    uint64_t cur = (uint64_t)w0 * 32u;
+    const uint32_t *row_words = a.bits + w0;
+    const uint32_t avail = (uint64_t)w0 < a.nwords ? (uint32_t)min(a.nwords - w0, (uint64_t)0xFFFFFFFFu) : 0u;
+    uint32_t cur = 0;  // bits from the row's first word
     uint32_t row_escapes = 0;
     uint64_t esc_base = 0;
     bool esc_room = false;
@@ -76,7 +104,7 @@ __global__ void __launch_bounds__(RICE_THREADS) rice_kernel(RiceArgs a) {
       uint32_t bound = 0;
       for (int t = lane; t < T; t += 32) {
         const uint32_t m = a.meta[row * T + t], k = m & 3u, qmax = m >> 2;
-        if (((qmax << k) | ((1u << k) - 1u)) >= 15u) bound += (uint32_t)min((int64_t)BN_TILE, K - (int64_t)t * BN_TILE);
+        if (((qmax << k) | ((1u << k) - 1u)) >= 15u) bound += (uint32_t)min(BN_TILE, (int)K - t * BN_TILE);
       }
 #pragma unroll
       for (int o = 16; o >= 1; o >>= 1) bound += __shfl_xor_sync(BN_FULL, bound, o);
@@ -95,17 +123,17 @@ __global__ void __launch_bounds__(RICE_THREADS) rice_kernel(RiceArgs a) {
         const int t = t0 + u;
         const uint32_t m = __shfl_sync(BN_FULL, my_meta, u);
         const uint32_t k = m & 3u, qmax = m >> 2;
-        const int n = (int)min((int64_t)BN_TILE, K - (int64_t)t * BN_TILE);
+        const int n = min(BN_TILE, (int)K - t * BN_TILE);
         const uint32_t nv = (uint32_t)max(0, min(4, n - (int)lane * 4));
         uint32_t lo = 0;
-        if (nv * k) lo = read_bits(a.bits, a.nwords, cur + lane * 4u * k, nv * k);
-        cur += (uint64_t)n * k;
+        if (nv * k) lo = row_bits(row_words, avail, cur + lane * 4u * k, nv * k);
+        cur += (uint32_t)n * k;
         uint32_t q4 = 0;  // one byte per weight
         uint32_t alive = (1u << nv) - 1u;
         for (uint32_t j = 0; j < qmax; j++) {
           const uint32_t c = __popc(alive);
           uint32_t pre, tot;
-          warp_scan_small(c, lt, pre, tot);
+          warp_scan_count(c, lt, pre, tot);
           if (tot == 0) break;  // only a corrupt stream: the remaining planes are empty
           if (tot == 1) {
             // one weight left: its remaining planes are a run of ones closed by a zero (or by
@@ -116,7 +144,7 @@ __global__ void __launch_bounds__(RICE_THREADS) rice_kernel(RiceArgs a) {
               uint32_t ones = 0;
               for (uint32_t done = 0; done < rem; done += 32) {
                 const uint32_t take = min(32u, rem - done);
-                const uint32_t b = read_bits(a.bits, a.nwords, cur + done, take);
+                const uint32_t b = row_bits(row_words, avail, cur + done, take);
                 const uint32_t run = __ffs(~b) - 1;  // 32 when b is all ones (ffs(0) = 0 wraps)
                 if (run < take) { ones += run; break; }
                 ones += take;
@@ -128,18 +156,9 @@ __global__ void __launch_bounds__(RICE_THREADS) rice_kernel(RiceArgs a) {
             cur += __shfl_sync(BN_FULL, used, owner);
             break;
           }
-          uint32_t b = c ? read_bits(a.bits, a.nwords, cur + pre, c) : 0u;
-          uint32_t na = 0;
-#pragma unroll
-          for (int i = 0; i < 4; i++) {
-            if ((alive >> i) & 1u) {
-              const uint32_t v = b & 1u;
-              b >>= 1;
-              q4 += v << (8 * i);
-              na |= v << i;
-            }
-          }
-          alive = na;
+          const uint32_t b = c ? row_bits(row_words, avail, cur + pre, c) : 0u;
+          alive = deposit[alive | (b << 4)];             // the plane's bits at the alive positions
+          q4 += (alive * 0x00204081u) & 0x01010101u;     // bit i -> byte i: one more for the survivors
           cur += tot;
         }
         // ranks of the lane's four weights, one per byte: q << k | low bits
@@ -196,7 +215,7 @@ __global__ void __launch_bounds__(RICE_THREADS) rice_kernel(RiceArgs a) {
       if (MODE == RICE_R4 && t0 + (int)lane < T) a.flags[row * T + t0 + lane] = (uint8_t)my_flag;
     }
     if (lane == 0) {
-      const uint32_t rend = (uint32_t)((cur + 31u) >> 5);
+      const uint32_t rend = w0 + ((cur + 31u) >> 5);
       if (MODE == RICE_R4) {
         a.row_cnt[row] = row_escapes;
         if (row_escapes) atomicAdd(a.counters + 2, row_escapes);
