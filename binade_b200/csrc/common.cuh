@@ -33,6 +33,10 @@ int stream_matvec(const bn_r4 *w, const uint16_t *x, int64_t N, int64_t K, uint1
 
 int stream_gather(const bn_r4 *w, const uint16_t *x, const uint32_t *xi, const uint32_t *ei, int64_t G, int64_t n, int64_t K, int64_t RS, int64_t R0, int64_t split, uint16_t *y, uint16_t *y2, cudaStream_t s);
 
+// Register-pipelined batch-1 matvec and expert gather (r4_direct.cu); -1 outside their coverage.
+int direct_matvec(const bn_r4 *w, const uint16_t *x, int64_t N, int64_t K, uint16_t *y, cudaStream_t s);
+int direct_gather(const bn_r4 *w, const uint16_t *x, const uint32_t *xi, const uint32_t *ei, int64_t G, int64_t n, int64_t K, int64_t RS, int64_t R0, int64_t split, uint16_t *y, uint16_t *y2, cudaStream_t s);
+
 inline int64_t tiles(int64_t K) { return (K + BN_TILE - 1) / BN_TILE; }
 
 // Raises a kernel's dynamic shared memory limit once per (kernel, device).

@@ -323,8 +323,12 @@ extern "C" int bn_r4_rows(const uint16_t *x, int64_t x_stride, const bn_r4 *w, i
   a.m = (int)M;
   // the instantiation is the next power of two >= M: absent input rows are zeros in shared
   // memory and are never stored, so the weights stream once whatever M
-  if (M == 1 && x_stride >= 0) {
-    const int e = stream_matvec(w, x, N, K, y, s);
+  if (M == 1) {
+    // long rows: the register-pipelined kernel (its x and table leave no room for deep rings
+    // anyway); otherwise the streaming kernel, which needs K % 16 == 0; then whichever is left
+    int e = K >= 8192 ? direct_matvec(w, x, N, K, y, s) : -1;
+    if (e == -1) e = stream_matvec(w, x, N, K, y, s);
+    if (e == -1) e = direct_matvec(w, x, N, K, y, s);
     if (e >= 0) return e;
   }
   if (M == 1) return N >= 8192 ? launch_rows<1, 2, false>(a, 1, s) : launch_rows<1, 1, false>(a, 1, s);
@@ -342,7 +346,8 @@ extern "C" int bn_r4_gather(const uint16_t *x, const bn_r4 *w, const uint32_t *x
   if (G == 0 || n == 0) return BN_OK;
   if (G > 65535) return fail(BN_ERR_ARG, "bn_r4_gather: more than 65535 slots");
   {
-    const int e = stream_gather(w, x, xi, ei, G, n, K, RS, R0, split, y, y2, (cudaStream_t)stream);
+    int e = stream_gather(w, x, xi, ei, G, n, K, RS, R0, split, y, y2, (cudaStream_t)stream);
+    if (e == -1) e = direct_gather(w, x, xi, ei, G, n, K, RS, R0, split, y, y2, (cudaStream_t)stream);
     if (e >= 0) return e;
   }
   RowsArgs a{};
