@@ -332,6 +332,10 @@ extern "C" int bn_r4_rows(const uint16_t *x, int64_t x_stride, const bn_r4 *w, i
     if (e >= 0) return e;
   }
   if (M == 1) return N >= 8192 ? launch_rows<1, 2, false>(a, 1, s) : launch_rows<1, 1, false>(a, 1, s);
+  if (M <= 8) {
+    const int e = stream_rows(w, x, x_stride, M, N, K, y, y_stride, s);
+    if (e >= 0) return e;
+  }
   if (M == 2) return launch_rows<2, 2, false>(a, 1, s);
   if (M <= 4) return launch_rows<4, 2, false>(a, 1, s);
   if (M <= 8) return launch_rows<8, 2, false>(a, 1, s);

@@ -96,7 +96,9 @@ struct StreamArgs {
   uint16_t *y;
   int64_t N, K;
   int T;
-  int stages;     // ring depth per warp
+  int m;                       // input rows really present (<= M of the instantiation)
+  int64_t x_stride, y_stride;  // elements between input rows / output rows (m > 1)
+  int stages;                  // ring depth per warp
   uint32_t smem;  // dynamic shared memory of the launch, bytes
   // expert gather (blockIdx.y = slot g): rows ei[g] * RS + R0 .. + N, input row xi[g]; outputs
   // y [G, N], or with 0 < split < N: y [G, split] and y2 [G, N - split]. ei == nullptr: plain.
@@ -104,6 +106,28 @@ struct StreamArgs {
   int64_t RS, R0, split;
   uint16_t *y2;
 };
+
+// Where everything sits in the shared window, by absolute shared address (base = start of the
+// dynamic allocation): [base, 64K) and [128K, end) hold x, the mbarriers and the per-warp rings,
+// [64K, 128K) the pair table. One input row: x below the table; several: x above it.
+struct StreamLayout {
+  uint32_t x_at, bar_at, pool_a, pool_c, in_a, end;
+};
+__host__ __device__ inline StreamLayout stream_layout(uint32_t base, int T, int M, int warps, int S, uint32_t stage) {
+  StreamLayout L;
+  const uint32_t a0 = (base + 15u) & ~15u, xbytes = (uint32_t)M * (uint32_t)T * 256u, ring = (uint32_t)S * stage;
+  if (M == 1) {
+    L.x_at = a0, L.bar_at = a0 + xbytes, L.pool_c = 131072u;
+  } else {
+    L.bar_at = a0, L.x_at = 131072u, L.pool_c = (131072u + xbytes + 127u) & ~127u;
+  }
+  L.pool_a = (L.bar_at + (uint32_t)warps * S * 8u + 127u) & ~127u;
+  L.in_a = L.pool_a < 65536u ? (65536u - L.pool_a) / ring : 0u;  // warps whose rings sit below the table
+  if (L.in_a > (uint32_t)warps) L.in_a = warps;
+  L.end = L.pool_c + ((uint32_t)warps - L.in_a) * ring;
+  if (L.pool_a > 65536u) L.end = 0xFFFFFFFFu;  // x or the barriers would run into the table
+  return L;
+}
 
 // Escapes of one flagged lane word, in weight order across the warp: exponent bits of its
 // code-15 weights are OR-ed into the two BF16x2 words from the row's escape cursor, which then
@@ -138,56 +162,70 @@ __device__ __forceinline__ void escape_patch(uint32_t c, const uint8_t *__restri
   }
 }
 
-// Decode + accumulate of lane word (row I, tile U) of a block, all offsets immediate.
-template <int I, int U, uint32_t RAW_ROW, uint32_t CODE_ROW>
-__device__ __forceinline__ float word_fma(uint32_t raw, uint32_t codes, uint32_t lut, uint32_t token, uint2 xv, float acc) {
+// The M input rows' four BF16 values of one tile for this lane: row m sits `xrow` bytes after
+// row m-1 in shared memory.
+template <int M, int OFF>
+__device__ __forceinline__ void x_tile(uint32_t xs, uint32_t xrow, uint32_t token, uint2 (&xv)[M]) {
+#pragma unroll
+  for (int m = 0; m < M; m++) xv[m] = x_read<OFF>(xs + m * xrow, token);
+}
+
+// Decode of lane word (row I, tile U) of a block, all offsets immediate, and its M products.
+template <int I, int U, int M, uint32_t RAW_ROW, uint32_t CODE_ROW>
+__device__ __forceinline__ void word_fma(uint32_t raw, uint32_t codes, uint32_t lut, uint32_t token, const uint2 (&xv)[M], float (&acc)[M]) {
   const uint32_t r4 = ring_u32<I * RAW_ROW + U * 128>(raw, token);
   const uint32_t c4 = ring_u16<I * CODE_ROW + U * 64>(codes, token);
   const uint32_t e01 = lut_read(__byte_perm(c4, lut, 0x7604), token);  // lut + code byte 0 * 256
   const uint32_t e23 = lut_read(__byte_perm(c4, lut, 0x7614), token);  // lut + code byte 1 * 256
   const uint32_t w01 = (__byte_perm(r4, 0u, 0x1100) & 0x807F807Fu) | e01;
   const uint32_t w23 = (__byte_perm(r4, 0u, 0x3322) & 0x807F807Fu) | e23;
-  return fma2_bf16(w23, xv.y, fma2_bf16(w01, xv.x, acc));
+#pragma unroll
+  for (int m = 0; m < M; m++) acc[m] = fma2_bf16(w23, xv[m].y, fma2_bf16(w01, xv[m].x, acc[m]));
 }
 
 // NT tiles x RWG rows, straight-line: no loop, no test, every offset an immediate.
-template <int RWG, int NT, uint32_t RAW_ROW, uint32_t CODE_ROW, int U = 0>
-__device__ __forceinline__ void block_fma(uint32_t raw, uint32_t codes, uint32_t xs, uint32_t lut, uint32_t token, float (&acc)[RWG]) {
+template <int RWG, int NT, int M, uint32_t RAW_ROW, uint32_t CODE_ROW, int U = 0>
+__device__ __forceinline__ void block_fma(uint32_t raw, uint32_t codes, uint32_t xs, uint32_t xrow, uint32_t lut, uint32_t token, float (&acc)[RWG][M]) {
   if constexpr (U < NT) {
-    const uint2 xv = x_read<U * 256>(xs, token);
-    acc[0] = word_fma<0, U, RAW_ROW, CODE_ROW>(raw, codes, lut, token, xv, acc[0]);
-    if constexpr (RWG > 1) acc[1] = word_fma<1, U, RAW_ROW, CODE_ROW>(raw, codes, lut, token, xv, acc[1]);
-    if constexpr (RWG > 2) acc[2] = word_fma<2, U, RAW_ROW, CODE_ROW>(raw, codes, lut, token, xv, acc[2]);
-    if constexpr (RWG > 3) acc[3] = word_fma<3, U, RAW_ROW, CODE_ROW>(raw, codes, lut, token, xv, acc[3]);
-    block_fma<RWG, NT, RAW_ROW, CODE_ROW, U + 1>(raw, codes, xs, lut, token, acc);
+    uint2 xv[M];
+    x_tile<M, U * 256>(xs, xrow, token, xv);
+    word_fma<0, U, M, RAW_ROW, CODE_ROW>(raw, codes, lut, token, xv, acc[0]);
+    if constexpr (RWG > 1) word_fma<1, U, M, RAW_ROW, CODE_ROW>(raw, codes, lut, token, xv, acc[1]);
+    if constexpr (RWG > 2) word_fma<2, U, M, RAW_ROW, CODE_ROW>(raw, codes, lut, token, xv, acc[2]);
+    if constexpr (RWG > 3) word_fma<3, U, M, RAW_ROW, CODE_ROW>(raw, codes, lut, token, xv, acc[3]);
+    block_fma<RWG, NT, M, RAW_ROW, CODE_ROW, U + 1>(raw, codes, xs, xrow, lut, token, acc);
   }
 }
 
 // One tile of RWG rows with every check: escapes where fbits says so, lanes outside a partial
 // tile masked. `u`: the tile's bit in fbits.
-template <int RWG, uint32_t RAW_ROW, uint32_t CODE_ROW, int I = 0>
-__device__ __forceinline__ void careful_tile(uint32_t raw, uint32_t codes, uint32_t lut, uint32_t token, uint2 xv, int u, bool in, const uint32_t (&fbits)[RWG], const uint8_t *__restrict__ esc, uint32_t (&epos)[RWG], float (&acc)[RWG]) {
+template <int RWG, int M, uint32_t RAW_ROW, uint32_t CODE_ROW, int I = 0>
+__device__ __forceinline__ void careful_tile(uint32_t raw, uint32_t codes, uint32_t lut, uint32_t token, const uint2 (&xv)[M], int u, bool in, const uint32_t (&fbits)[RWG], const uint8_t *__restrict__ esc, uint32_t (&epos)[RWG], float (&acc)[RWG][M]) {
   if constexpr (I < RWG) {
     const uint32_t r4 = ring_u32<I * RAW_ROW>(raw, token);
     const uint32_t c4 = ring_u16<I * CODE_ROW>(codes, token);
     uint32_t w01 = (__byte_perm(r4, 0u, 0x1100) & 0x807F807Fu) | lut_read(__byte_perm(c4, lut, 0x7604), token);
     uint32_t w23 = (__byte_perm(r4, 0u, 0x3322) & 0x807F807Fu) | lut_read(__byte_perm(c4, lut, 0x7614), token);
     if ((fbits[I] >> u) & 1u) escape_patch(c4, esc, epos[I], w01, w23);
-    const float s = fma2_bf16(w23, xv.y, fma2_bf16(w01, xv.x, acc[I]));
-    acc[I] = in ? s : acc[I];
-    careful_tile<RWG, RAW_ROW, CODE_ROW, I + 1>(raw, codes, lut, token, xv, u, in, fbits, esc, epos, acc);
+#pragma unroll
+    for (int m = 0; m < M; m++) {
+      const float s = fma2_bf16(w23, xv[m].y, fma2_bf16(w01, xv[m].x, acc[I][m]));
+      acc[I][m] = in ? s : acc[I][m];
+    }
+    careful_tile<RWG, M, RAW_ROW, CODE_ROW, I + 1>(raw, codes, lut, token, xv, u, in, fbits, esc, epos, acc);
   }
 }
 
-// One stage (nt tiles) of RWG rows, in blocks of BT tiles. A full block without a flagged tile
-// (and not holding a row's partial last tile) runs as one straight line of code: no loop, no test,
-// every offset an immediate. Any other block goes tile by tile with every check.
+// One stage (nt tiles) of RWG rows against M input rows, in blocks of BT tiles. A full block
+// without a flagged tile (and not holding a row's partial last tile) runs as one straight line of
+// code: no loop, no test, every offset an immediate. Any other block goes tile by tile with every
+// check.
 //   fbits[i]  bit u: tile u of row i holds escapes
 //   partial   the stage's last tile is a row's partial last tile; lanes without
 //             `lane_in_partial` hold no weight in it
-template <int RWG, int KC, uint32_t RAW_ROW, uint32_t CODE_ROW>
-__device__ __forceinline__ void consume_stage(uint32_t raw, uint32_t codes, uint32_t xs, uint32_t lut, uint32_t token, int nt, bool partial, bool lane_in_partial, const uint32_t (&fbits)[RWG], const uint8_t *__restrict__ esc, uint32_t (&epos)[RWG], float (&acc)[RWG]) {
-  constexpr int BT = KC < 4 ? KC : (RWG >= 4 ? 2 : 4);
+template <int RWG, int KC, int M, uint32_t RAW_ROW, uint32_t CODE_ROW>
+__device__ __forceinline__ void consume_stage(uint32_t raw, uint32_t codes, uint32_t xs, uint32_t xrow, uint32_t lut, uint32_t token, int nt, bool partial, bool lane_in_partial, const uint32_t (&fbits)[RWG], const uint8_t *__restrict__ esc, uint32_t (&epos)[RWG], float (&acc)[RWG][M]) {
+  constexpr int BT = KC < 4 ? KC : (RWG * M >= 4 ? 2 : 4);
   constexpr int NB = (KC + BT - 1) / BT;
   uint32_t any = 0;
 #pragma unroll
@@ -199,12 +237,14 @@ __device__ __forceinline__ void consume_stage(uint32_t raw, uint32_t codes, uint
     const uint32_t braw = raw + b * BT * 128, bcodes = codes + b * BT * 64, bxs = xs + b * BT * 256;
     const bool tail = partial && left <= BT;  // this block holds the partial tile
     if (left >= BT && !tail && !((any >> (b * BT)) & ((1u << BT) - 1u))) {
-      block_fma<RWG, BT, RAW_ROW, CODE_ROW>(braw, bcodes, bxs, lut, token, acc);
+      block_fma<RWG, BT, M, RAW_ROW, CODE_ROW>(braw, bcodes, bxs, xrow, lut, token, acc);
     } else {
       const int n = left < BT ? left : BT;
       for (int k = 0; k < n; k++) {
         const bool in = lane_in_partial || !(tail && k == n - 1);
-        careful_tile<RWG, RAW_ROW, CODE_ROW>(braw + k * 128, bcodes + k * 64, lut, token, x_read<0>(bxs + k * 256, token), b * BT + k, in, fbits, esc, epos, acc);
+        uint2 xv[M];
+        x_tile<M, 0>(bxs + k * 256, xrow, token, xv);
+        careful_tile<RWG, M, RAW_ROW, CODE_ROW>(braw + k * 128, bcodes + k * 64, lut, token, xv, b * BT + k, in, fbits, esc, epos, acc);
       }
     }
   }
@@ -214,10 +254,11 @@ __device__ __forceinline__ void consume_stage(uint32_t raw, uint32_t codes, uint
 // rows % RW rows are walked one at a time); KC: tiles per stage.
 //
 // Shared window, by absolute shared address (base = start of the dynamic allocation):
-//   [base, 64K)    x as BF16 [T*128] | mbarriers | rings of the first warps
+//   [base, 64K)    (x as BF16 [T*128] when M == 1) | mbarriers | rings of the first warps
 //   [64K, 128K)    pair table
-//   [128K, end)    rings of the remaining warps
-template <int WARPS, int RW, int KC>
+//   [128K, end)    (x [M][T*128] when M > 1) | rings of the remaining warps
+// M: input rows multiplied in one pass (accumulators per weight row); rows >= a.m are zeros.
+template <int WARPS, int RW, int KC, int M>
 __global__ void __launch_bounds__(WARPS * 32, 1) r4_stream_kernel(StreamArgs a) {
   extern __shared__ __align__(128) uint8_t smem_raw[];
   static_assert(32 % KC == 0, "a stage must not straddle a 32-tile flag word");
@@ -229,14 +270,10 @@ __global__ void __launch_bounds__(WARPS * 32, 1) r4_stream_kernel(StreamArgs a) 
   const int64_t K = a.K;
   const int T = a.T, S = a.stages;
   const uint32_t base = smem_addr(smem_raw);
-  const uint32_t x_at = (base + 15u) & ~15u;
-  const uint32_t bar_at = x_at + (uint32_t)T * 256u;
-  const uint32_t pool_a = (bar_at + WARPS * (uint32_t)S * 8u + 127u) & ~127u;
-  const uint32_t ring_bytes = (uint32_t)S * STAGE;
-  const uint32_t in_a = pool_a < 65536u ? (65536u - pool_a) / ring_bytes : 0u;  // warps with rings below the table
-  const uint32_t s_ring = warp < in_a ? pool_a + warp * ring_bytes : 131072u + (warp - in_a) * ring_bytes;
-  const uint32_t need_end = in_a >= WARPS ? 131072u : 131072u + (WARPS - in_a) * ring_bytes;
-  if (base > ST_BASE_MAX || need_end > base + a.smem) {  // the host sized the window for another layout
+  const StreamLayout L = stream_layout(base, T, M, WARPS, S, STAGE);
+  const uint32_t x_at = L.x_at, bar_at = L.bar_at, xrow = (uint32_t)T * 256u;
+  const uint32_t s_ring = warp < L.in_a ? L.pool_a + warp * (uint32_t)S * STAGE : L.pool_c + (warp - L.in_a) * (uint32_t)S * STAGE;
+  if (base > ST_BASE_MAX || L.end > base + a.smem) {  // the host sized the window for another layout
     if (threadIdx.x == 0) atomicExch(&g_stream_error, 2);
     return;
   }
@@ -292,9 +329,12 @@ __global__ void __launch_bounds__(WARPS * 32, 1) r4_stream_kernel(StreamArgs a) 
 
   // while the first stages fly: x and the pair table into shared memory (whole block)
   {
-    const uint4 *x8 = reinterpret_cast<const uint4 *>(a.x + (a.ei ? (int64_t)a.xi[slot] * K : 0));
     uint4 *dst = reinterpret_cast<uint4 *>(smem_raw + (x_at - base));
-    for (int i = threadIdx.x; i < T * 16; i += THREADS) dst[i] = (int64_t)i * 8 < K ? __ldg(x8 + i) : make_uint4(0, 0, 0, 0);  // K % 16 == 0
+    for (int i = threadIdx.x; i < M * T * 16; i += THREADS) {
+      const int m = i / (T * 16), j = i - m * (T * 16);
+      const uint4 *x8 = reinterpret_cast<const uint4 *>(a.x + (a.ei ? (int64_t)a.xi[slot] * K : (int64_t)m * a.x_stride));
+      dst[i] = (m < a.m && (int64_t)j * 8 < K) ? __ldg(x8 + j) : make_uint4(0, 0, 0, 0);  // K % 16 == 0
+    }
     uint32_t *lut = reinterpret_cast<uint32_t *>(smem_raw + (65536u - base));
     for (uint32_t i = threadIdx.x; i < 256 * 32; i += THREADS) {
       const uint32_t code = i >> 5, l = i & 31, c0 = code & 15, c1 = code >> 4;
@@ -331,10 +371,14 @@ __global__ void __launch_bounds__(WARPS * 32, 1) r4_stream_kernel(StreamArgs a) 
   for (int g = 0; g < ngroups; g++) {
     const bool wide = g < nfull;
     const int64_t row = r_begin + group_row(g);
-    float acc[RW];
+    float acc[RW][M];
     uint32_t epos[RW], fmask[RW];
 #pragma unroll
-    for (int i = 0; i < RW; i++) acc[i] = 0.0f, epos[i] = pf_epos[i], fmask[i] = 0u;
+    for (int i = 0; i < RW; i++) {
+      epos[i] = pf_epos[i], fmask[i] = 0u;
+#pragma unroll
+      for (int m = 0; m < M; m++) acc[i][m] = 0.0f;
+    }
     if (g + 1 < ngroups) prefetch_epos(g + 1);
     uint32_t xs = x_at + lane * 8;
     for (int c = 0; c < nchunks; c++) {
@@ -361,33 +405,44 @@ __global__ void __launch_bounds__(WARPS * 32, 1) r4_stream_kernel(StreamArgs a) 
         uint32_t fbits[RW];
 #pragma unroll
         for (int i = 0; i < RW; i++) fbits[i] = (fmask[i] >> (t0 & 31)) & STAGE_MASK;
-        consume_stage<RW, KC, RAW_ROW, CODE_ROW>(raw, codes, xs, lut_lane, token, nt, partial, lane_in_partial, fbits, a.w.esc, epos, acc);
+        consume_stage<RW, KC, M, RAW_ROW, CODE_ROW>(raw, codes, xs, xrow, lut_lane, token, nt, partial, lane_in_partial, fbits, a.w.esc, epos, acc);
       } else {
         uint32_t fb1[1] = {(fmask[0] >> (t0 & 31)) & STAGE_MASK}, ep1[1] = {epos[0]};
-        float ac1[1] = {acc[0]};
-        consume_stage<1, KC, RAW_ROW, CODE_ROW>(raw, codes, xs, lut_lane, token, nt, partial, lane_in_partial, fb1, a.w.esc, ep1, ac1);
-        epos[0] = ep1[0], acc[0] = ac1[0];
+        float ac1[1][M];
+#pragma unroll
+        for (int m = 0; m < M; m++) ac1[0][m] = acc[0][m];
+        consume_stage<1, KC, M, RAW_ROW, CODE_ROW>(raw, codes, xs, xrow, lut_lane, token, nt, partial, lane_in_partial, fb1, a.w.esc, ep1, ac1);
+        epos[0] = ep1[0];
+#pragma unroll
+        for (int m = 0; m < M; m++) acc[0][m] = ac1[0][m];
       }
       xs += KC * 256;
       // every read of the slot feeds an accumulator: pin them before the slot is refilled
 #pragma unroll
-      for (int i = 0; i < RW; i++) asm volatile("" ::"f"(acc[i]) : "memory");
+      for (int i = 0; i < RW; i++)
+#pragma unroll
+        for (int m = 0; m < M; m++) asm volatile("" ::"f"(acc[i][m]) : "memory");
       __syncwarp();
       issue();  // refill the slot just drained
       cs = cs + 1 == S ? 0 : cs + 1;
     }
+    // lane i * M + m ends up with the sum of (row i, input m)
     float mine = 0.0f;
 #pragma unroll
-    for (int i = 0; i < RW; i++) {
-      float s = acc[i];
+    for (int i = 0; i < RW; i++)
 #pragma unroll
-      for (int o = 16; o >= 1; o >>= 1) s = s + __shfl_xor_sync(BN_FULL, s, o);
-      if ((int)lane == i) mine = s;
-    }
-    if ((int)lane < (wide ? RW : 1)) {
-      const int64_t r = row - row0 + lane;  // output row within the slot
+      for (int m = 0; m < M; m++) {
+        float s = acc[i][m];
+#pragma unroll
+        for (int o = 16; o >= 1; o >>= 1) s = s + __shfl_xor_sync(BN_FULL, s, o);
+        if ((int)lane == i * M + m) mine = s;
+      }
+    const int li = (int)lane / M, lm = (int)lane % M;  // this lane's (row, input)
+    if (li < (wide ? RW : 1) && lm < a.m) {
+      const int64_t r = row - row0 + li;  // output row within the slot
       const uint16_t v = f32_to_bf16_bits(mine);
-      if (a.split > 0 && r >= a.split) a.y2[slot * (a.N - a.split) + (r - a.split)] = v;
+      if (M > 1) a.y[(int64_t)lm * a.y_stride + r] = v;
+      else if (a.split > 0 && r >= a.split) a.y2[slot * (a.N - a.split) + (r - a.split)] = v;
       else a.y[slot * (a.split > 0 ? a.split : a.N) + r] = v;
     }
   }
@@ -406,29 +461,24 @@ static int stream_sms() {
 
 constexpr uint32_t ST_SMEM_MAX = 227 * 1024;  // dynamic shared memory one block may ask for
 
-// Ring depth that fits the shared window when the dynamic allocation starts at `base` (mirrors
-// the kernel's layout arithmetic); 0 if not even two stages per warp fit.
-static int stream_stages(int warps, uint32_t stage, int T, uint32_t base) {
-  for (int S = 6; S >= 2; S--) {
-    const uint32_t x_at = (base + 15u) & ~15u, bar_at = x_at + (uint32_t)T * 256u;
-    const uint32_t pool_a = (bar_at + (uint32_t)warps * S * 8u + 127u) & ~127u, ring = S * stage;
-    if (pool_a > 65536u) return 0;
-    const uint32_t in_a = (65536u - pool_a) / ring;
-    const uint32_t end = in_a >= (uint32_t)warps ? 131072u : 131072u + ((uint32_t)warps - in_a) * ring;
-    if (end <= ST_SMEM_MAX) return S;  // the window ends at base + ST_SMEM_MAX >= ST_SMEM_MAX
-  }
+// Ring depth that fits the shared window when the dynamic allocation starts at `base` (the
+// kernel's own layout arithmetic); 0 if not even two stages per warp fit.
+static int stream_stages(int warps, uint32_t stage, int T, int M, uint32_t base) {
+  for (int S = 6; S >= 2; S--)
+    if (stream_layout(base, T, M, warps, S, stage).end <= ST_SMEM_MAX) return S;  // the window ends at base + ST_SMEM_MAX >= ST_SMEM_MAX
   return 0;
 }
 
-template <int WARPS, int RW, int KC>
+template <int WARPS, int RW, int KC, int M = 1>
 static int launch_stream(StreamArgs a, cudaStream_t s, int64_t slots = 1) {
   // worst case of the two extremes of the window's start; the kernel re-derives the layout
   // from the real start and refuses to run if it does not fit
-  const int stages = min(stream_stages(WARPS, RW * KC * 192, a.T, 0), stream_stages(WARPS, RW * KC * 192, a.T, ST_BASE_MAX));
+  const int stages = min(stream_stages(WARPS, RW * KC * 192, a.T, M, 0), stream_stages(WARPS, RW * KC * 192, a.T, M, ST_BASE_MAX));
   if (stages < 2) return -1;  // does not fit: caller falls back
   a.stages = stages;
   a.smem = ST_SMEM_MAX;
-  auto kern = r4_stream_kernel<WARPS, RW, KC>;
+  if (a.m < 1) a.m = 1;
+  auto kern = r4_stream_kernel<WARPS, RW, KC, M>;
   BN_CUDA(allow_smem(kern, a.smem));
   int64_t blocks = (stream_sms() + slots - 1) / slots;  // blocks per slot: about one block per SM in all
   const int64_t need = (a.N + WARPS - 1) / WARPS;
@@ -464,6 +514,27 @@ int stream_gather(const bn_r4 *w, const uint16_t *x, const uint32_t *xi, const u
   if (e == -1) e = launch_stream<16, 2, 8>(a, s, G);
   if (e == -1) e = launch_stream<8, 2, 8>(a, s, G);
   return e;
+}
+
+// 2..8 input rows through the streaming kernel (weights stream once, M accumulators per weight
+// row, every output in the documented order); -1 when the shape is outside its coverage.
+template <int M>
+static int stream_rows_m(StreamArgs a, cudaStream_t s) {
+  int e = launch_stream<16, 2, 8, M>(a, s);
+  if (e == -1) e = launch_stream<12, 2, 8, M>(a, s);
+  if (e == -1) e = launch_stream<8, 2, 8, M>(a, s);
+  return e;
+}
+
+int stream_rows(const bn_r4 *w, const uint16_t *x, int64_t x_stride, int64_t M, int64_t N, int64_t K, uint16_t *y, int64_t y_stride, cudaStream_t s) {
+  const int64_t T = tiles(K);
+  if (K % 16 || x_stride % 8 || N < 1 || T > 200 || M < 2 || M > 8) return -1;
+  StreamArgs a{};
+  a.w = *w, a.x = x, a.y = y, a.N = N, a.K = K, a.T = (int)T;
+  a.m = (int)M, a.x_stride = x_stride, a.y_stride = y_stride;
+  if (M == 2) return stream_rows_m<2>(a, s);
+  if (M <= 4) return stream_rows_m<4>(a, s);
+  return stream_rows_m<8>(a, s);
 }
 
 }  // namespace bn

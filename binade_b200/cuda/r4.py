@@ -21,7 +21,7 @@ from torch import nn
 from ..format import TILE
 from . import kernels as ck
 
-FUSED_MAX_ROWS = 2  # input rows served by the fused decode kernel; beyond, rebuilding BF16 and calling cuBLAS is faster on B200 (measured on 15360 x 3840: fused 52 / 148 / 252 us at 2 / 8 / 16 rows, rebuild 93 us)
+FUSED_MAX_ROWS = 8  # input rows served by the fused decode kernel; beyond, rebuilding BF16 and calling cuBLAS is faster on B200 (measured on 15360 x 3840: fused 38 / 73 us at 2 / 8 rows and 252 us at 16, rebuild 92 us)
 
 
 class BinadeLinear(nn.Module):
