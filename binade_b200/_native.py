@@ -18,7 +18,7 @@ _vp, _i64, _u64, _int = C.c_void_p, C.c_int64, C.c_uint64, C.c_int
 class R4Struct(C.Structure):
     """bn_r4: device pointers of one R4 matrix."""
 
-    _fields_ = [(n, _vp) for n in ("raw", "codes", "flags", "esc", "table", "row_esc")]
+    _fields_ = [(n, _vp) for n in ("raw", "codes", "flags", "esc", "table", "row_esc")] + [("n_esc", _u64)]
 
 
 _SIGNATURES = {

@@ -17,7 +17,6 @@
 
 namespace bn {
 
-constexpr uint32_t ST_LUT_BYTES = 256 * 256;
 constexpr uint32_t ST_SPIN_LIMIT = 1u << 24;
 constexpr uint32_t ST_BASE_MAX = 2048;  // the dynamic shared window starts below this address
 
@@ -325,31 +324,6 @@ __global__ void __launch_bounds__(WARPS * 32, 1) r4_stream_kernel(StreamArgs a) 
     }
     ps = ps + 1 == S ? 0 : ps + 1;
   };
-  for (int s = 0; s < S; s++) issue();
-
-  // while the first stages fly: x and the pair table into shared memory (whole block)
-  {
-    uint4 *dst = reinterpret_cast<uint4 *>(smem_raw + (x_at - base));
-    for (int i = threadIdx.x; i < M * T * 16; i += THREADS) {
-      const int m = i / (T * 16), j = i - m * (T * 16);
-      const uint4 *x8 = reinterpret_cast<const uint4 *>(a.x + (a.ei ? (int64_t)a.xi[slot] * K : (int64_t)m * a.x_stride));
-      dst[i] = (m < a.m && (int64_t)j * 8 < K) ? __ldg(x8 + j) : make_uint4(0, 0, 0, 0);  // K % 16 == 0
-    }
-    uint32_t *lut = reinterpret_cast<uint32_t *>(smem_raw + (65536u - base));
-    for (uint32_t i = threadIdx.x; i < 256 * 32; i += THREADS) {
-      const uint32_t code = i >> 5, l = i & 31, c0 = code & 15, c1 = code >> 4;
-      const uint32_t e0 = c0 == 15 ? 0u : __ldg(a.w.table + c0), e1 = c1 == 15 ? 0u : __ldg(a.w.table + c1);
-      lut[code * 64 + l] = (e0 << 7) | (e1 << 23);
-    }
-    __syncthreads();
-  }
-
-  const uint32_t lut_lane = 65536u + lane * 4;
-  // in a row's partial last tile (K % 128 != 0) only the lanes below K % 128 hold weights
-  const bool has_partial = (K & 127) != 0;
-  const bool lane_in_partial = (int64_t)lane * 4 < (K & 127);
-  int cs = 0;           // consumer slot
-  uint32_t phases = 0;  // bit s: parity to wait for on slot s
   // flag bytes (one 32-tile group per row at a time) and escape cursors are fetched one step
   // ahead of their use, so their global-memory latency hides behind the previous tiles
   uint32_t pf_flag[RW], pf_epos[RW];
@@ -366,7 +340,46 @@ __global__ void __launch_bounds__(WARPS * 32, 1) r4_stream_kernel(StreamArgs a) 
 #pragma unroll
     for (int i = 0; i < RW; i++) pf_epos[i] = a.w.row_esc[r_begin + r0 + min(i, live - 1)];
   };
+
+  // Start-up order matters: the first ring fills ask for megabytes at once across the GPU, and a
+  // load issued after them queues behind them. So the small loads everything waits on (x, the
+  // table, the first rows' flags and cursors) are issued first, then the ring fills; their
+  // results are consumed only afterwards.
+  const int x_words = M * T * 16;  // 16-byte pieces of x
+  auto x_piece = [&](int i) {
+    const int m = i / (T * 16), j = i - m * (T * 16);
+    const uint4 *x8 = reinterpret_cast<const uint4 *>(a.x + (a.ei ? (int64_t)a.xi[slot] * K : (int64_t)m * a.x_stride));
+    return (m < a.m && (int64_t)j * 8 < K) ? __ldg(x8 + j) : make_uint4(0, 0, 0, 0);  // K % 16 == 0
+  };
+  const uint32_t tab_byte = threadIdx.x < 15 ? (uint32_t)__ldg(a.w.table + threadIdx.x) : 0u;
+  const uint4 x_first = (int)threadIdx.x < x_words ? x_piece(threadIdx.x) : make_uint4(0, 0, 0, 0);
   if (ngroups > 0) prefetch_flags(0, 0), prefetch_epos(0);
+  for (int s = 0; s < S; s++) issue();
+
+  // x and the pair table into shared memory (whole block). The 15 table bytes go through shared
+  // memory first, so the 8192 table words are built from on-chip reads.
+  {
+    uint32_t *s_tab = reinterpret_cast<uint32_t *>(smem_raw + (65536u + 128u - base));  // an unused half of table entry 0
+    if (threadIdx.x < 16) s_tab[threadIdx.x] = tab_byte;
+    uint4 *dst = reinterpret_cast<uint4 *>(smem_raw + (x_at - base));
+    if ((int)threadIdx.x < x_words) dst[threadIdx.x] = x_first;
+    for (int i = threadIdx.x + THREADS; i < x_words; i += THREADS) dst[i] = x_piece(i);
+    __syncthreads();
+    uint32_t *lut = reinterpret_cast<uint32_t *>(smem_raw + (65536u - base));
+#pragma unroll 4
+    for (uint32_t i = threadIdx.x; i < 256 * 32; i += THREADS) {
+      const uint32_t code = i >> 5, l = i & 31;
+      lut[code * 64 + l] = (s_tab[code & 15] << 7) | (s_tab[code >> 4] << 23);  // entry 15: no exponent bits
+    }
+    __syncthreads();
+  }
+
+  const uint32_t lut_lane = 65536u + lane * 4;
+  // in a row's partial last tile (K % 128 != 0) only the lanes below K % 128 hold weights
+  const bool has_partial = (K & 127) != 0;
+  const bool lane_in_partial = (int64_t)lane * 4 < (K & 127);
+  int cs = 0;           // consumer slot
+  uint32_t phases = 0;  // bit s: parity to wait for on slot s
   const int fgroups = (T + 31) / 32;
   for (int g = 0; g < ngroups; g++) {
     const bool wide = g < nfull;

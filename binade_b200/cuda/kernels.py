@@ -51,7 +51,7 @@ def _call(fn, *args):
 
 
 def r4_struct(a: dict) -> _native.R4Struct:
-    return _native.R4Struct(*(a[k].data_ptr() for k in R4_KEYS))
+    return _native.R4Struct(*(a[k].data_ptr() for k in R4_KEYS), a["esc"].numel() - 1)
 
 
 def rice_ranks(meta: torch.Tensor, bits: torch.Tensor, roff: torch.Tensor, K: int):

@@ -45,7 +45,9 @@ int bn_abi_version(void);
  *   flags   [N*T]      non-zero iff the tile holds a code 15 (escape)
  *   esc     [n_esc+1]  exponent bytes of the escaped weights, row-major order, one trailing 0
  *   table   [256]      exponent by rank (only entries 0..14 are read by the kernels)
- *   row_esc [N]        number of escapes before each row                                    */
+ *   row_esc [N]        number of escapes before each row
+ *   n_esc              escapes in `esc` (which holds n_esc + 1 bytes): lets the kernels fetch a
+ *                      row's escape bytes ahead of use without reading past the array        */
 typedef struct bn_r4 {
   const uint8_t *raw;
   const uint16_t *codes;
@@ -53,6 +55,7 @@ typedef struct bn_r4 {
   const uint8_t *esc;
   const uint8_t *table;
   const uint32_t *row_esc;
+  uint64_t n_esc;
 } bn_r4;
 
 /* ------------------------------------------------------------------ 2. CUDA entry points -- */
