@@ -31,6 +31,8 @@ _SIGNATURES = {
         "bn_r4_finish": [_vp, _vp, _vp, _i64, _vp, _vp, _u64, _vp],
         "bn_rice_to_r4_static": [_vp, _vp, _u64, _vp, _vp, _i64, _i64, _vp, _vp, _vp, _vp, _u64, _vp, _vp],
         "bn_r4_decode": [C.POINTER(R4Struct), _i64, _i64, _i64, _i64, _i64, _vp, _vp],
+        "bn_r4_lookup": [C.POINTER(R4Struct), _i64, _vp, _i64, _i64, _vp, _vp],
+        "bn_rice_lookup": [_vp, _vp, _u64, _vp, _vp, _vp, _i64, _i64, _vp, _i64, _vp, _vp],
         "bn_r4_rows": [_vp, _i64, C.POINTER(R4Struct), _i64, _i64, _i64, _vp, _i64, _vp],
         "bn_r4_gather": [_vp, C.POINTER(R4Struct), _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i64, _vp, _vp, _vp],
     },

@@ -58,7 +58,7 @@ __device__ __forceinline__ float hi_f32(uint32_t w) { return __uint_as_float(w &
 // ---------------------------------------------------------------------------------------------
 constexpr int DEC_THREADS = 256;
 
-__global__ void __launch_bounds__(DEC_THREADS) r4_decode_kernel(bn_r4 w, int64_t N, int64_t K, int T, int64_t NB, int64_t RS, int64_t R0, uint16_t *__restrict__ out) {
+__global__ void __launch_bounds__(DEC_THREADS) r4_decode_kernel(bn_r4 w, int64_t N, int64_t K, int T, int64_t NB, int64_t RS, int64_t R0, const uint32_t *__restrict__ ids, int64_t rows, uint16_t *__restrict__ out) {
   extern __shared__ uint32_t lut[];
   build_pair_lut(lut, w.table);
   __syncthreads();
@@ -66,7 +66,11 @@ __global__ void __launch_bounds__(DEC_THREADS) r4_decode_kernel(bn_r4 w, int64_t
   const uint32_t lut_lane = smem_addr(lut) + lane * 4;
   const int warps = DEC_THREADS / 32;
   for (int64_t orow = (int64_t)blockIdx.x * warps + (threadIdx.x >> 5); orow < N; orow += (int64_t)gridDim.x * warps) {
-    const int64_t row = (orow / NB) * RS + R0 + orow % NB;
+    const int64_t row = ids ? (int64_t)ids[orow] : (orow / NB) * RS + R0 + orow % NB;
+    if (ids && row >= rows) {  // an id outside the table: a row of zeros
+      for (int64_t c = lane; c < K; c += 32) out[orow * K + c] = 0;
+      continue;
+    }
     uint32_t epos = w.row_esc[row];
     const uint8_t *raw = w.raw + row * K;
     const uint16_t *codes = w.codes + row * T * 32;
@@ -308,7 +312,21 @@ extern "C" int bn_r4_decode(const bn_r4 *w, int64_t N, int64_t K, int64_t NB, in
   const int warps = DEC_THREADS / 32;
   int64_t blocks = (N + warps - 1) / warps;
   if (blocks > (int64_t)sm_count() * 8) blocks = (int64_t)sm_count() * 8;
-  r4_decode_kernel<<<(unsigned)blocks, DEC_THREADS, smem, (cudaStream_t)stream>>>(*w, N, K, (int)tiles(K), NB, RS, R0, out);
+  r4_decode_kernel<<<(unsigned)blocks, DEC_THREADS, smem, (cudaStream_t)stream>>>(*w, N, K, (int)tiles(K), NB, RS, R0, nullptr, 0, out);
+  return launched("r4_decode_kernel");
+}
+
+extern "C" int bn_r4_lookup(const bn_r4 *w, int64_t rows, const uint32_t *ids, int64_t n, int64_t K, uint16_t *out, void *stream) {
+  if (int e = check_r4(w)) return e;
+  if (!ids || !out || n < 0 || K <= 0 || rows < 0) return fail(BN_ERR_ARG, "bn_r4_lookup: bad size or null pointer");
+  if (K % 4) return fail(BN_ERR_ARG, "R4 needs K % 4 == 0");
+  if (n == 0) return BN_OK;
+  const size_t smem = LUT_WORDS * 4;
+  BN_CUDA(allow_smem(r4_decode_kernel, smem));
+  const int warps = DEC_THREADS / 32;
+  int64_t blocks = (n + warps - 1) / warps;
+  if (blocks > (int64_t)sm_count() * 8) blocks = (int64_t)sm_count() * 8;
+  r4_decode_kernel<<<(unsigned)blocks, DEC_THREADS, smem, (cudaStream_t)stream>>>(*w, n, K, (int)tiles(K), 1, 1, 0, ids, rows, out);
   return launched("r4_decode_kernel");
 }
 

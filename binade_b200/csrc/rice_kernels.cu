@@ -22,6 +22,9 @@ struct RiceArgs {
   const uint8_t *raw;
   int64_t R, K;
   int T;
+  // lookups (RICE_UNPACK only): output row i decodes stream row ids[i] of a table of `rows` rows
+  const uint32_t *ids;
+  int64_t rows;
   // outputs
   uint32_t *ranks;   // RICE_RANKS: [R, T*32] four 8-bit ranks per word
   uint32_t *rend;    // RICE_RANKS / RICE_UNPACK: word after each row's last bit
@@ -85,8 +88,14 @@ __global__ void __launch_bounds__(RICE_THREADS) rice_kernel(RiceArgs a) {
   const int T = a.T;
   const int64_t K = a.K;
   for (int64_t row = (int64_t)blockIdx.x * warps + (threadIdx.x >> 5); row < a.R; row += (int64_t)gridDim.x * warps) {
-    const uint32_t w0 = a.roff[row];
-    const uint64_t w_end = row + 1 < a.R ? (uint64_t)a.roff[row + 1] : a.nwords;
+    const int64_t srow = (MODE == RICE_UNPACK && a.ids) ? (int64_t)a.ids[row] : row;  // row of the stream
+    if (MODE == RICE_UNPACK && a.ids && srow >= a.rows) {  // an id outside the table: a row of zeros
+      for (int64_t c = lane; c < K; c += 32) a.out[row * K + c] = 0;
+      continue;
+    }
+    const int64_t srows = (MODE == RICE_UNPACK && a.ids) ? a.rows : a.R;
+    const uint32_t w0 = a.roff[srow];
+    const uint64_t w_end = srow + 1 < srows ? (uint64_t)a.roff[srow + 1] : a.nwords;
     // pull the row's stream toward the SM: one 128-byte line per lane, up to 4 KB
     {
       const uint64_t p = (uint64_t)w0 + lane * 32u;
@@ -116,7 +125,7 @@ __global__ void __launch_bounds__(RICE_THREADS) rice_kernel(RiceArgs a) {
       if (lane == 0) a.tmp_off[row] = (uint32_t)base;
     }
     for (int t0 = 0; t0 < T; t0 += 32) {
-      const uint32_t my_meta = t0 + (int)lane < T ? a.meta[row * T + t0 + lane] : 0u;
+      const uint32_t my_meta = t0 + (int)lane < T ? a.meta[srow * T + t0 + lane] : 0u;
       uint32_t my_flag = 0;
       const int tn = min(32, T - t0);
       for (int u = 0; u < tn; u++) {
@@ -174,7 +183,7 @@ __global__ void __launch_bounds__(RICE_THREADS) rice_kernel(RiceArgs a) {
         } else if (MODE == RICE_UNPACK) {
           const int64_t col = (int64_t)t * BN_TILE + lane * 4;
           if (nv == 4 && (K & 3) == 0) {  // aligned: one 4-byte load, one 8-byte store
-            const uint32_t rw = ldg_stream_u32(a.raw + row * K + col);
+            const uint32_t rw = ldg_stream_u32(a.raw + srow * K + col);
             uint32_t o[4];
 #pragma unroll
             for (int i = 0; i < 4; i++) {
@@ -184,7 +193,7 @@ __global__ void __launch_bounds__(RICE_THREADS) rice_kernel(RiceArgs a) {
             *reinterpret_cast<uint2 *>(a.out + row * K + col) = make_uint2(o[0] | (o[1] << 16), o[2] | (o[3] << 16));
           } else {
             for (uint32_t i = 0; i < nv; i++) {
-              const uint32_t b = a.raw[row * K + col + i], e = tbl[(r4 >> (8 * i)) & 0xFFu];
+              const uint32_t b = a.raw[srow * K + col + i], e = tbl[(r4 >> (8 * i)) & 0xFFu];
               a.out[row * K + col + i] = (uint16_t)(((b & 0x80u) << 8) | (e << 7) | (b & 0x7Fu));
             }
           }
@@ -220,7 +229,7 @@ __global__ void __launch_bounds__(RICE_THREADS) rice_kernel(RiceArgs a) {
         a.row_cnt[row] = row_escapes;
         if (row_escapes) atomicAdd(a.counters + 2, row_escapes);
         if ((uint64_t)rend != w_end) atomicMax(a.counters + 1, (uint32_t)(a.R - row));
-      } else {
+      } else if (a.rend) {
         a.rend[row] = rend;
       }
     }
@@ -299,6 +308,17 @@ extern "C" int bn_rice_unpack(const uint8_t *meta, const uint32_t *bits, uint64_
   a.meta = meta, a.bits = bits, a.nwords = nwords, a.roff = roff, a.table = table, a.raw = raw, a.R = R, a.K = K, a.T = (int)tiles(K);
   a.out = out, a.rend = rend;
   rice_kernel<RICE_UNPACK><<<rice_grid(R), RICE_THREADS, 0, (cudaStream_t)stream>>>(a);
+  return launched("rice_kernel<unpack>");
+}
+
+extern "C" int bn_rice_lookup(const uint8_t *meta, const uint32_t *bits, uint64_t nwords, const uint32_t *roff, const uint8_t *table, const uint8_t *raw, int64_t rows, int64_t K, const uint32_t *ids, int64_t n, uint16_t *out, void *stream) {
+  if (int e = check_stream(meta, bits, roff, rows, K)) return e;
+  if (!table || !raw || !ids || !out || n < 0) return fail(BN_ERR_ARG, "bn_rice_lookup: null pointer or negative count");
+  if (n == 0) return BN_OK;
+  RiceArgs a{};
+  a.meta = meta, a.bits = bits, a.nwords = nwords, a.roff = roff, a.table = table, a.raw = raw, a.R = n, a.K = K, a.T = (int)tiles(K);
+  a.ids = ids, a.rows = rows, a.out = out, a.rend = nullptr;
+  rice_kernel<RICE_UNPACK><<<rice_grid(n), RICE_THREADS, 0, (cudaStream_t)stream>>>(a);
   return launched("rice_kernel<unpack>");
 }
 

@@ -123,6 +123,29 @@ def r4_decode(a: dict, N: int, K: int, nb: int | None = None, rs: int | None = N
     return out
 
 
+def r4_lookup(a: dict, ids: torch.Tensor, N: int, K: int) -> torch.Tensor:
+    """BF16 rows [n, K] of an R4 table of N rows for ids [n] (int32 on the device); an id outside
+    the table gives a row of zeros."""
+    out = torch.empty((ids.numel(), K), dtype=torch.bfloat16, device=a["raw"].device)
+    if ids.numel() == 0:
+        return out
+    _call("bn_r4_lookup", ctypes.byref(r4_struct(a)), N, _p(ids), ids.numel(), K, _p(out))
+    return out
+
+
+def rice_lookup(meta, bits, roff, table, raw, N: int, K: int, ids: torch.Tensor) -> torch.Tensor:
+    """BF16 rows [n, K] for ids [n] (int32 on the device) of an N x K table kept as a Rice stream;
+    an id outside the table gives a row of zeros."""
+    out = torch.empty((ids.numel(), K), dtype=torch.bfloat16, device=raw.device)
+    if ids.numel() == 0:
+        return out
+    nwords = bits.numel()
+    if nwords == 0:
+        bits = torch.zeros(1, dtype=torch.int32, device=raw.device)
+    _call("bn_rice_lookup", _p(meta), _p(bits), nwords, _p(roff), _p(table), _p(raw), N, K, _p(ids), ids.numel(), _p(out))
+    return out
+
+
 def r4_rows(a: dict, x: torch.Tensor, N: int, K: int) -> torch.Tensor:
     """x [M, K] (1 <= M <= 16, bfloat16, contiguous rows) -> [M, N], fused decode."""
     M = x.shape[0]

@@ -75,7 +75,9 @@ class Decoder(nn.Module):
             r0, r1 = row_range(count, rank, world)
             return w[r0:r1]
 
-        self.embed = synthetic_weight(s.vocab, s.hidden, seed + 1, dev)
+        emb = synthetic_weight(s.vocab, s.hidden, seed + 1, dev)
+        self.embed = r4.R4Embedding(r4.from_dense(emb)) if kind == "r4" else emb  # whole table on every rank
+        del emb
         self.qkv, self.o, self.gate_up, self.down, self.norm1, self.norm2 = nn.ModuleList(), nn.ModuleList(), nn.ModuleList(), nn.ModuleList(), [], []
         for l in range(s.layers):
             base = seed + 100 * (l + 1)
@@ -133,7 +135,7 @@ class Decoder(nn.Module):
     def step(self, token: torch.Tensor, pos: torch.Tensor) -> torch.Tensor:
         """One decode step: token, pos are device int64 tensors of one element -> logits [1, vocab]."""
         s, d = self.shape, self.shape.head_dim
-        x = self.embed.index_select(0, token)  # [1, hidden]
+        x = self.embed(token) if isinstance(self.embed, r4.R4Embedding) else self.embed.index_select(0, token)  # [1, hidden]
         mask = (self.positions <= pos)[None, None, :]  # [1, 1, max_seq]
         for l in range(s.layers):
             h = torch.nn.functional.rms_norm(x, (s.hidden,), self.norm1[l], s.eps)

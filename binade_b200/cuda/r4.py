@@ -4,6 +4,9 @@ Same roles and names as the reference's binade/mlx/r4.py, on torch:
   transcode(module)   Rice arrays {raw, table, meta, bits, roff} -> R4 dict, on the GPU in one
                       fused pass (reference: transcode + _rank_chunks, r4.py:119-175)
   R4Linear(a)         the linear-layer hook: y = x @ W.T with W decoded inside the kernel
+  R4Embedding(a)      token rows decoded from an R4 table (r4.py:303-325); as_linear for tied heads
+  RiceEmbedding(w)    gather-only table kept as a Rice stream, about 10.7 bits per weight resident
+                      (r4.py:328-367)
   convert(model)      swap every BinadeLinear holder for an R4Linear in place (r4.py:375-410)
 
 Row counts: 1..FUSED_MAX_ROWS input rows run the fused decode kernel (weights stream once, fp32
@@ -34,6 +37,20 @@ class BinadeLinear(nn.Module):
 
     def forward(self, x):
         raise RuntimeError("packed weights run on the R4 runtime: call binade_b200.cuda.r4.convert(model)")
+
+
+class BinadeEmbedding(nn.Module):
+    """Holder of one packed embedding table's file arrays until `convert` swaps it. gather_only
+    marks a table that never enters a matmul; it is then kept in its file coding
+    (RiceEmbedding), as the reference does (binade/mlx/slow_linear.py:149-160, r4.py:397-399)."""
+
+    def __init__(self, weight: dict, gather_only: bool = False):
+        super().__init__()
+        self.weight = weight
+        self.gather_only = gather_only
+
+    def forward(self, ids):
+        raise RuntimeError("packed tables run on the R4 runtime: call binade_b200.cuda.r4.convert(model)")
 
 
 def transcode(module) -> dict:
@@ -147,13 +164,64 @@ class R4Linear(nn.Module, _R4):
         return self._rows(x)
 
 
+class R4Embedding(nn.Module, _R4):
+    """Rows for token ids from an R4 table: one kernel decodes only the looked-up rows, with no
+    host synchronisation (reference: R4Embedding, binade/mlx/r4.py:303-325)."""
+
+    def __init__(self, a: dict):
+        nn.Module.__init__(self)
+        self._init_r4(a)
+
+    def forward(self, ids: torch.Tensor) -> torch.Tensor:
+        flat = ids.reshape(-1).to(device=self._a["raw"].device, dtype=torch.int32)
+        return ck.r4_lookup(self._a, flat, self.N, self.K).reshape(*ids.shape, self.K)
+
+    def as_linear(self, x: torch.Tensor) -> torch.Tensor:
+        """x @ table.T (a tied output head) through the fused decode kernels."""
+        return self._rows(x)
+
+
+class RiceEmbedding(nn.Module):
+    """Gather-only table kept in format 2 (Rice) in GPU memory. A lookup decodes just the rows
+    asked for: their stream offsets are read inside the kernel, so ids never visit the host.
+    No as_linear: the table never enters a matmul (reference: RiceEmbedding, r4.py:328-367)."""
+
+    def __init__(self, w: dict):
+        super().__init__()
+        w = w.weight if hasattr(w, "weight") else w
+        raw = ck.to_device(w["raw"])
+        self.K = raw.shape[-1]
+        self.N = raw.numel() // self.K
+        self.T = -(-self.K // TILE)
+        meta, bits, roff, table = (ck.to_device(w[k]) for k in ("meta", "bits", "roff", "table"))
+        if meta.numel() != self.N * self.T or roff.numel() != self.N:
+            raise ValueError(f"{meta.numel()} tiles and {roff.numel()} row offsets for {self.N} x {self.K}")
+        self._a = {"raw": raw.reshape(self.N, self.K), "table": table, "meta": meta.reshape(-1), "bits": bits, "roff": roff, "shape": tuple(raw.shape)}
+
+    def forward(self, ids: torch.Tensor) -> torch.Tensor:
+        a = self._a
+        flat = ids.reshape(-1).to(device=a["raw"].device, dtype=torch.int32)
+        return ck.rice_lookup(a["meta"], a["bits"], a["roff"], a["table"], a["raw"], self.N, self.K, flat).reshape(*ids.shape, self.K)
+
+    def dense(self) -> torch.Tensor:
+        """The BF16 table."""
+        a = self._a
+        return ck.rice_unpack(a["meta"], a["bits"], a["roff"], a["table"], a["raw"], self.N, self.K)[0].reshape(a["shape"])
+
+
 def convert(model: nn.Module, log=None) -> int:
-    """Swap every BinadeLinear for an R4Linear in place; returns how many were converted. Each
-    holder's file arrays are dropped as soon as its R4 arrays exist."""
-    todo = [(parent, name) for parent in model.modules() for name, child in parent.named_children() if isinstance(child, BinadeLinear)]
+    """Swap every file-array holder for its runtime counterpart in place: BinadeLinear ->
+    R4Linear, BinadeEmbedding -> R4Embedding, or RiceEmbedding for a gather-only table; returns
+    how many were converted (reference: r4.py:375-410). Each holder's file arrays are dropped as
+    soon as its runtime arrays exist."""
+    todo = [(parent, name) for parent in model.modules() for name, child in parent.named_children() if isinstance(child, (BinadeLinear, BinadeEmbedding))]
     for i, (parent, name) in enumerate(todo, 1):
         holder = getattr(parent, name)
-        setattr(parent, name, R4Linear(transcode(holder)))
+        if isinstance(holder, BinadeEmbedding):
+            new = RiceEmbedding(holder.weight) if holder.gather_only and "bits" in holder.weight else R4Embedding(transcode(holder))
+        else:
+            new = R4Linear(transcode(holder))
+        setattr(parent, name, new)
         holder.weight = None
         if log and (i % 50 == 0 or i == len(todo)):
             log(f"R4 transcode {i}/{len(todo)}")

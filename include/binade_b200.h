@@ -124,6 +124,21 @@ int bn_rice_to_r4_static(const uint8_t *meta, const uint32_t *bits, uint64_t nwo
 int bn_r4_decode(const bn_r4 *w, int64_t N, int64_t K, int64_t NB, int64_t RS, int64_t R0,
                  uint16_t *out, void *stream);
 
+/* Embedding lookup from an R4 table of `rows` rows: out [n,K] row i = BF16 row ids[i]; an id
+ * >= rows gives a row of zeros. Replaces R4Embedding.__call__, binade/mlx/r4.py:308-322 (a graph
+ * of elementwise array ops there; one kernel here, no host synchronisation either). */
+int bn_r4_lookup(const bn_r4 *w, int64_t rows, const uint32_t *ids, int64_t n, int64_t K,
+                 uint16_t *out, void *stream);
+
+/* Embedding lookup from a table kept as a Rice stream (about 10.7 bits per weight resident):
+ * out [n,K] row i = BF16 row ids[i] of the `rows` x K table (meta [rows*T], roff [rows], raw
+ * [rows*K]); an id >= rows gives a row of zeros. Replaces RiceEmbedding.__call__,
+ * binade/mlx/r4.py:357-364 (gather of the rows' meta and offsets, then rice_ranks, then the
+ * join): the gather, the decode, the table lookup and the join are one pass here. */
+int bn_rice_lookup(const uint8_t *meta, const uint32_t *bits, uint64_t nwords, const uint32_t *roff,
+                   const uint8_t *table, const uint8_t *raw, int64_t rows, int64_t K,
+                   const uint32_t *ids, int64_t n, uint16_t *out, void *stream);
+
 /* Fused R4-decode products Y [M,N] = X [M,K] . W^T for 1 <= M <= 16 input rows, fp32
  * accumulation in a fixed order per output: 32 lanes, lane l owns weights 128t + 4l + j and adds
  * their products (fused multiply-add) for t then j ascending; columns >= K are skipped; lanes

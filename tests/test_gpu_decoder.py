@@ -42,6 +42,8 @@ def test_decoder_r4_matches_bf16_weights_and_graph_matches_eager():
     d = Decoder(tiny(), kind="bf16")
     for a, b in zip(list(m.qkv) + list(m.gate_up) + list(m.o) + list(m.down) + [m.lm_head], list(d.qkv) + list(d.gate_up) + list(d.o) + list(d.down) + [d.lm_head]):
         assert torch.equal(a.dense().reshape(b.w.shape), b.w)
+    # the token table is compressed too: lookups return the BF16 rows the dense model reads
+    assert torch.equal(m.embed(prompt), d.embed.index_select(0, prompt))
     # same weights, different summation order (documented lane order vs cuBLAS): logits agree
     # to BF16 rounding, not bit for bit
     tok, pos = prompt[:1].clone(), torch.zeros(1, dtype=torch.int64, device="cuda")

@@ -217,6 +217,68 @@ def test_dense_row_remap():
     assert np.array_equal(words(m.dense()), u)
 
 
+# ------------------------------------------------------------------------------ embedding lookups
+@pytest.mark.parametrize("N,K", [(1000, 384), (257, 100), (64, 4096), (33, 4)])
+def test_embedding_lookups(N, K):
+    """R4Embedding and RiceEmbedding return exactly the packed rows (reference r4.py:303-367), in
+    any id order, with repeats; the oracle's decode of the same rows is the check."""
+    from binade_b200.cuda import r4
+
+    rng = np.random.default_rng(N + K)
+    u = weights(rng, (N, K))
+    p = packed_arrays(u)
+    ranks, _ = o.c_rice_decode_ranks(p["meta"], p["bits"], p["roff"], K)
+    want_all = o.np_join(np.asarray(p["raw"]).reshape(N, K), np.asarray(p["table"])[ranks[:, :K]])
+    assert np.array_equal(want_all, u)
+    ids = np.concatenate([rng.integers(0, N, 50), [0, N - 1, N - 1, 0]]).astype(np.int64).reshape(6, 9)
+    e_r4 = r4.R4Embedding(r4.transcode(p))
+    e_rice = r4.RiceEmbedding(p)
+    for ids_t in (torch.from_numpy(ids).cuda(), torch.from_numpy(ids.astype(np.int32)).cuda(), torch.from_numpy(ids)):
+        for e in (e_r4, e_rice):
+            got = e(ids_t)
+            assert got.shape == (6, 9, K) and got.dtype == torch.bfloat16
+            assert np.array_equal(words(got), want_all[ids])
+    assert np.array_equal(words(e_rice.dense()), u)
+    assert np.array_equal(words(e_r4.dense()), u)
+    # an id outside the table: a row of zeros, nothing read out of bounds
+    bad = torch.tensor([N, 0, 2**31 - 1], dtype=torch.int64).cuda()
+    for e in (e_r4, e_rice):
+        got = words(e(bad))
+        assert not got[0].any() and not got[2].any() and np.array_equal(got[1], u[0])
+    assert e_r4(torch.zeros((0,), dtype=torch.int64)).shape == (0, K)
+
+
+def test_convert_swaps_embedding_holders():
+    from binade_b200.cuda import r4
+
+    rng = np.random.default_rng(12)
+    u1, u2 = weights(rng, (50, 128)), weights(rng, (40, 256))
+
+    class Tiny(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.tok = r4.BinadeEmbedding(packed_arrays(u1))
+            self.ple = r4.BinadeEmbedding(packed_arrays(u2), gather_only=True)
+
+    m = Tiny()
+    with pytest.raises(RuntimeError):
+        m.tok(torch.zeros(1, dtype=torch.int64))
+    assert r4.convert(m) == 2
+    assert isinstance(m.tok, r4.R4Embedding) and isinstance(m.ple, r4.RiceEmbedding)
+    ids = torch.tensor([[3, 49], [0, 3]]).cuda()
+    assert np.array_equal(words(m.tok(ids)), u1[ids.cpu().numpy()])
+    assert np.array_equal(words(m.ple(ids % 40)), u2[(ids % 40).cpu().numpy()])
+
+
+def test_embedding_as_linear_is_the_matvec():
+    from binade_b200.cuda import r4
+
+    u = weights(np.random.default_rng(4), (96, 256))
+    a = r4.transcode(packed_arrays(u))
+    x = torch.randn(1, 256, device="cuda").to(torch.bfloat16)
+    assert np.array_equal(words(r4.R4Embedding(a).as_linear(x)), words(r4.R4Linear(a)(x)))
+
+
 # ------------------------------------------------------------------------------ fused products
 @pytest.mark.parametrize("N,K", [(64, 704), (160, 2112), (300, 260), (48, 100), (64, 128), (40, 4), (4096, 512), (520, 3840), (200, 15360)])
 def test_matvec_bit_exact(N, K):
