@@ -1,0 +1,279 @@
+// Fused R4-decode GEMM for 16..128 input rows on the 5th-generation tensor cores (tcgen05):
+//   Y[m, n] = sum_k X[m, k] W[n, k]      X [M, K] BF16, W [N, K] in R4, Y [M, N] BF16
+// computed as D = W_tile . X^T so that the few input rows sit in the MMA's N dimension:
+//   A operand  128 weight rows x 128 k, decoded from R4 to BF16 by the CUDA cores straight into
+//              shared memory in the tensor core's K-major 128-byte-swizzled layout
+//   B operand  BN = M rounded up to 16 input rows x 128 k, copied from X into the same layout
+//   D          128 x BN fp32 accumulators in tensor memory (TMEM), read back with tcgen05.ld
+// One block per 128 weight rows. 16 warps decode (8 rows each per stage: a weight row stays with
+// one warp, so its escape cursor is a register), one warp issues the MMAs; a ring of stages
+// (mbarriers: `full` armed by the decoders, `empty` by tcgen05.commit) lets decode run ahead.
+// The weights are read once whatever M. Accumulation order inside an MMA is the hardware's: this
+// path is not bit-identical to the documented lane order of the one-row kernels (the outputs are
+// checked against an fp32 reference to one BF16 unit in the last place).
+//
+// Every wait is bounded: when one gives up, a status flag is set, every thread still reaches the
+// end of the kernel, and the tensor memory is released.
+#include "common.cuh"
+#include "decode.cuh"
+
+namespace bn {
+
+constexpr int MMA_DECODE_WARPS = 16;
+constexpr int MMA_THREADS = (MMA_DECODE_WARPS + 1) * 32;
+constexpr int MMA_BM = 128;                  // weight rows per block (MMA M)
+constexpr int MMA_BK = 128;                  // k per stage: one R4 tile
+constexpr uint32_t MMA_A_STAGE = MMA_BM * MMA_BK * 2;  // 32 KB: two 64-k atoms of 128 rows x 128 B
+constexpr uint32_t MMA_SPIN_LIMIT = 1u << 22;
+constexpr uint32_t MMA_SMEM_MAX = 226 * 1024;  // dynamic part; the pair-table builder keeps 64 static bytes
+
+__device__ int g_mma_error;  // 1: a bounded wait gave up
+
+__device__ __forceinline__ void mm_bar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mm_bar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mm_bar_wait(uint32_t bar, uint32_t parity) {
+  for (uint32_t i = 0; i < MMA_SPIN_LIMIT; i++) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    if (ok) return true;
+  }
+  atomicExch(&g_mma_error, 1);
+  return false;
+}
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+// Shared-memory matrix descriptor of a K-major, 128-byte-swizzled operand tile that starts at
+// shared address `addr` (1024-byte aligned atom; `addr` may point 32 * j bytes into the first
+// row to select the j-th group of 16 k): start address >> 4 in bits 0..13, leading byte offset
+// (unused for swizzled K-major, set to 1) in 16..29, stride between 8-row groups (1024 B) >> 4
+// in 32..45, descriptor version 1 in 46..47, layout 2 = 128-byte swizzle in 61..63.
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr) {
+  return (uint64_t)((addr >> 4) & 0x3FFFu) | (1ull << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
+}
+// Instruction descriptor: fp32 accumulate (bits 4..5 = 1), A and B BF16 (bits 7..9, 10..12 = 1),
+// both K-major (bits 15, 16 = 0), N >> 3 in bits 17..22, M >> 4 in bits 24..28.
+__host__ __device__ constexpr uint32_t mma_idesc(int m, int n) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+__device__ __forceinline__ void mma_bf16(uint32_t tmem_d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
+      "l"(a), "l"(b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void mma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+struct MmaArgs {
+  bn_r4 w;
+  const uint16_t *x;
+  uint16_t *y;
+  int64_t N, K, x_stride, y_stride;
+  int T, M, BN, stages;
+  uint32_t tmem_cols;
+};
+
+// Byte offset of (row r, 16-byte chunk c of the row's 128 bytes) inside a swizzled atom.
+__device__ __forceinline__ uint32_t swz(uint32_t r, uint32_t c) { return r * 128u + ((c ^ (r & 7u)) << 4); }
+
+__global__ void __launch_bounds__(MMA_THREADS, 1) r4_mma_kernel(MmaArgs a) {
+  extern __shared__ uint8_t mma_smem[];
+  const uint32_t lane = lane_id(), warp = threadIdx.x >> 5, lt = lanemask_lt();
+  const int T = a.T, S = a.stages, BN = a.BN;
+  const int64_t K = a.K;
+  const uint32_t b_stage = (uint32_t)BN * MMA_BK * 2u;  // two 64-k atoms of BN rows x 128 B
+  // shared window: A stages | B stages | pair table | barriers
+  const uint32_t base = (smem_addr(mma_smem) + 1023u) & ~1023u;
+  const uint32_t a_at = base, b_at = a_at + (uint32_t)S * MMA_A_STAGE, lut_at = b_at + (uint32_t)S * b_stage;
+  const uint32_t bar_at = lut_at + LUT_WORDS * 4u;  // full[S], empty[S], done, then the TMEM address
+  const uint32_t full = bar_at, empty = bar_at + 8u * S, done = bar_at + 16u * S, slot = done + 8u;
+  uint8_t *const gen = mma_smem + (base - smem_addr(mma_smem));  // generic pointer to `base`
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < S; s++) mm_bar_init(full + 8 * s, MMA_DECODE_WARPS), mm_bar_init(empty + 8 * s, 1);
+    mm_bar_init(done, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == MMA_DECODE_WARPS) {  // the MMA warp owns the tensor memory
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(slot), "r"(a.tmem_cols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  build_pair_lut(reinterpret_cast<uint32_t *>(gen + (lut_at - base)), a.w.table);  // syncs once inside
+  // rows of B beyond M stay zero for the whole kernel
+  for (uint32_t i = threadIdx.x; i < (uint32_t)S * b_stage / 16u; i += MMA_THREADS) reinterpret_cast<uint4 *>(gen + (b_at - base))[i] = make_uint4(0, 0, 0, 0);
+  fence_async_smem();
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  uint32_t tmem;
+  asm volatile("ld.shared.u32 %0, [%1];" : "=r"(tmem) : "r"(slot));
+
+  const int64_t row_base = (int64_t)blockIdx.x * MMA_BM;
+  bool ok = true;
+
+  if (warp < MMA_DECODE_WARPS) {
+    // ---------------------------------------------------------------- decode side
+    constexpr int RPW = MMA_BM / MMA_DECODE_WARPS;  // 8 rows of the block per warp
+    const uint32_t lut_lane = lut_at + lane * 4u;
+    const uint32_t r0 = warp * RPW;
+    uint32_t epos[RPW];
+    bool live[RPW];
+#pragma unroll
+    for (int i = 0; i < RPW; i++) {
+      const int64_t r = row_base + r0 + i;
+      live[i] = r < a.N;
+      epos[i] = live[i] ? a.w.row_esc[r] : 0u;
+    }
+    // this thread's pieces of the B tile: 16-byte chunk c of input row m, M * 16 chunks per stage
+    constexpr int XP = MMA_BM * 16 / (MMA_DECODE_WARPS * 32);  // at most 4 per thread (M <= 128)
+    const uint32_t xi0 = warp * 32u + lane;
+    auto load_stage = [&](int t, uint32_t (&rw)[RPW], uint32_t (&cd)[RPW], uint32_t &flag, uint4 (&xp)[XP]) {
+      const bool col_in = (int64_t)t * BN_TILE + (int64_t)lane * 4 < K;  // K % 4 == 0
+#pragma unroll
+      for (int i = 0; i < RPW; i++) {
+        const int64_t r = row_base + r0 + i;
+        rw[i] = (live[i] && col_in) ? ldg_stream_u32(a.w.raw + r * K + (int64_t)t * BN_TILE + lane * 4) : 0u;
+        cd[i] = live[i] ? ldg_stream_u16(a.w.codes + (r * T + t) * 32 + lane) : 0u;
+      }
+      flag = (lane < RPW && row_base + r0 + lane < a.N) ? (uint32_t)a.w.flags[(row_base + r0 + lane) * T + t] : 0u;
+#pragma unroll
+      for (int j = 0; j < XP; j++) {
+        const uint32_t idx = xi0 + j * (MMA_DECODE_WARPS * 32), m = idx >> 4, c = idx & 15u;
+        const int64_t k0 = (int64_t)t * BN_TILE + c * 8;
+        // K % 8 == 0 is required by the entry point, so a chunk is inside a row or wholly outside
+        xp[j] = ((int)m < a.M && k0 < K) ? __ldg(reinterpret_cast<const uint4 *>(a.x + (int64_t)m * a.x_stride + k0)) : make_uint4(0, 0, 0, 0);
+      }
+    };
+    uint32_t rw[RPW], cd[RPW], flag;
+    uint4 xp[XP];
+    load_stage(0, rw, cd, flag, xp);
+    for (int t = 0; t < T; t++) {
+      const int s = t % S;
+      uint32_t rw_n[RPW] = {}, cd_n[RPW] = {}, flag_n = 0;
+      uint4 xp_n[XP] = {};
+      if (t + 1 < T) load_stage(t + 1, rw_n, cd_n, flag_n, xp_n);
+      if (t >= S && ok) ok = mm_bar_wait(empty + 8 * s, ((t / S) - 1) & 1);
+      tc_fence_after();
+      const uint32_t fmask = __ballot_sync(BN_FULL, flag != 0);
+      const uint32_t a_s = a_at + (uint32_t)s * MMA_A_STAGE + (lane >> 4) * (MMA_BM * 128u) + (lane & 1u) * 8u;
+      const uint32_t chunk = (lane & 15u) >> 1;
+#pragma unroll
+      for (int i = 0; i < RPW; i++) {
+        uint32_t w01, w23;
+        decode4(rw[i], cd[i], lut_lane, w01, w23);
+        if ((fmask >> i) & 1u) apply_escapes(cd[i], a.w.esc, epos[i], lt, w01, w23);
+        const bool in = live[i] && (int64_t)t * BN_TILE + (int64_t)lane * 4 < K;
+        if (!in) w01 = 0u, w23 = 0u;
+        asm volatile("st.shared.v2.u32 [%0], {%1, %2};" ::"r"(a_s + swz(r0 + i, chunk)), "r"(w01), "r"(w23) : "memory");
+      }
+      const uint32_t b_s = b_at + (uint32_t)s * b_stage;
+#pragma unroll
+      for (int j = 0; j < XP; j++) {
+        const uint32_t idx = xi0 + j * (MMA_DECODE_WARPS * 32), m = idx >> 4, c = idx & 15u;
+        if ((int)m < a.M) asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(b_s + (c >> 3) * ((uint32_t)BN * 128u) + swz(m, c & 7u)), "r"(xp[j].x), "r"(xp[j].y), "r"(xp[j].z), "r"(xp[j].w) : "memory");
+      }
+      fence_async_smem();  // the tensor core reads shared memory through the async proxy
+      __syncwarp();
+      if (lane == 0) mm_bar_arrive(full + 8 * s);
+#pragma unroll
+      for (int i = 0; i < RPW; i++) rw[i] = rw_n[i], cd[i] = cd_n[i];
+#pragma unroll
+      for (int j = 0; j < XP; j++) xp[j] = xp_n[j];
+      flag = flag_n;
+    }
+  } else {
+    // ---------------------------------------------------------------- MMA issue (one thread)
+    const uint32_t idesc = mma_idesc(MMA_BM, BN);
+    for (int t = 0; t < T; t++) {
+      const int s = t % S;
+      if (ok) ok = mm_bar_wait(full + 8 * s, (t / S) & 1);
+      tc_fence_after();
+      if (lane == 0 && ok) {
+        const uint32_t a_s = a_at + (uint32_t)s * MMA_A_STAGE, b_s = b_at + (uint32_t)s * b_stage;
+#pragma unroll
+        for (int j = 0; j < MMA_BK / 16; j++) {  // 16 k per MMA: 32 bytes further along the swizzled row
+          const uint64_t da = smem_desc(a_s + (j >> 2) * (MMA_BM * 128u) + (j & 3) * 32u);
+          const uint64_t db = smem_desc(b_s + (j >> 2) * ((uint32_t)BN * 128u) + (j & 3) * 32u);
+          mma_bf16(tmem, da, db, idesc, (t | j) != 0);
+        }
+        mma_commit(empty + 8 * s);  // arrives when these MMAs have read the stage
+      }
+      __syncwarp();
+    }
+    if (lane == 0 && ok) mma_commit(done);
+    __syncwarp();
+  }
+
+  // ------------------------------------------------------------------ epilogue: warps 0..3
+  if (warp < 4) {
+    if (ok) ok = mm_bar_wait(done, 0);
+    tc_fence_after();
+    const int64_t n = row_base + warp * 32 + lane;  // TMEM lane 32 * warp + lane = weight row
+    if (ok) {
+      for (int c = 0; c < BN; c += 8) {
+        uint32_t v[8];
+        asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+                     : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7])
+                     : "r"(tmem + ((warp * 32u) << 16) + (uint32_t)c));
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+        for (int i = 0; i < 8; i++)
+          if (c + i < a.M && n < a.N) a.y[(int64_t)(c + i) * a.y_stride + n] = f32_to_bf16_bits(__uint_as_float(v[i]));
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == MMA_DECODE_WARPS) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(a.tmem_cols) : "memory");
+}
+
+// Fused decode GEMM for 16 <= M <= 128 input rows; -1 when the shape is outside its coverage.
+int mma_rows(const bn_r4 *w, const uint16_t *x, int64_t x_stride, int64_t M, int64_t N, int64_t K, uint16_t *y, int64_t y_stride, cudaStream_t s) {
+  if (M < 1 || M > MMA_BM || K % 8 || x_stride % 8 || N < 1) return -1;
+  MmaArgs a{};
+  a.w = *w, a.x = x, a.y = y, a.N = N, a.K = K, a.x_stride = x_stride, a.y_stride = y_stride;
+  a.T = (int)tiles(K), a.M = (int)M, a.BN = (int)((M + 15) / 16 * 16);
+  a.tmem_cols = 32;
+  while ((int)a.tmem_cols < a.BN) a.tmem_cols *= 2;
+  const uint32_t fixed = 1024 + LUT_WORDS * 4 + 256;  // alignment slack, pair table, barriers
+  const uint32_t per_stage = MMA_A_STAGE + (uint32_t)a.BN * MMA_BK * 2u;
+  int stages = (int)((MMA_SMEM_MAX - fixed) / per_stage);
+  if (stages > 4) stages = 4;
+  if (stages < 2) return -1;
+  a.stages = stages;
+  const uint32_t smem = fixed + (uint32_t)stages * per_stage;
+  BN_CUDA(allow_smem(r4_mma_kernel, smem));
+  r4_mma_kernel<<<(unsigned)((N + MMA_BM - 1) / MMA_BM), MMA_THREADS, smem, s>>>(a);
+  return launched("r4_mma_kernel");
+}
+
+int mma_status(int *status) {
+  BN_CUDA(cudaMemcpyFromSymbol(status, g_mma_error, sizeof(int)));
+  return BN_OK;
+}
+
+}  // namespace bn
+
+extern "C" int bn_r4_mma(const uint16_t *x, int64_t x_stride, const bn_r4 *w, int64_t M, int64_t N, int64_t K, uint16_t *y, int64_t y_stride, void *stream) {
+  if (!w || !w->raw || !w->codes || !w->flags || !w->esc || !w->table || !w->row_esc) return bn::fail(BN_ERR_ARG, "bn_r4_mma: null R4 array");
+  if (!x || !y || N < 0 || K <= 0 || M < 1 || M > 128) return bn::fail(BN_ERR_ARG, "bn_r4_mma: bad size (1 <= M <= 128) or null pointer");
+  if (K % 8 || x_stride % 8) return bn::fail(BN_ERR_ARG, "bn_r4_mma needs K % 8 == 0 and x rows 16-byte aligned");
+  if (N == 0) return BN_OK;
+  const int e = bn::mma_rows(w, x, x_stride, M, N, K, y, y_stride, (cudaStream_t)stream);
+  return e == -1 ? bn::fail(BN_ERR_ARG, "bn_r4_mma: shape does not fit shared memory") : e;
+}

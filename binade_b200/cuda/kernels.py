@@ -123,6 +123,15 @@ def r4_decode(a: dict, N: int, K: int, nb: int | None = None, rs: int | None = N
     return out
 
 
+def r4_mma(a: dict, x: torch.Tensor, N: int, K: int) -> torch.Tensor:
+    """x [M, K] (1 <= M <= 128, bfloat16, contiguous rows, K % 8 == 0) -> [M, N] through the fused
+    decode GEMM on the tensor cores (tcgen05); accumulation order is the hardware's."""
+    M = x.shape[0]
+    y = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
+    _call("bn_r4_mma", _p(x), x.stride(0), ctypes.byref(r4_struct(a)), M, N, K, _p(y), N)
+    return y
+
+
 def r4_lookup(a: dict, ids: torch.Tensor, N: int, K: int) -> torch.Tensor:
     """BF16 rows [n, K] of an R4 table of N rows for ids [n] (int32 on the device); an id outside
     the table gives a row of zeros."""

@@ -27,6 +27,9 @@ from . import kernels as ck
 FUSED_MAX_ROWS = 8  # input rows served by the fused decode kernel; beyond, rebuilding BF16 and calling cuBLAS is faster on B200 (measured on 15360 x 3840: fused 38 / 73 us at 2 / 8 rows and 252 us at 16, rebuild 92 us)
 
 
+MMA_MAX_ROWS = 128  # input rows served by the tensor-core decode GEMM (one pass over the weights); beyond, rebuild + cuBLAS
+
+
 class BinadeLinear(nn.Module):
     """Holder of one packed weight's file arrays (`weight` = dict of raw, table, meta, bits, roff,
     numpy or torch) until `convert` turns it into an R4Linear. It cannot run."""
@@ -146,12 +149,20 @@ class _R4:
         M = x.numel() // self.K
         return ck.r4_rows(self._a, x.reshape(M, self.K).contiguous(), self.N, self.K).reshape(*x.shape[:-1], self.N)
 
+    def mma_rows(self, x: torch.Tensor) -> torch.Tensor:
+        """x [..., K] with up to 128 rows -> [..., N] through the tensor-core decode GEMM (weights
+        decoded to BF16 inside the kernel and read once; the sum over K in the hardware's order)."""
+        M = x.numel() // self.K
+        return ck.r4_mma(self._a, x.reshape(M, self.K).contiguous(), self.N, self.K).reshape(*x.shape[:-1], self.N)
+
     def _rows(self, x: torch.Tensor) -> torch.Tensor:
         M = x.numel() // self.K
         if M == 1:
             return self._matvec(x)
         if M <= FUSED_MAX_ROWS:
             return self.fused_rows(x)
+        if M <= MMA_MAX_ROWS and self.K % 8 == 0:
+            return self.mma_rows(x)
         return x @ self.dense().reshape(self.N, self.K).T
 
 

@@ -124,6 +124,16 @@ int bn_rice_to_r4_static(const uint8_t *meta, const uint32_t *bits, uint64_t nwo
 int bn_r4_decode(const bn_r4 *w, int64_t N, int64_t K, int64_t NB, int64_t RS, int64_t R0,
                  uint16_t *out, void *stream);
 
+/* Fused R4-decode GEMM on the tensor cores for 1 <= M <= 128 input rows (meant for 16 and more):
+ * Y [M,N] = X [M,K] . W^T with the weights decoded to BF16 inside the kernel (tcgen05 MMA, fp32
+ * accumulators in tensor memory); the weights are read once whatever M. K % 8 == 0, rows of X
+ * 16-byte aligned. The sum over K is formed by the tensor core in its own order: outputs agree
+ * with an fp32 reference to one BF16 unit in the last place, not bit for bit with bn_r4_rows.
+ * Replaces the fused decode GEMM of _R4._cuda_fused, binade/mlx/r4.py:254-268 (r4_gemm,
+ * binade/mlx/cuda_kernels.py:640-700, an mma.sync kernel there). */
+int bn_r4_mma(const uint16_t *x, int64_t x_stride, const bn_r4 *w, int64_t M, int64_t N, int64_t K,
+              uint16_t *y, int64_t y_stride, void *stream);
+
 /* Embedding lookup from an R4 table of `rows` rows: out [n,K] row i = BF16 row ids[i]; an id
  * >= rows gives a row of zeros. Replaces R4Embedding.__call__, binade/mlx/r4.py:308-322 (a graph
  * of elementwise array ops there; one kernel here, no host synchronisation either). */

@@ -345,10 +345,38 @@ def test_small_m_rows(M):
     assert np.array_equal(words(got)[0], o.c_dense_rows(xw, u))
 
 
+@pytest.mark.parametrize("M,N,K", [(16, 128, 128), (16, 256, 512), (32, 200, 3840), (128, 384, 1024), (24, 130, 264), (100, 96, 2048), (1, 64, 128)])
+def test_mma_rows_against_fp32(M, N, K):
+    """Tensor-core decode GEMM: the weights it multiplies by are exactly the decoded BF16 weights
+    (checked with one-hot inputs, where every output is a single weight), and on random inputs
+    every output is within one BF16 unit in the last place of the fp32 product (plus the fp32
+    summation noise of a differently ordered sum, 1e-5 of the output scale)."""
+    from binade_b200.cuda import r4
+
+    rng = np.random.default_rng(M * 7 + N + K)
+    u = weights(rng, (N, K), escapes=False)
+    u.reshape(-1)[3::173] = 0x5F80  # rare finite exponent: escapes
+    m = r4.R4Linear(r4.transcode(packed_arrays(u)))
+    w = dev(u).view(torch.bfloat16)
+    # one-hot rows: output m is column k_m of W, exactly
+    ks = rng.integers(0, K, M)
+    x1 = torch.zeros((M, K), dtype=torch.bfloat16, device="cuda")
+    x1[torch.arange(M), torch.from_numpy(ks).cuda()] = 1.0
+    got1, want1 = words(m.mma_rows(x1)), u[:, ks].T.copy()
+    want1[want1 == 0x8000] = 0  # a sum that starts at +0 turns a lone -0 product into +0
+    assert np.array_equal(got1, want1)
+    x = torch.randn((M, K), device="cuda").to(torch.bfloat16)
+    got = m.mma_rows(x).float()
+    ref = x.float() @ w.float().T
+    scale = ref.abs().mean()
+    bound = ref.abs() * 2.0**-7 + scale * 1e-5
+    assert bool(((got - ref).abs() <= bound).all()), float(((got - ref).abs() - bound).max())
+
+
 def test_many_rows_rebuild_path():
     from binade_b200.cuda import r4
 
-    N, K, M = 256, 512, 40
+    N, K, M = 256, 512, 200  # more rows than the fused kernels take
     rng = np.random.default_rng(5)
     u = weights(rng, (N, K), escapes=False)
     u.reshape(-1)[5::199] = 0x5F80  # 2^64: a rare exponent (escape) that keeps every sum finite
