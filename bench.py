@@ -459,8 +459,10 @@ def run_ours(args) -> dict | None:
 
 def prefill_leg(torch, dev, graph_us) -> dict:
     """Fused decode products for short prompts on the gate projection (15360 x 3840): M rows of
-    N(0,1) inputs; 1..16 rows run the fused kernel (weights stream once), more rows rebuild the
-    BF16 weight and call cuBLAS; against cuBLAS on the pre-decoded weight."""
+    N(0,1) inputs; up to FUSED_MAX_ROWS rows run the fused kernel in the documented order, up to
+    MMA_MAX_ROWS the tensor-core decode GEMM (weights stream once in both), more rows rebuild the
+    BF16 weight and call cuBLAS; against cuBLAS on the pre-decoded weight, and against the rebuild
+    path where a fused kernel serves the row count."""
     from binade_b200.cuda import kernels as ck
     from binade_b200.cuda import r4
 
@@ -472,9 +474,10 @@ def prefill_leg(torch, dev, graph_us) -> dict:
         x = torch.randn((M, k), device=dev, generator=torch.Generator(device=dev).manual_seed(M)).to(torch.bfloat16)
         us = graph_us(lambda i: m(x), iters=10)
         us_ref = graph_us(lambda i: torch.matmul(x, w.T), iters=10)
-        out[str(M)] = {"us": round(us, 1), "cublas_bf16_us": round(us_ref, 1), "vs_cublas": round(us_ref / us, 3), "path": "fused rows" if M <= r4.FUSED_MAX_ROWS else "rebuild + cuBLAS"}
-        if r4.FUSED_MAX_ROWS < M <= 16:
-            out[str(M)]["fused_rows_us"] = round(graph_us(lambda i: m.fused_rows(x), iters=10), 1)
+        path = "fused rows" if M <= r4.FUSED_MAX_ROWS else "tcgen05 decode GEMM" if M <= r4.MMA_MAX_ROWS else "rebuild + cuBLAS"
+        out[str(M)] = {"us": round(us, 1), "cublas_bf16_us": round(us_ref, 1), "vs_cublas": round(us_ref / us, 3), "path": path}
+        if M <= r4.MMA_MAX_ROWS:
+            out[str(M)]["rebuild_us"] = round(graph_us(lambda i: x @ m.dense().reshape(n, k).T, iters=10), 1)
     return out
 
 

@@ -1,27 +1,34 @@
 // Fused R4-decode GEMM for 16..128 input rows on the 5th-generation tensor cores (tcgen05):
 //   Y[m, n] = sum_k X[m, k] W[n, k]      X [M, K] BF16, W [N, K] in R4, Y [M, N] BF16
 // computed as D = W_tile . X^T so that the few input rows sit in the MMA's N dimension:
-//   A operand  128 weight rows x 128 k, decoded from R4 to BF16 by the CUDA cores straight into
-//              shared memory in the tensor core's K-major 128-byte-swizzled layout
-//   B operand  BN = M rounded up to 16 input rows x 128 k, copied from X into the same layout
+//   A operand  up to 112 weight rows x 128 k, decoded from R4 to BF16 by the CUDA cores straight
+//              into shared memory in the tensor core's K-major 128-byte-swizzled layout
+//   B operand  BN = M rounded up to 16 input rows x 128 k, brought in by TMA (2-D tensor map over
+//              X with the same swizzle; rows past M and columns past K arrive as zeros)
 //   D          128 x BN fp32 accumulators in tensor memory (TMEM), read back with tcgen05.ld
-// One block per 128 weight rows. 16 warps decode (8 rows each per stage: a weight row stays with
-// one warp, so its escape cursor is a register), one warp issues the MMAs; a ring of stages
-// (mbarriers: `full` armed by the decoders, `empty` by tcgen05.commit) lets decode run ahead.
-// The weights are read once whatever M. Accumulation order inside an MMA is the hardware's: this
-// path is not bit-identical to the documented lane order of the one-row kernels (the outputs are
-// checked against an fp32 reference to one BF16 unit in the last place).
+// One block per SM, each with an equal share of the weight rows. 28 warps decode (4 rows each
+// per stage: a weight row stays with one warp, so its escape cursor is a register; raw bytes and
+// codes are fetched two stages ahead into registers), one warp issues the TMA copies and the
+// MMAs; a ring of stages (mbarriers: `full` armed by the decoders and the TMA bytes, `empty` by
+// tcgen05.commit) lets decode run ahead. The weights are read once whatever M. Accumulation order
+// inside an MMA is the hardware's: this path is not bit-identical to the documented lane order of
+// the one-row kernels (the outputs are checked against an fp32 reference to one BF16 unit in the
+// last place).
 //
 // Every wait is bounded: when one gives up, a status flag is set, every thread still reaches the
 // end of the kernel, and the tensor memory is released.
+#include <cuda.h>
+
 #include "common.cuh"
 #include "decode.cuh"
 
 namespace bn {
 
-constexpr int MMA_DECODE_WARPS = 16;
+constexpr int MMA_DECODE_WARPS = 28;
+constexpr int MMA_RPW = 4;                                  // weight rows per decode warp and stage
+constexpr int MMA_ROWS = MMA_DECODE_WARPS * MMA_RPW;        // most weight rows a block takes (112)
 constexpr int MMA_THREADS = (MMA_DECODE_WARPS + 1) * 32;
-constexpr int MMA_BM = 128;                  // weight rows per block (MMA M)
+constexpr int MMA_BM = 128;                  // MMA M: rows of the A tile (the block's rows, then unused)
 constexpr int MMA_BK = 128;                  // k per stage: one R4 tile
 constexpr uint32_t MMA_A_STAGE = MMA_BM * MMA_BK * 2;  // 32 KB: two 64-k atoms of 128 rows x 128 B
 constexpr uint32_t MMA_SPIN_LIMIT = 1u << 22;
@@ -34,6 +41,12 @@ __device__ __forceinline__ void mm_bar_init(uint32_t bar, uint32_t count) {
 }
 __device__ __forceinline__ void mm_bar_arrive(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mm_bar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, int x, int y, uint32_t bar) {
+  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
 }
 __device__ __forceinline__ bool mm_bar_wait(uint32_t bar, uint32_t parity) {
   for (uint32_t i = 0; i < MMA_SPIN_LIMIT; i++) {
@@ -81,17 +94,17 @@ __device__ __forceinline__ void mma_commit(uint32_t bar) {
 
 struct MmaArgs {
   bn_r4 w;
-  const uint16_t *x;
   uint16_t *y;
-  int64_t N, K, x_stride, y_stride;
+  int64_t N, K, y_stride;
   int T, M, BN, stages;
+  int rows;  // weight rows per block (a multiple of MMA_RPW, at most MMA_ROWS)
   uint32_t tmem_cols;
 };
 
 // Byte offset of (row r, 16-byte chunk c of the row's 128 bytes) inside a swizzled atom.
 __device__ __forceinline__ uint32_t swz(uint32_t r, uint32_t c) { return r * 128u + ((c ^ (r & 7u)) << 4); }
 
-__global__ void __launch_bounds__(MMA_THREADS, 1) r4_mma_kernel(MmaArgs a) {
+__global__ void __launch_bounds__(MMA_THREADS, 1) r4_mma_kernel(const __grid_constant__ CUtensorMap x_map, MmaArgs a) {
   extern __shared__ uint8_t mma_smem[];
   const uint32_t lane = lane_id(), warp = threadIdx.x >> 5, lt = lanemask_lt();
   const int T = a.T, S = a.stages, BN = a.BN;
@@ -104,8 +117,12 @@ __global__ void __launch_bounds__(MMA_THREADS, 1) r4_mma_kernel(MmaArgs a) {
   const uint32_t full = bar_at, empty = bar_at + 8u * S, done = bar_at + 16u * S, slot = done + 8u;
   uint8_t *const gen = mma_smem + (base - smem_addr(mma_smem));  // generic pointer to `base`
 
+  const int64_t row_base = (int64_t)blockIdx.x * a.rows;
+  const int rows = (int)min((int64_t)a.rows, a.N - row_base);  // this block's weight rows
+  const uint32_t active = (uint32_t)(rows + MMA_RPW - 1) / MMA_RPW;  // decode warps with rows
+
   if (threadIdx.x == 0) {
-    for (int s = 0; s < S; s++) mm_bar_init(full + 8 * s, MMA_DECODE_WARPS), mm_bar_init(empty + 8 * s, 1);
+    for (int s = 0; s < S; s++) mm_bar_init(full + 8 * s, active + 1), mm_bar_init(empty + 8 * s, 1);
     mm_bar_init(done, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -114,91 +131,78 @@ __global__ void __launch_bounds__(MMA_THREADS, 1) r4_mma_kernel(MmaArgs a) {
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
   build_pair_lut(reinterpret_cast<uint32_t *>(gen + (lut_at - base)), a.w.table);  // syncs once inside
-  // rows of B beyond M stay zero for the whole kernel
-  for (uint32_t i = threadIdx.x; i < (uint32_t)S * b_stage / 16u; i += MMA_THREADS) reinterpret_cast<uint4 *>(gen + (b_at - base))[i] = make_uint4(0, 0, 0, 0);
-  fence_async_smem();
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   uint32_t tmem;
   asm volatile("ld.shared.u32 %0, [%1];" : "=r"(tmem) : "r"(slot));
 
-  const int64_t row_base = (int64_t)blockIdx.x * MMA_BM;
   bool ok = true;
 
-  if (warp < MMA_DECODE_WARPS) {
+  if (warp < active) {
     // ---------------------------------------------------------------- decode side
-    constexpr int RPW = MMA_BM / MMA_DECODE_WARPS;  // 8 rows of the block per warp
+    constexpr int RPW = MMA_RPW;
     const uint32_t lut_lane = lut_at + lane * 4u;
     const uint32_t r0 = warp * RPW;
     uint32_t epos[RPW];
     bool live[RPW];
 #pragma unroll
     for (int i = 0; i < RPW; i++) {
-      const int64_t r = row_base + r0 + i;
-      live[i] = r < a.N;
-      epos[i] = live[i] ? a.w.row_esc[r] : 0u;
+      live[i] = (int)(r0 + i) < rows;
+      epos[i] = live[i] ? a.w.row_esc[row_base + r0 + i] : 0u;
     }
-    // this thread's pieces of the B tile: 16-byte chunk c of input row m, M * 16 chunks per stage
-    constexpr int XP = MMA_BM * 16 / (MMA_DECODE_WARPS * 32);  // at most 4 per thread (M <= 128)
-    const uint32_t xi0 = warp * 32u + lane;
-    auto load_stage = [&](int t, uint32_t (&rw)[RPW], uint32_t (&cd)[RPW], uint32_t &flag, uint4 (&xp)[XP]) {
-      const bool col_in = (int64_t)t * BN_TILE + (int64_t)lane * 4 < K;  // K % 4 == 0
+    auto load_stage = [&](int t, uint32_t (&rw)[RPW], uint32_t (&cd)[RPW], uint32_t &flag) {
+      const bool col_in = t < T && (int64_t)t * BN_TILE + (int64_t)lane * 4 < K;  // K % 4 == 0
 #pragma unroll
       for (int i = 0; i < RPW; i++) {
         const int64_t r = row_base + r0 + i;
         rw[i] = (live[i] && col_in) ? ldg_stream_u32(a.w.raw + r * K + (int64_t)t * BN_TILE + lane * 4) : 0u;
-        cd[i] = live[i] ? ldg_stream_u16(a.w.codes + (r * T + t) * 32 + lane) : 0u;
+        cd[i] = (live[i] && t < T) ? ldg_stream_u16(a.w.codes + (r * T + t) * 32 + lane) : 0u;
       }
-      flag = (lane < RPW && row_base + r0 + lane < a.N) ? (uint32_t)a.w.flags[(row_base + r0 + lane) * T + t] : 0u;
-#pragma unroll
-      for (int j = 0; j < XP; j++) {
-        const uint32_t idx = xi0 + j * (MMA_DECODE_WARPS * 32), m = idx >> 4, c = idx & 15u;
-        const int64_t k0 = (int64_t)t * BN_TILE + c * 8;
-        // K % 8 == 0 is required by the entry point, so a chunk is inside a row or wholly outside
-        xp[j] = ((int)m < a.M && k0 < K) ? __ldg(reinterpret_cast<const uint4 *>(a.x + (int64_t)m * a.x_stride + k0)) : make_uint4(0, 0, 0, 0);
-      }
+      flag = (t < T && lane < RPW && (int)(r0 + lane) < rows) ? (uint32_t)a.w.flags[(row_base + r0 + lane) * T + t] : 0u;
     };
-    uint32_t rw[RPW], cd[RPW], flag;
-    uint4 xp[XP];
-    load_stage(0, rw, cd, flag, xp);
+    // raw bytes, codes and flags of the next two stages wait in registers
+    uint32_t rw0[RPW], cd0[RPW], fl0, rw1[RPW], cd1[RPW], fl1;
+    load_stage(0, rw0, cd0, fl0);
+    load_stage(1, rw1, cd1, fl1);
     for (int t = 0; t < T; t++) {
       const int s = t % S;
-      uint32_t rw_n[RPW] = {}, cd_n[RPW] = {}, flag_n = 0;
-      uint4 xp_n[XP] = {};
-      if (t + 1 < T) load_stage(t + 1, rw_n, cd_n, flag_n, xp_n);
+      uint32_t rw2[RPW], cd2[RPW], fl2;
+      load_stage(t + 2, rw2, cd2, fl2);
       if (t >= S && ok) ok = mm_bar_wait(empty + 8 * s, ((t / S) - 1) & 1);
       tc_fence_after();
-      const uint32_t fmask = __ballot_sync(BN_FULL, flag != 0);
+      const uint32_t fmask = __ballot_sync(BN_FULL, fl0 != 0);
       const uint32_t a_s = a_at + (uint32_t)s * MMA_A_STAGE + (lane >> 4) * (MMA_BM * 128u) + (lane & 1u) * 8u;
       const uint32_t chunk = (lane & 15u) >> 1;
+      const bool col_in = (int64_t)t * BN_TILE + (int64_t)lane * 4 < K;
 #pragma unroll
       for (int i = 0; i < RPW; i++) {
         uint32_t w01, w23;
-        decode4(rw[i], cd[i], lut_lane, w01, w23);
-        if ((fmask >> i) & 1u) apply_escapes(cd[i], a.w.esc, epos[i], lt, w01, w23);
-        const bool in = live[i] && (int64_t)t * BN_TILE + (int64_t)lane * 4 < K;
-        if (!in) w01 = 0u, w23 = 0u;
+        decode4(rw0[i], cd0[i], lut_lane, w01, w23);
+        if ((fmask >> i) & 1u) apply_escapes(cd0[i], a.w.esc, epos[i], lt, w01, w23);
+        if (!(live[i] && col_in)) w01 = 0u, w23 = 0u;
         asm volatile("st.shared.v2.u32 [%0], {%1, %2};" ::"r"(a_s + swz(r0 + i, chunk)), "r"(w01), "r"(w23) : "memory");
-      }
-      const uint32_t b_s = b_at + (uint32_t)s * b_stage;
-#pragma unroll
-      for (int j = 0; j < XP; j++) {
-        const uint32_t idx = xi0 + j * (MMA_DECODE_WARPS * 32), m = idx >> 4, c = idx & 15u;
-        if ((int)m < a.M) asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(b_s + (c >> 3) * ((uint32_t)BN * 128u) + swz(m, c & 7u)), "r"(xp[j].x), "r"(xp[j].y), "r"(xp[j].z), "r"(xp[j].w) : "memory");
       }
       fence_async_smem();  // the tensor core reads shared memory through the async proxy
       __syncwarp();
       if (lane == 0) mm_bar_arrive(full + 8 * s);
 #pragma unroll
-      for (int i = 0; i < RPW; i++) rw[i] = rw_n[i], cd[i] = cd_n[i];
-#pragma unroll
-      for (int j = 0; j < XP; j++) xp[j] = xp_n[j];
-      flag = flag_n;
+      for (int i = 0; i < RPW; i++) rw0[i] = rw1[i], cd0[i] = cd1[i], rw1[i] = rw2[i], cd1[i] = cd2[i];
+      fl0 = fl1, fl1 = fl2;
     }
-  } else {
-    // ---------------------------------------------------------------- MMA issue (one thread)
+  } else if (warp == MMA_DECODE_WARPS) {
+    // ---------------------------------------------------------------- TMA for X, MMA issue
     const uint32_t idesc = mma_idesc(MMA_BM, BN);
+    auto fetch_x = [&](int t) {  // stage t % S must be free
+      const int s = t % S;
+      const uint32_t b_s = b_at + (uint32_t)s * b_stage;
+      mm_bar_expect_tx(full + 8 * s, b_stage);
+      tma_load_2d(b_s, &x_map, t * MMA_BK, 0, full + 8 * s);
+      tma_load_2d(b_s + (uint32_t)BN * 128u, &x_map, t * MMA_BK + 64, 0, full + 8 * s);
+    };
+    if (lane == 0)
+      for (int t = 0; t < S && t < T; t++) fetch_x(t);
+    __syncwarp();
     for (int t = 0; t < T; t++) {
       const int s = t % S;
       if (ok) ok = mm_bar_wait(full + 8 * s, (t / S) & 1);
@@ -214,6 +218,12 @@ __global__ void __launch_bounds__(MMA_THREADS, 1) r4_mma_kernel(MmaArgs a) {
         mma_commit(empty + 8 * s);  // arrives when these MMAs have read the stage
       }
       __syncwarp();
+      // the X tile of stage t + S goes into the slot as soon as these MMAs are through with it
+      if (t + S < T) {
+        if (ok) ok = mm_bar_wait(empty + 8 * s, (t / S) & 1);
+        if (lane == 0 && ok) fetch_x(t + S);
+        __syncwarp();
+      }
     }
     if (lane == 0 && ok) mma_commit(done);
     __syncwarp();
@@ -223,7 +233,7 @@ __global__ void __launch_bounds__(MMA_THREADS, 1) r4_mma_kernel(MmaArgs a) {
   if (warp < 4) {
     if (ok) ok = mm_bar_wait(done, 0);
     tc_fence_after();
-    const int64_t n = row_base + warp * 32 + lane;  // TMEM lane 32 * warp + lane = weight row
+    const int r = (int)(warp * 32 + lane);  // TMEM lane = weight row of the block
     if (ok) {
       for (int c = 0; c < BN; c += 8) {
         uint32_t v[8];
@@ -233,7 +243,7 @@ __global__ void __launch_bounds__(MMA_THREADS, 1) r4_mma_kernel(MmaArgs a) {
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
         for (int i = 0; i < 8; i++)
-          if (c + i < a.M && n < a.N) a.y[(int64_t)(c + i) * a.y_stride + n] = f32_to_bf16_bits(__uint_as_float(v[i]));
+          if (c + i < a.M && r < rows) a.y[(int64_t)(c + i) * a.y_stride + row_base + r] = f32_to_bf16_bits(__uint_as_float(v[i]));
       }
     }
   }
@@ -242,23 +252,60 @@ __global__ void __launch_bounds__(MMA_THREADS, 1) r4_mma_kernel(MmaArgs a) {
   if (warp == MMA_DECODE_WARPS) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(a.tmem_cols) : "memory");
 }
 
-// Fused decode GEMM for 16 <= M <= 128 input rows; -1 when the shape is outside its coverage.
+typedef CUresult (*TensorMapEncodeFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static TensorMapEncodeFn tensor_map_encoder() {
+  static TensorMapEncodeFn fn = nullptr;
+  if (!fn) {
+    void *p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess) fn = (TensorMapEncodeFn)p;
+  }
+  return fn;
+}
+
+static int mma_sms() {
+  static int n = 0;
+  if (!n) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    if (n <= 0) n = 148;
+  }
+  return n;
+}
+
+// Fused decode GEMM for up to 128 input rows; -1 when the shape is outside its coverage.
 int mma_rows(const bn_r4 *w, const uint16_t *x, int64_t x_stride, int64_t M, int64_t N, int64_t K, uint16_t *y, int64_t y_stride, cudaStream_t s) {
-  if (M < 1 || M > MMA_BM || K % 8 || x_stride % 8 || N < 1) return -1;
+  if (M < 1 || M > 128 || K % 8 || x_stride % 8 || N < 1 || ((uintptr_t)x & 15)) return -1;
+  TensorMapEncodeFn encode = tensor_map_encoder();
+  if (!encode) return fail(BN_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
   MmaArgs a{};
-  a.w = *w, a.x = x, a.y = y, a.N = N, a.K = K, a.x_stride = x_stride, a.y_stride = y_stride;
+  a.w = *w, a.y = y, a.N = N, a.K = K, a.y_stride = y_stride;
   a.T = (int)tiles(K), a.M = (int)M, a.BN = (int)((M + 15) / 16 * 16);
   a.tmem_cols = 32;
   while ((int)a.tmem_cols < a.BN) a.tmem_cols *= 2;
+  // an equal share of the rows for every SM, in whole warps' worth of rows
+  int64_t rows = (N + mma_sms() - 1) / mma_sms();
+  rows = (rows + MMA_RPW - 1) / MMA_RPW * MMA_RPW;
+  if (rows > MMA_ROWS) rows = MMA_ROWS;
+  a.rows = (int)rows;
   const uint32_t fixed = 1024 + LUT_WORDS * 4 + 256;  // alignment slack, pair table, barriers
   const uint32_t per_stage = MMA_A_STAGE + (uint32_t)a.BN * MMA_BK * 2u;
   int stages = (int)((MMA_SMEM_MAX - fixed) / per_stage);
   if (stages > 4) stages = 4;
   if (stages < 2) return -1;
   a.stages = stages;
+  // X as a 2-D tensor [M rows, K columns] of BF16; a box is 64 columns (one 128-byte swizzled row
+  // each) of BN rows; rows past M and columns past K read as zeros
+  CUtensorMap x_map;
+  const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)M}, strides[1] = {(cuuint64_t)x_stride * 2};
+  const cuuint32_t box[2] = {64, (cuuint32_t)a.BN}, elem[2] = {1, 1};
+  if (encode(&x_map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<uint16_t *>(x), dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+    return fail(BN_ERR_CUDA, "cuTensorMapEncodeTiled failed for the input rows");
   const uint32_t smem = fixed + (uint32_t)stages * per_stage;
   BN_CUDA(allow_smem(r4_mma_kernel, smem));
-  r4_mma_kernel<<<(unsigned)((N + MMA_BM - 1) / MMA_BM), MMA_THREADS, smem, s>>>(a);
+  r4_mma_kernel<<<(unsigned)((N + rows - 1) / rows), MMA_THREADS, smem, s>>>(x_map, a);
   return launched("r4_mma_kernel");
 }
 
