@@ -410,7 +410,9 @@ def run_ours(args) -> dict | None:
         note(f"decode leg done: R4 {decode['r4_tok_s']} tok/s, BF16 {decode['bf16_tok_s']} tok/s")
     # ---- the other two configurations, single GPU only (no collective in them)
     prefill = moe_leg = None
-    if world == 1 and not args.quick:
+    if world == 1 and args.prefill_rows:
+        prefill, moe_leg = prefill_leg(torch, dev, graph_us, rows=tuple(int(v) for v in args.prefill_rows.split(","))), None
+    elif world == 1 and not args.quick:
         prefill, moe_leg = prefill_leg(torch, dev, graph_us), moe_path_leg(torch, dev, graph_us)
         note("prefill and MoE legs done")
     if rank != 0:
@@ -457,7 +459,7 @@ def run_ours(args) -> dict | None:
     return result
 
 
-def prefill_leg(torch, dev, graph_us) -> dict:
+def prefill_leg(torch, dev, graph_us, rows=(2, 4, 8, 16, 32, 128, 2048)) -> dict:
     """Fused decode products for short prompts on the gate projection (15360 x 3840): M rows of
     N(0,1) inputs; up to FUSED_MAX_ROWS rows run the fused kernel in the documented order, up to
     MMA_MAX_ROWS the tensor-core decode GEMM (weights stream once in both), more rows rebuild the
@@ -470,7 +472,7 @@ def prefill_leg(torch, dev, graph_us) -> dict:
     w = ck.to_device(synthetic_weight("gate", n, k)).view(torch.bfloat16)
     m = r4.R4Linear(r4.from_dense(w))
     out = {}
-    for M in (2, 8, 16, 32, 128, 2048):
+    for M in rows:
         x = torch.randn((M, k), device=dev, generator=torch.Generator(device=dev).manual_seed(M)).to(torch.bfloat16)
         us = graph_us(lambda i: m(x), iters=10)
         us_ref = graph_us(lambda i: torch.matmul(x, w.T), iters=10)
@@ -513,6 +515,7 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-decode", action="store_true", help="skip the whole-model decode leg")
     ap.add_argument("--shapes", default="", help="comma list of matrices to keep (default: all seven); for small profiling runs")
+    ap.add_argument("--prefill-rows", default="", help="comma list of input row counts: run the prefill leg on just these (with --quick, for profiling runs)")
     ap.add_argument("--quick", action="store_true", help="timed region only: skip the per-shape, end-to-end and CPU legs")
     ap.add_argument("--outliers", type=float, default=OUTLIERS, help="fraction of weights scaled x64 (default: the benchmark's 0.1 %%)")
     ap.add_argument("--no-parity", action="store_true", help="skip the oracle check (only for kernel experiments whose output is wrong on purpose)")

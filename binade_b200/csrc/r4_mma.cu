@@ -144,44 +144,55 @@ __global__ void __launch_bounds__(MMA_THREADS, 1) r4_mma_kernel(const __grid_con
     constexpr int RPW = MMA_RPW;
     const uint32_t lut_lane = lut_at + lane * 4u;
     const uint32_t r0 = warp * RPW;
-    uint32_t epos[RPW];
-    bool live[RPW];
+    // A warp slot past the block's last row decodes that last row again (its MMA row is never
+    // stored), so the loop needs no per-row predicate. Row pointers are formed once.
+    uint32_t epos[RPW], a_off[RPW];
+    const uint8_t *rawp[RPW];
+    const uint16_t *codp[RPW];
 #pragma unroll
     for (int i = 0; i < RPW; i++) {
-      live[i] = (int)(r0 + i) < rows;
-      epos[i] = live[i] ? a.w.row_esc[row_base + r0 + i] : 0u;
+      const int64_t r = row_base + min((int)(r0 + i), rows - 1);
+      epos[i] = a.w.row_esc[r];
+      rawp[i] = a.w.raw + r * K + lane * 4;
+      codp[i] = a.w.codes + r * T * 32 + lane;
+      a_off[i] = (lane >> 4) * (MMA_BM * 128u) + (lane & 1u) * 8u + swz(r0 + i, (lane & 15u) >> 1);
     }
+    const uint8_t *flagp = a.w.flags + (row_base + min((int)(r0 + (lane & (RPW - 1))), rows - 1)) * T;
+    // a row's last tile may be partial (K % 128 != 0): lanes past the row's end read nothing and
+    // store zeros (the matching columns of X arrive as zeros, but 0 x Inf must not happen)
+    const bool in_last = (int64_t)(T - 1) * BN_TILE + (int64_t)lane * 4 < K;
     auto load_stage = [&](int t, uint32_t (&rw)[RPW], uint32_t (&cd)[RPW], uint32_t &flag) {
-      const bool col_in = t < T && (int64_t)t * BN_TILE + (int64_t)lane * 4 < K;  // K % 4 == 0
+      if (t < T) {
+        const bool in = t < T - 1 || in_last;
 #pragma unroll
-      for (int i = 0; i < RPW; i++) {
-        const int64_t r = row_base + r0 + i;
-        rw[i] = (live[i] && col_in) ? ldg_stream_u32(a.w.raw + r * K + (int64_t)t * BN_TILE + lane * 4) : 0u;
-        cd[i] = (live[i] && t < T) ? ldg_stream_u16(a.w.codes + (r * T + t) * 32 + lane) : 0u;
+        for (int i = 0; i < RPW; i++) {
+          rw[i] = in ? ldg_stream_u32(rawp[i] + t * BN_TILE) : 0u;
+          cd[i] = ldg_stream_u16(codp[i] + t * 32);
+        }
+        flag = lane < RPW ? (uint32_t)flagp[t] : 0u;
       }
-      flag = (t < T && lane < RPW && (int)(r0 + lane) < rows) ? (uint32_t)a.w.flags[(row_base + r0 + lane) * T + t] : 0u;
     };
     // raw bytes, codes and flags of the next two stages wait in registers
-    uint32_t rw0[RPW], cd0[RPW], fl0, rw1[RPW], cd1[RPW], fl1;
+    uint32_t rw0[RPW] = {}, cd0[RPW] = {}, fl0 = 0, rw1[RPW] = {}, cd1[RPW] = {}, fl1 = 0;
     load_stage(0, rw0, cd0, fl0);
     load_stage(1, rw1, cd1, fl1);
+    int s = 0;
+    uint32_t ph = 1;  // parity of the `empty` phase that frees slot s (first pass: slots start free)
     for (int t = 0; t < T; t++) {
-      const int s = t % S;
-      uint32_t rw2[RPW], cd2[RPW], fl2;
+      uint32_t rw2[RPW] = {}, cd2[RPW] = {}, fl2 = 0;
       load_stage(t + 2, rw2, cd2, fl2);
-      if (t >= S && ok) ok = mm_bar_wait(empty + 8 * s, ((t / S) - 1) & 1);
+      if (t >= S && ok) ok = mm_bar_wait(empty + 8 * s, ph);
       tc_fence_after();
       const uint32_t fmask = __ballot_sync(BN_FULL, fl0 != 0);
-      const uint32_t a_s = a_at + (uint32_t)s * MMA_A_STAGE + (lane >> 4) * (MMA_BM * 128u) + (lane & 1u) * 8u;
-      const uint32_t chunk = (lane & 15u) >> 1;
-      const bool col_in = (int64_t)t * BN_TILE + (int64_t)lane * 4 < K;
+      const uint32_t a_s = a_at + (uint32_t)s * MMA_A_STAGE;
+      const bool zero = t == T - 1 && !in_last;
 #pragma unroll
       for (int i = 0; i < RPW; i++) {
         uint32_t w01, w23;
         decode4(rw0[i], cd0[i], lut_lane, w01, w23);
         if ((fmask >> i) & 1u) apply_escapes(cd0[i], a.w.esc, epos[i], lt, w01, w23);
-        if (!(live[i] && col_in)) w01 = 0u, w23 = 0u;
-        asm volatile("st.shared.v2.u32 [%0], {%1, %2};" ::"r"(a_s + swz(r0 + i, chunk)), "r"(w01), "r"(w23) : "memory");
+        if (zero) w01 = 0u, w23 = 0u;
+        asm volatile("st.shared.v2.u32 [%0], {%1, %2};" ::"r"(a_s + a_off[i]), "r"(w01), "r"(w23) : "memory");
       }
       fence_async_smem();  // the tensor core reads shared memory through the async proxy
       __syncwarp();
@@ -189,23 +200,24 @@ __global__ void __launch_bounds__(MMA_THREADS, 1) r4_mma_kernel(const __grid_con
 #pragma unroll
       for (int i = 0; i < RPW; i++) rw0[i] = rw1[i], cd0[i] = cd1[i], rw1[i] = rw2[i], cd1[i] = cd2[i];
       fl0 = fl1, fl1 = fl2;
+      if (++s == S) s = 0, ph ^= 1u;
     }
   } else if (warp == MMA_DECODE_WARPS) {
     // ---------------------------------------------------------------- TMA for X, MMA issue
     const uint32_t idesc = mma_idesc(MMA_BM, BN);
-    auto fetch_x = [&](int t) {  // stage t % S must be free
-      const int s = t % S;
+    auto fetch_x = [&](int t, int s) {  // X tile of k-tile t into slot s, which must be free
       const uint32_t b_s = b_at + (uint32_t)s * b_stage;
       mm_bar_expect_tx(full + 8 * s, b_stage);
       tma_load_2d(b_s, &x_map, t * MMA_BK, 0, full + 8 * s);
       tma_load_2d(b_s + (uint32_t)BN * 128u, &x_map, t * MMA_BK + 64, 0, full + 8 * s);
     };
     if (lane == 0)
-      for (int t = 0; t < S && t < T; t++) fetch_x(t);
+      for (int t = 0; t < S && t < T; t++) fetch_x(t, t);
     __syncwarp();
+    int s = 0, sp = 0;        // slot of tile t, slot of tile t - 1
+    uint32_t ph = 0, php = 0;  // parity of their current phases
     for (int t = 0; t < T; t++) {
-      const int s = t % S;
-      if (ok) ok = mm_bar_wait(full + 8 * s, (t / S) & 1);
+      if (ok) ok = mm_bar_wait(full + 8 * s, ph);
       tc_fence_after();
       if (lane == 0 && ok) {
         const uint32_t a_s = a_at + (uint32_t)s * MMA_A_STAGE, b_s = b_at + (uint32_t)s * b_stage;
@@ -218,12 +230,16 @@ __global__ void __launch_bounds__(MMA_THREADS, 1) r4_mma_kernel(const __grid_con
         mma_commit(empty + 8 * s);  // arrives when these MMAs have read the stage
       }
       __syncwarp();
-      // the X tile of stage t + S goes into the slot as soon as these MMAs are through with it
-      if (t + S < T) {
-        if (ok) ok = mm_bar_wait(empty + 8 * s, (t / S) & 1);
-        if (lane == 0 && ok) fetch_x(t + S);
+      // The slot of the previous tile takes the X tile that will use it next. Waiting for that
+      // tile's MMAs here costs nothing (they were issued a whole stage ago), whereas waiting for
+      // the MMAs just issued would put their latency between every two stages.
+      if (t >= 1 && t - 1 + S < T) {
+        if (ok) ok = mm_bar_wait(empty + 8 * sp, php);
+        if (lane == 0 && ok) fetch_x(t - 1 + S, sp);
         __syncwarp();
       }
+      sp = s, php = ph;
+      if (++s == S) s = 0, ph ^= 1u;
     }
     if (lane == 0 && ok) mma_commit(done);
     __syncwarp();
