@@ -6,7 +6,7 @@
 //   B operand  BN = M rounded up to 16 input rows x 128 k, brought in by TMA (2-D tensor map over
 //              X with the same swizzle; rows past M and columns past K arrive as zeros)
 //   D          128 x BN fp32 accumulators in tensor memory (TMEM), read back with tcgen05.ld
-// One block per SM, each with an equal share of the weight rows. 28 warps decode (4 rows each
+// One block per SM, each with an equal share of the weight rows. 14 warps decode (8 rows each
 // per stage: a weight row stays with one warp, so its escape cursor is a register; raw bytes and
 // codes are fetched two stages ahead into registers), one warp issues the TMA copies and the
 // MMAs; a ring of stages (mbarriers: `full` armed by the decoders and the TMA bytes, `empty` by
@@ -18,16 +18,16 @@
 // Every wait is bounded: when one gives up, a status flag is set, every thread still reaches the
 // end of the kernel, and the tensor memory is released.
 #include <cuda.h>
+#include <stdio.h>
+#include <stdlib.h>
 
 #include "common.cuh"
 #include "decode.cuh"
 
 namespace bn {
 
-constexpr int MMA_DECODE_WARPS = 28;
-constexpr int MMA_RPW = 4;                                  // weight rows per decode warp and stage
-constexpr int MMA_ROWS = MMA_DECODE_WARPS * MMA_RPW;        // most weight rows a block takes (112)
-constexpr int MMA_THREADS = (MMA_DECODE_WARPS + 1) * 32;
+constexpr int MMA_DECODE_WARPS = 14;  // decode warps of the shape used (measured: 14 x 8 rows 46 us, 28 x 4 rows 55 us on 15360 x 3840)
+constexpr int MMA_RPW = 8;            // weight rows per decode warp and stage
 constexpr int MMA_BM = 128;                  // MMA M: rows of the A tile (the block's rows, then unused)
 constexpr int MMA_BK = 128;                  // k per stage: one R4 tile
 constexpr uint32_t MMA_A_STAGE = MMA_BM * MMA_BK * 2;  // 32 KB: two 64-k atoms of 128 rows x 128 B
@@ -104,7 +104,12 @@ struct MmaArgs {
 // Byte offset of (row r, 16-byte chunk c of the row's 128 bytes) inside a swizzled atom.
 __device__ __forceinline__ uint32_t swz(uint32_t r, uint32_t c) { return r * 128u + ((c ^ (r & 7u)) << 4); }
 
-__global__ void __launch_bounds__(MMA_THREADS, 1) r4_mma_kernel(const __grid_constant__ CUtensorMap x_map, MmaArgs a) {
+// DW decode warps (plus the MMA warp), RPW weight rows per decode warp and stage: a block takes
+// up to DW * RPW <= 128 weight rows.
+template <int DW, int RPWT>
+__global__ void __launch_bounds__((DW + 1) * 32, 1) r4_mma_kernel(const __grid_constant__ CUtensorMap x_map, MmaArgs a) {
+  constexpr int MMA_DECODE_WARPS = DW, MMA_RPW = RPWT;
+  static_assert(DW * RPWT <= MMA_BM, "a block's rows are the MMA's M");
   extern __shared__ uint8_t mma_smem[];
   const uint32_t lane = lane_id(), warp = threadIdx.x >> 5, lt = lanemask_lt();
   const int T = a.T, S = a.stages, BN = a.BN;
@@ -146,18 +151,20 @@ __global__ void __launch_bounds__(MMA_THREADS, 1) r4_mma_kernel(const __grid_con
     const uint32_t r0 = warp * RPW;
     // A warp slot past the block's last row decodes that last row again (its MMA row is never
     // stored), so the loop needs no per-row predicate. Row pointers are formed once.
-    uint32_t epos[RPW], a_off[RPW];
-    const uint8_t *rawp[RPW];
-    const uint16_t *codp[RPW];
+    // (32-bit offsets from the block's first row: a block spans at most 112 rows.)
+    uint32_t epos[RPW], a_off[RPW], raw_off[RPW], cod_off[RPW];
+    const uint8_t *const raw_blk = a.w.raw + row_base * K;
+    const uint16_t *const cod_blk = a.w.codes + row_base * T * 32;
+    const uint8_t *const flag_blk = a.w.flags + row_base * T;
 #pragma unroll
     for (int i = 0; i < RPW; i++) {
-      const int64_t r = row_base + min((int)(r0 + i), rows - 1);
-      epos[i] = a.w.row_esc[r];
-      rawp[i] = a.w.raw + r * K + lane * 4;
-      codp[i] = a.w.codes + r * T * 32 + lane;
+      const uint32_t r = (uint32_t)min((int)(r0 + i), rows - 1);
+      epos[i] = a.w.row_esc[row_base + r];
+      raw_off[i] = r * (uint32_t)K + lane * 4u;
+      cod_off[i] = r * (uint32_t)T * 32u + lane;
       a_off[i] = (lane >> 4) * (MMA_BM * 128u) + (lane & 1u) * 8u + swz(r0 + i, (lane & 15u) >> 1);
     }
-    const uint8_t *flagp = a.w.flags + (row_base + min((int)(r0 + (lane & (RPW - 1))), rows - 1)) * T;
+    const uint32_t flag_off = (uint32_t)min((int)(r0 + (lane < RPW ? lane : 0u)), rows - 1) * (uint32_t)T;
     // a row's last tile may be partial (K % 128 != 0): lanes past the row's end read nothing and
     // store zeros (the matching columns of X arrive as zeros, but 0 x Inf must not happen)
     const bool in_last = (int64_t)(T - 1) * BN_TILE + (int64_t)lane * 4 < K;
@@ -166,10 +173,10 @@ __global__ void __launch_bounds__(MMA_THREADS, 1) r4_mma_kernel(const __grid_con
         const bool in = t < T - 1 || in_last;
 #pragma unroll
         for (int i = 0; i < RPW; i++) {
-          rw[i] = in ? ldg_stream_u32(rawp[i] + t * BN_TILE) : 0u;
-          cd[i] = ldg_stream_u16(codp[i] + t * 32);
+          rw[i] = in ? ldg_stream_u32(raw_blk + (raw_off[i] + (uint32_t)t * BN_TILE)) : 0u;
+          cd[i] = ldg_stream_u16(cod_blk + (cod_off[i] + (uint32_t)t * 32u));
         }
-        flag = lane < RPW ? (uint32_t)flagp[t] : 0u;
+        flag = lane < RPW ? (uint32_t)flag_blk[flag_off + (uint32_t)t] : 0u;
       }
     };
     // raw bytes, codes and flags of the next two stages wait in registers
@@ -302,9 +309,11 @@ int mma_rows(const bn_r4 *w, const uint16_t *x, int64_t x_stride, int64_t M, int
   a.tmem_cols = 32;
   while ((int)a.tmem_cols < a.BN) a.tmem_cols *= 2;
   // an equal share of the rows for every SM, in whole warps' worth of rows
+  int dw = MMA_DECODE_WARPS, rpw = MMA_RPW;
+  if (const char *e = getenv("BINADE_B200_MMA_SHAPE")) sscanf(e, "%dx%d", &dw, &rpw);  // experiments only
   int64_t rows = (N + mma_sms() - 1) / mma_sms();
-  rows = (rows + MMA_RPW - 1) / MMA_RPW * MMA_RPW;
-  if (rows > MMA_ROWS) rows = MMA_ROWS;
+  rows = (rows + rpw - 1) / rpw * rpw;
+  if (rows > dw * rpw) rows = dw * rpw;
   a.rows = (int)rows;
   const uint32_t fixed = 1024 + LUT_WORDS * 4 + 256;  // alignment slack, pair table, barriers
   const uint32_t per_stage = MMA_A_STAGE + (uint32_t)a.BN * MMA_BK * 2u;
@@ -320,9 +329,20 @@ int mma_rows(const bn_r4 *w, const uint16_t *x, int64_t x_stride, int64_t M, int
   if (encode(&x_map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<uint16_t *>(x), dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
     return fail(BN_ERR_CUDA, "cuTensorMapEncodeTiled failed for the input rows");
   const uint32_t smem = fixed + (uint32_t)stages * per_stage;
-  BN_CUDA(allow_smem(r4_mma_kernel, smem));
-  r4_mma_kernel<<<(unsigned)((N + rows - 1) / rows), MMA_THREADS, smem, s>>>(x_map, a);
-  return launched("r4_mma_kernel");
+  const unsigned grid = (unsigned)((N + rows - 1) / rows);
+#define BN_MMA_LAUNCH(DW, RPW)                                                        \
+  if (dw == DW && rpw == RPW) {                                                       \
+    BN_CUDA(allow_smem(r4_mma_kernel<DW, RPW>, smem));                                \
+    r4_mma_kernel<DW, RPW><<<grid, (DW + 1) * 32, smem, s>>>(x_map, a);               \
+    return launched("r4_mma_kernel");                                                 \
+  }
+  BN_MMA_LAUNCH(28, 4)
+  BN_MMA_LAUNCH(24, 5)
+  BN_MMA_LAUNCH(20, 6)
+  BN_MMA_LAUNCH(16, 7)
+  BN_MMA_LAUNCH(14, 8)
+#undef BN_MMA_LAUNCH
+  return -1;
 }
 
 int mma_status(int *status) {
