@@ -1,0 +1,103 @@
+// All-gather of small output slices over NVLink peer memory, as one kernel per rank: every rank
+// stores its slice straight into every peer's buffer (plain peer stores, no TMA, no multicast),
+// raises a flag there, and waits for the peers' flags. For the few KB a row-sharded matvec
+// produces, the cost is two flag round trips instead of a library collective's launch latency.
+//
+// Each rank owns one symmetric buffer (the same layout on every rank, mapped on all of them):
+//   [0, 32)    enter[src]  u32: rank src has entered exchange number enter[src]
+//   [32, 64)   done[src]   u32: rank src's slice of exchange number done[src] has landed here
+//   [256, ...) data: world slices of `bytes` bytes, slice r written by rank r
+// Protocol of exchange number q (a per-rank counter in device memory, so a captured graph can
+// replay the launch): (1) tell every peer "I am in q" and wait until every peer is: its readers
+// of exchange q - 1 ran before this kernel in stream order, so the single data area may be
+// overwritten; (2) store the slice into every peer's data area, fence, tell every peer "done q",
+// wait for every peer's done q. Every wait is bounded: on giving up the kernel sets a status flag
+// and returns (the output is then invalid, the context stays usable).
+#include "common.cuh"
+
+namespace bn {
+
+constexpr int XCH_MAX_RANKS = 8;
+constexpr uint32_t XCH_DATA_OFFSET = 256;
+constexpr uint32_t XCH_SPIN_LIMIT = 1u << 24;
+
+__device__ int g_exchange_error;
+
+struct PushArgs {
+  uint8_t *peer[XCH_MAX_RANKS];  // every rank's symmetric buffer, as mapped on this GPU
+  const uint8_t *local;
+  uint64_t bytes;
+  uint32_t *counter;
+  int rank, world;
+};
+
+__device__ __forceinline__ void st_release_sys(uint32_t *p, uint32_t v) { asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory"); }
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t *p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+// Waits until *p has reached `want` (counters only grow; the difference is taken modulo 2^32).
+__device__ __forceinline__ bool wait_reached(const uint32_t *p, uint32_t want) {
+  for (uint32_t i = 0; i < XCH_SPIN_LIMIT; i++)
+    if ((int32_t)(ld_acquire_sys(p) - want) >= 0) return true;
+  atomicExch(&g_exchange_error, 1);
+  return false;
+}
+
+__global__ void __launch_bounds__(1024, 1) push_gather_kernel(PushArgs a) {
+  __shared__ uint32_t s_seq;
+  __shared__ int s_ok;
+  if (threadIdx.x == 0) {
+    s_seq = *a.counter + 1;  // launches of one exchange object are ordered by their stream
+    *a.counter = s_seq;
+    s_ok = 1;
+  }
+  __syncthreads();
+  const uint32_t seq = s_seq;
+  uint32_t *const mine = reinterpret_cast<uint32_t *>(a.peer[a.rank]);
+  if ((int)threadIdx.x < a.world) {
+    st_release_sys(reinterpret_cast<uint32_t *>(a.peer[threadIdx.x]) + a.rank, seq);  // enter[rank] on peer
+    if (!wait_reached(mine + threadIdx.x, seq)) s_ok = 0;
+  }
+  __syncthreads();
+  if (!s_ok) return;
+  // the slice into every peer's data area (own buffer included), 16 bytes per store
+  const uint64_t n16 = a.bytes / 16;
+  const uint4 *src = reinterpret_cast<const uint4 *>(a.local);
+  for (uint64_t i = threadIdx.x; i < n16; i += blockDim.x) {
+    const uint4 v = src[i];
+    for (int p = 0; p < a.world; p++) {
+      const int q = (a.rank + p) % a.world;  // start with the own buffer, then round the ring
+      reinterpret_cast<uint4 *>(a.peer[q] + XCH_DATA_OFFSET + (uint64_t)a.rank * a.bytes)[i] = v;
+    }
+  }
+  __threadfence_system();
+  __syncthreads();
+  if ((int)threadIdx.x < a.world) {
+    st_release_sys(reinterpret_cast<uint32_t *>(a.peer[threadIdx.x]) + 8 + a.rank, seq);  // done[rank] on peer
+    wait_reached(mine + 8 + threadIdx.x, seq);
+  }
+  __syncthreads();
+}
+
+int exchange_status(int *status) {
+  BN_CUDA(cudaMemcpyFromSymbol(status, g_exchange_error, sizeof(int)));
+  return BN_OK;
+}
+
+}  // namespace bn
+
+extern "C" int bn_push_gather(const void *local, uint64_t bytes, const uint64_t *peers, int rank, int world, uint32_t *counter, void *stream) {
+  if (!local || !peers || !counter || world < 1 || world > bn::XCH_MAX_RANKS || rank < 0 || rank >= world) return bn::fail(BN_ERR_ARG, "bn_push_gather: bad rank, world (1..8) or null pointer");
+  if ((uintptr_t)local % 16 || bytes % 16) return bn::fail(BN_ERR_ARG, "bn_push_gather: the slice must be 16-byte aligned and a multiple of 16 bytes");
+  if (bytes == 0) return BN_OK;
+  bn::PushArgs a{};
+  for (int r = 0; r < world; r++) {
+    if (!peers[r]) return bn::fail(BN_ERR_ARG, "bn_push_gather: null peer buffer");
+    a.peer[r] = reinterpret_cast<uint8_t *>(peers[r]);
+  }
+  a.local = static_cast<const uint8_t *>(local), a.bytes = bytes, a.counter = counter, a.rank = rank, a.world = world;
+  bn::push_gather_kernel<<<1, 1024, 0, (cudaStream_t)stream>>>(a);
+  return bn::launched("push_gather_kernel");
+}

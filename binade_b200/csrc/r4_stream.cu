@@ -554,9 +554,10 @@ int stream_rows(const bn_r4 *w, const uint16_t *x, int64_t x_stride, int64_t M, 
 
 extern "C" int bn_device_status(int *status) {
   if (!status) return bn::fail(BN_ERR_ARG, "bn_device_status: null pointer");
-  int stream = 0, mma = 0;
+  int stream = 0, mma = 0, xch = 0;
   BN_CUDA(cudaMemcpyFromSymbol(&stream, bn::g_stream_error, sizeof(int)));
   if (int e = bn::mma_status(&mma)) return e;
-  *status = stream | (mma << 8);
+  if (int e = bn::exchange_status(&xch)) return e;
+  *status = stream | (mma << 8) | (xch << 16);
   return BN_OK;
 }

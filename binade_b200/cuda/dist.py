@@ -8,6 +8,12 @@ reference is single-device; this module is the multi-GPU form of its linear-laye
   shard_packed(p, rank, world)     format-2 arrays of those rows only (what a rank loads and expands)
   shard_r4(a, rank, world)         the same cut on an R4 dict that is already expanded
   RowShardedLinear(local, N, ...)  y = all_gather(local(x)) over the process group
+  RowShardedGroup(locals, Ns, ...) several projections of the same input (q, k, v; gate, up)
+                                   with one all-gather for all of them
+
+  PushGather(group, max_bytes)     the all-gather as one kernel of this library over NVLink peer
+                                   memory (symmetric buffers from torch.distributed); the sharded
+                                   modules take it as `exchange=` in place of the NCCL call
 
 The cuts are pure index arithmetic on numpy arrays or torch tensors of any device; only
 RowShardedLinear.forward touches a process group.
@@ -75,17 +81,86 @@ def shard_r4(a: dict, rank: int, world: int) -> dict:
     }
 
 
+class PushGather:
+    """All-gather of small slices by peer stores (bn_push_gather): every rank writes its slice
+    into every peer's symmetric buffer and the ranks meet on flags, in one kernel launch per rank
+    and call. torch.distributed's symmetric memory allocates and maps the buffers (plumbing); the
+    kernel is this library's. Needs CUDA ranks of one node with peer access; at most 8 ranks.
+
+        ex = PushGather(group, max_bytes)   # collective: every rank of the group
+        out = ex(flat)                      # flat [M, W] on this rank -> [world, M, W]
+
+    `out` is a view of this rank's buffer: it is overwritten by the next call, which every rank
+    enters only after its own readers of the previous result (stream order). Safe to capture in a
+    CUDA graph (the call number lives in device memory)."""
+
+    HEADER = 256
+
+    def __init__(self, group=None, max_bytes: int = 1 << 20):
+        import ctypes
+
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm_mem
+
+        group = group if group is not None else dist.group.WORLD
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        if self.world > 8:
+            raise ValueError("PushGather serves at most 8 ranks")
+        self.cap = (max_bytes + 15) // 16 * 16
+        dev = torch.device("cuda", torch.cuda.current_device())
+        self.buf = symm_mem.empty(self.HEADER + self.world * self.cap, dtype=torch.uint8, device=dev)
+        self.buf.zero_()
+        self.handle = symm_mem.rendezvous(self.buf, group)
+        self.peers = (ctypes.c_uint64 * self.world)(*[int(p) for p in self.handle.buffer_ptrs])
+        self.counter = torch.zeros(1, dtype=torch.int32, device=dev)
+        torch.cuda.synchronize()
+        dist.barrier(group)  # every buffer is zeroed before anyone's first flag arrives
+
+    def __call__(self, flat: torch.Tensor) -> torch.Tensor:
+        from .kernels import _call, _p
+
+        flat = flat.contiguous()
+        nbytes = flat.numel() * flat.element_size()
+        padded = (nbytes + 15) // 16 * 16
+        if padded > self.cap:
+            raise ValueError(f"slice of {nbytes} bytes exceeds the exchange's {self.cap}")
+        if padded != nbytes or flat.data_ptr() % 16:
+            stage = torch.zeros(padded, dtype=torch.uint8, device=flat.device)
+            stage[:nbytes] = flat.reshape(-1).view(torch.uint8)
+            src = stage
+        else:
+            src = flat
+        import ctypes
+
+        _call("bn_push_gather", _p(src), padded, ctypes.cast(self.peers, ctypes.c_void_p), self.rank, self.world, _p(self.counter))
+        data = self.buf[self.HEADER : self.HEADER + self.world * padded].view(self.world, padded)[:, :nbytes]
+        return data.reshape(self.world, nbytes).view(flat.dtype).view(self.world, *flat.shape)
+
+
+def _all_gather(flat: torch.Tensor, world: int, group, exchange) -> torch.Tensor:
+    """[M, W] on every rank -> [world, M, W], by the peer-store kernel when an exchange is given,
+    else by NCCL / gloo."""
+    if exchange is not None:
+        return exchange(flat)
+    import torch.distributed as dist
+
+    out = torch.empty((world * flat.shape[0], flat.shape[1]), dtype=flat.dtype, device=flat.device)
+    dist.all_gather_into_tensor(out, flat.contiguous(), group=group)
+    return out.view(world, flat.shape[0], flat.shape[1])
+
+
 class RowShardedLinear(nn.Module):
     """y = x @ W.T with W's rows spread over the ranks of `group`: every rank multiplies by its
     own rows (`local`, e.g. an R4Linear over shard_r4 / a transcoded shard_packed) and the slices
     are gathered with one all-gather, in rank order = row order. Ranks may hold different row
     counts (N % world != 0): slices are then padded to the largest count for the collective."""
 
-    def __init__(self, local, N: int, group=None):
+    def __init__(self, local, N: int, group=None, exchange=None):
         super().__init__()
         self.local = local
         self.N = N
         self.group = group
+        self.exchange = exchange  # a PushGather, or None for the library collective
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         import torch.distributed as dist
@@ -102,9 +177,45 @@ class RowShardedLinear(nn.Module):
             y = torch.nn.functional.pad(y, (0, width - y.shape[-1]))
         lead = y.shape[:-1]
         flat = y.reshape(-1, width).contiguous()  # [M, width]
-        out = torch.empty((world * flat.shape[0], width), dtype=y.dtype, device=y.device)
-        dist.all_gather_into_tensor(out, flat, group=self.group)
-        out = out.view(world, flat.shape[0], width)
+        out = _all_gather(flat, world, self.group, self.exchange)
         if all(c == width for c in counts):
             return out.movedim(0, 1).reshape(*lead, world * width)
         return torch.cat([out[r, :, : counts[r]] for r in range(world)], dim=-1).reshape(*lead, self.N)
+
+
+class RowShardedGroup(nn.Module):
+    """Several row-sharded projections of the same input with ONE collective: every rank runs its
+    local modules, lays their output slices side by side, one all-gather moves them, and each
+    full output is cut back out in rank order = row order. This is how a decoder layer uses the
+    hook (q, k and v share their input, so do gate and up): the small-message latency of the
+    collective is paid once per group instead of once per projection. Every N must divide evenly
+    over the ranks. forward(x) returns the list of full outputs, bit-identical to what
+    RowShardedLinear gives for each projection alone."""
+
+    def __init__(self, locals_, Ns, group=None, exchange=None):
+        super().__init__()
+        self.exchange = exchange
+        locals_ = list(locals_)
+        self.locals = nn.ModuleList(locals_) if all(isinstance(m, nn.Module) for m in locals_) else locals_
+        self.Ns = list(Ns)
+        self.group = group
+
+    def forward(self, x: torch.Tensor):
+        import torch.distributed as dist
+
+        world = dist.get_world_size(self.group)
+        ys = [m(x) for m in self.locals]
+        if world == 1:
+            return ys
+        widths = [N // world for N in self.Ns]
+        for y, w, N in zip(ys, widths, self.Ns):
+            if N % world or y.shape[-1] != w:
+                raise ValueError(f"a projection of {N} rows does not split evenly over {world} ranks (local slice {y.shape[-1]})")
+        lead = ys[0].shape[:-1]
+        flat = torch.cat([y.reshape(-1, w) for y, w in zip(ys, widths)], dim=-1)  # [M, sum of widths]
+        out = _all_gather(flat, world, self.group, self.exchange)
+        res, c = [], 0
+        for w, N in zip(widths, self.Ns):
+            res.append(out[:, :, c : c + w].movedim(0, 1).reshape(*lead, N))
+            c += w
+        return res

@@ -109,6 +109,43 @@ def test_row_sharded_linear_two_gloo_ranks(tmp_path, N):
         assert np.array_equal(np.load(tmp_path / f"y{rank}.npy"), want), rank
 
 
+def _group_main(rank: int, world: int, port: int, out_dir: str):
+    import torch.distributed as dist
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    K, Ns = 128, (32, 8, 8)
+    x = _weights((3, K), seed=9)
+
+    def local_of(N, seed):
+        r0, r1 = bd.row_range(N, rank, world)
+        w_local = _weights((N, K), seed=seed)[r0:r1]
+
+        def local(xt):
+            y = o.c_dense_rows(xt.view(torch.int16).numpy().view(np.uint16).reshape(-1, K), w_local)
+            return torch.from_numpy(y.view(np.int16)).view(torch.bfloat16).reshape(*xt.shape[:-1], -1)
+
+        return local
+
+    g = bd.RowShardedGroup([local_of(N, 20 + i) for i, N in enumerate(Ns)], Ns)
+    ys = g(torch.from_numpy(x.view(np.int16)).view(torch.bfloat16))
+    for i, y in enumerate(ys):
+        np.save(os.path.join(out_dir, f"g{rank}_{i}.npy"), y.view(torch.int16).numpy().view(np.uint16))
+    dist.destroy_process_group()
+
+
+def test_row_sharded_group_two_gloo_ranks(tmp_path):
+    """Three projections of one input, one all-gather: every full output equals the unsharded
+    product on every rank."""
+    world = 2
+    mp.spawn(_group_main, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+    x = _weights((3, 128), seed=9)
+    for i, N in enumerate((32, 8, 8)):
+        want = o.c_dense_rows(x, _weights((N, 128), seed=20 + i))
+        for rank in range(world):
+            assert np.array_equal(np.load(tmp_path / f"g{rank}_{i}.npy"), want), (rank, i)
+
+
 def _ep_main(rank: int, world: int, port: int, out_dir: str):
     import torch.distributed as dist
 

@@ -80,3 +80,64 @@ def test_row_sharded_decoder_two_gpus(tmp_path):
         port = s.getsockname()[1]
     mp.spawn(_decoder_main, args=(2, port, str(tmp_path)), nprocs=2, join=True)
     assert [(tmp_path / f"ok{r}").read_text() for r in range(2)] == ["1", "1"]
+
+
+def _push_main(rank: int, world: int, port: int, out_dir: str):
+    import torch.distributed as dist
+
+    from binade_b200 import _native
+    from binade_b200.cuda import dist as bd
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    ex = bd.PushGather(max_bytes=1 << 16)
+    ok = True
+    g = torch.Generator(device="cuda").manual_seed(100 + rank)
+    for shape in ((1, 1920), (3, 200), (1, 8), (5, 33)):  # the last one needs padding to 16 bytes
+        flat = torch.randn(shape, device="cuda", generator=g).to(torch.bfloat16)
+        want = torch.empty((world * shape[0], shape[1]), dtype=torch.bfloat16, device="cuda")
+        dist.all_gather_into_tensor(want, flat)
+        got = ex(flat).clone()
+        ok = ok and torch.equal(got.view(torch.int16), want.view(world, *shape).view(torch.int16))
+    # a captured graph replays the exchange (the call number lives on the device)
+    flat = torch.full((1, 64), float(rank + 1), device="cuda", dtype=torch.bfloat16)
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(side):
+        ex(flat)
+        side.synchronize()
+        with torch.cuda.graph(graph, stream=side):
+            out = ex(flat).clone()
+    for i in range(3):
+        flat.fill_(float(10 * i + rank + 1))
+        graph.replay()
+        torch.cuda.synchronize()
+        ok = ok and all(bool((out[r] == 10 * i + r + 1).all()) for r in range(world))
+    # the grouped sharded hook over the exchange equals the NCCL one
+    locals_ = [lambda x, s=s: (x[..., : 16 * (s + 1)] * (rank + 1)).contiguous() for s in range(2)]
+    x = torch.randn((1, 64), device="cuda", generator=g).to(torch.bfloat16)
+    dist.broadcast(x, 0)
+    a = bd.RowShardedGroup(locals_, [16 * world, 32 * world], exchange=bd.PushGather(max_bytes=4096))(x)
+    b = bd.RowShardedGroup(locals_, [16 * world, 32 * world])(x)
+    ok = ok and all(torch.equal(p, q) for p, q in zip(a, b))
+    status = _native.C.c_int(-1)
+    _native.call("cuda", "bn_device_status", _native.C.byref(status))
+    ok = ok and status.value == 0
+    with open(os.path.join(out_dir, f"ok{rank}"), "w") as f:
+        f.write("1" if ok else "0")
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_push_gather_two_gpus(tmp_path):
+    """The peer-store all-gather kernel returns what NCCL's all-gather returns, also when
+    replayed from a CUDA graph and under the grouped sharded hook."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    mp.spawn(_push_main, args=(2, port, str(tmp_path)), nprocs=2, join=True)
+    assert [(tmp_path / f"ok{r}").read_text() for r in range(2)] == ["1", "1"]
