@@ -6,7 +6,9 @@
 // Each rank owns one symmetric buffer (the same layout on every rank, mapped on all of them):
 //   [0, 32)    enter[src]  u32: rank src has entered exchange number enter[src]
 //   [32, 64)   done[src]   u32: rank src's slice of exchange number done[src] has landed here
-//   [256, ...) data: world slices of `bytes` bytes, slice r written by rank r
+//   [256, ...) data: for each of up to 4 segments, world slices of that segment's size, slice r
+//              written by rank r (a segment is one projection's output: its slices end up side
+//              by side in rank order = row order, ready to use, with no copy afterwards)
 // Protocol of exchange number q (a per-rank counter in device memory, so a captured graph can
 // replay the launch): (1) tell every peer "I am in q" and wait until every peer is: its readers
 // of exchange q - 1 ran before this kernel in stream order, so the single data area may be
@@ -23,12 +25,15 @@ constexpr uint32_t XCH_SPIN_LIMIT = 1u << 24;
 
 __device__ int g_exchange_error;
 
+constexpr int XCH_MAX_SEGMENTS = 4;
+
 struct PushArgs {
   uint8_t *peer[XCH_MAX_RANKS];  // every rank's symmetric buffer, as mapped on this GPU
-  const uint8_t *local;
-  uint64_t bytes;
+  const uint8_t *local[XCH_MAX_SEGMENTS];
+  uint64_t bytes[XCH_MAX_SEGMENTS];  // this rank's slice of each segment
+  uint64_t base[XCH_MAX_SEGMENTS];   // where the segment's world slices start in the data area
   uint32_t *counter;
-  int rank, world;
+  int rank, world, segments;
 };
 
 __device__ __forceinline__ void st_release_sys(uint32_t *p, uint32_t v) { asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory"); }
@@ -62,14 +67,16 @@ __global__ void __launch_bounds__(1024, 1) push_gather_kernel(PushArgs a) {
   }
   __syncthreads();
   if (!s_ok) return;
-  // the slice into every peer's data area (own buffer included), 16 bytes per store
-  const uint64_t n16 = a.bytes / 16;
-  const uint4 *src = reinterpret_cast<const uint4 *>(a.local);
-  for (uint64_t i = threadIdx.x; i < n16; i += blockDim.x) {
-    const uint4 v = src[i];
-    for (int p = 0; p < a.world; p++) {
-      const int q = (a.rank + p) % a.world;  // start with the own buffer, then round the ring
-      reinterpret_cast<uint4 *>(a.peer[q] + XCH_DATA_OFFSET + (uint64_t)a.rank * a.bytes)[i] = v;
+  // the slices into every peer's data area (own buffer included), 16 bytes per store
+  for (int g = 0; g < a.segments; g++) {
+    const uint64_t n16 = a.bytes[g] / 16, at = XCH_DATA_OFFSET + a.base[g] + (uint64_t)a.rank * a.bytes[g];
+    const uint4 *src = reinterpret_cast<const uint4 *>(a.local[g]);
+    for (uint64_t i = threadIdx.x; i < n16; i += blockDim.x) {
+      const uint4 v = src[i];
+      for (int p = 0; p < a.world; p++) {
+        const int q = (a.rank + p) % a.world;  // start with the own buffer, then round the ring
+        reinterpret_cast<uint4 *>(a.peer[q] + at)[i] = v;
+      }
     }
   }
   __threadfence_system();
@@ -88,16 +95,21 @@ int exchange_status(int *status) {
 
 }  // namespace bn
 
-extern "C" int bn_push_gather(const void *local, uint64_t bytes, const uint64_t *peers, int rank, int world, uint32_t *counter, void *stream) {
-  if (!local || !peers || !counter || world < 1 || world > bn::XCH_MAX_RANKS || rank < 0 || rank >= world) return bn::fail(BN_ERR_ARG, "bn_push_gather: bad rank, world (1..8) or null pointer");
-  if ((uintptr_t)local % 16 || bytes % 16) return bn::fail(BN_ERR_ARG, "bn_push_gather: the slice must be 16-byte aligned and a multiple of 16 bytes");
-  if (bytes == 0) return BN_OK;
+extern "C" int bn_push_gather(const void *const *locals, const uint64_t *bytes, int segments, const uint64_t *peers, int rank, int world, uint32_t *counter, void *stream) {
+  if (!locals || !bytes || !peers || !counter || world < 1 || world > bn::XCH_MAX_RANKS || rank < 0 || rank >= world || segments < 1 || segments > bn::XCH_MAX_SEGMENTS)
+    return bn::fail(BN_ERR_ARG, "bn_push_gather: bad rank, world (1..8), segment count (1..4) or null pointer");
   bn::PushArgs a{};
+  uint64_t base = 0;
+  for (int g = 0; g < segments; g++) {
+    if (!locals[g] || (uintptr_t)locals[g] % 16 || bytes[g] % 16 || bytes[g] == 0) return bn::fail(BN_ERR_ARG, "bn_push_gather: a slice must be non-empty, 16-byte aligned and a multiple of 16 bytes");
+    a.local[g] = static_cast<const uint8_t *>(locals[g]), a.bytes[g] = bytes[g], a.base[g] = base;
+    base += (uint64_t)world * bytes[g];
+  }
   for (int r = 0; r < world; r++) {
     if (!peers[r]) return bn::fail(BN_ERR_ARG, "bn_push_gather: null peer buffer");
     a.peer[r] = reinterpret_cast<uint8_t *>(peers[r]);
   }
-  a.local = static_cast<const uint8_t *>(local), a.bytes = bytes, a.counter = counter, a.rank = rank, a.world = world;
+  a.counter = counter, a.rank = rank, a.world = world, a.segments = segments;
   bn::push_gather_kernel<<<1, 1024, 0, (cudaStream_t)stream>>>(a);
   return bn::launched("push_gather_kernel");
 }

@@ -90,8 +90,9 @@ class PushGather:
         ex = PushGather(group, max_bytes)   # collective: every rank of the group
         out = ex(flat)                      # flat [M, W] on this rank -> [world, M, W]
 
-    `out` is a view of this rank's buffer: it is overwritten by the next call, which every rank
-    enters only after its own readers of the previous result (stream order). Safe to capture in a
+    Results are views of this rank's buffer: they are overwritten by the next call on the same
+    object, which every rank enters only after its own readers of the previous result (stream
+    order), so a result must be consumed (or copied) before the object is used again. Safe to capture in a
     CUDA graph (the call number lives in device memory)."""
 
     HEADER = 256
@@ -116,9 +117,40 @@ class PushGather:
         torch.cuda.synchronize()
         dist.barrier(group)  # every buffer is zeroed before anyone's first flag arrives
 
-    def __call__(self, flat: torch.Tensor) -> torch.Tensor:
+    def _push(self, pieces):
+        """One exchange of 1..4 contiguous device tensors (16-byte aligned, sizes a multiple of
+        16 bytes): returns, per piece, the uint8 view [world, bytes] of the gathered slices."""
+        import ctypes
+
         from .kernels import _call, _p
 
+        sizes = [t.numel() * t.element_size() for t in pieces]
+        if self.world * sum(sizes) > self.world * self.cap:
+            raise ValueError(f"slices of {sum(sizes)} bytes exceed the exchange's {self.cap}")
+        n = len(pieces)
+        ptrs = (ctypes.c_void_p * n)(*[t.data_ptr() for t in pieces])
+        lens = (ctypes.c_uint64 * n)(*sizes)
+        _call("bn_push_gather", ctypes.cast(ptrs, ctypes.c_void_p), ctypes.cast(lens, ctypes.c_void_p), n, ctypes.cast(self.peers, ctypes.c_void_p), self.rank, self.world, _p(self.counter))
+        out, at = [], self.HEADER
+        for sz in sizes:
+            out.append(self.buf[at : at + self.world * sz].view(self.world, sz))
+            at += self.world * sz
+        return out
+
+    @staticmethod
+    def _pushable(t: torch.Tensor) -> bool:
+        return t.is_contiguous() and t.data_ptr() % 16 == 0 and (t.numel() * t.element_size()) % 16 == 0 and t.numel() > 0
+
+    def gather_rows(self, ys):
+        """Single-row slices ys[j] [.., w_j] (one row each) of 1..4 projections -> their full
+        rows [.., world * w_j], written by the kernel in their final layout: the results are
+        views of this rank's buffer, no copy before or after. None if a slice cannot be pushed
+        as it is (several rows, unaligned or odd size): the caller then takes __call__."""
+        if not 1 <= len(ys) <= 4 or any(y.numel() != y.shape[-1] or not self._pushable(y) for y in ys):
+            return None
+        return [g.view(y.dtype).reshape(*y.shape[:-1], self.world * y.shape[-1]) for g, y in zip(self._push(list(ys)), ys)]
+
+    def __call__(self, flat: torch.Tensor) -> torch.Tensor:
         flat = flat.contiguous()
         nbytes = flat.numel() * flat.element_size()
         padded = (nbytes + 15) // 16 * 16
@@ -130,10 +162,7 @@ class PushGather:
             src = stage
         else:
             src = flat
-        import ctypes
-
-        _call("bn_push_gather", _p(src), padded, ctypes.cast(self.peers, ctypes.c_void_p), self.rank, self.world, _p(self.counter))
-        data = self.buf[self.HEADER : self.HEADER + self.world * padded].view(self.world, padded)[:, :nbytes]
+        data = self._push([src])[0][:, :nbytes]
         return data.reshape(self.world, nbytes).view(flat.dtype).view(self.world, *flat.shape)
 
 
@@ -169,6 +198,10 @@ class RowShardedLinear(nn.Module):
         y = self.local(x)
         if world == 1:
             return y
+        if self.exchange is not None and self.N % world == 0:
+            fast = self.exchange.gather_rows([y])
+            if fast is not None:
+                return fast[0]
         counts = [r1 - r0 for r0, r1 in (row_range(self.N, r, world) for r in range(world))]
         width = max(counts)
         if y.shape[-1] != counts[rank]:
@@ -211,6 +244,10 @@ class RowShardedGroup(nn.Module):
         for y, w, N in zip(ys, widths, self.Ns):
             if N % world or y.shape[-1] != w:
                 raise ValueError(f"a projection of {N} rows does not split evenly over {world} ranks (local slice {y.shape[-1]})")
+        if self.exchange is not None:
+            fast = self.exchange.gather_rows(ys)
+            if fast is not None:
+                return fast
         lead = ys[0].shape[:-1]
         flat = torch.cat([y.reshape(-1, w) for y, w in zip(ys, widths)], dim=-1)  # [M, sum of widths]
         out = _all_gather(flat, world, self.group, self.exchange)

@@ -9,19 +9,21 @@ several GPUs. With `world` > 1 every linear is sharded by output rows: a rank ow
 query heads with their KV heads and FFN/world rows of gate and up, attention and SwiGLU stay
 local, and four all-gathers per layer (attention output, o_proj, SwiGLU output, down_proj) plus
 one for the logits rebuild the full vectors, in row order, so outputs do not depend on the GPU
-count.
+count. The all-gathers are this library's peer-store kernel (dist.PushGather), or NCCL with
+BINADE_B200_GATHER=nccl.
 """
 
 from __future__ import annotations
 
 import math
+import os
 from dataclasses import dataclass
 
 import torch
 from torch import nn
 
 from . import r4
-from .dist import RowShardedLinear, row_range
+from .dist import PushGather, RowShardedLinear, row_range
 
 
 @dataclass
@@ -67,9 +69,16 @@ class Decoder(nn.Module):
         self.hq, self.hkv = s.heads // world, s.kv_heads // world
         d = s.head_dim
 
+        # the all-gathers go through this library's peer-store kernel (one shared buffer: every
+        # gathered vector is consumed before the next exchange in stream order);
+        # BINADE_B200_GATHER=nccl keeps them on the library collective
+        self.exchange = None
+        if world > 1 and dev.type == "cuda" and os.environ.get("BINADE_B200_GATHER", "push") != "nccl":
+            self.exchange = PushGather(group, max_bytes=2 * max(s.vocab, s.ffn, s.heads * d, s.hidden) // world + 64)
+
         def lin(w_rows: torch.Tensor, n_total: int):
             local = r4.R4Linear(r4.from_dense(w_rows)) if kind == "r4" else DenseLinear(w_rows)
-            return RowShardedLinear(local, n_total, group) if world > 1 else local
+            return RowShardedLinear(local, n_total, group, exchange=self.exchange) if world > 1 else local
 
         def rows_of(w, count):  # this rank's share of `count` leading-dim rows
             r0, r1 = row_range(count, rank, world)
@@ -119,6 +128,9 @@ class Decoder(nn.Module):
         """All-gather a local slice [.., n_total / world] into the full vector (row order)."""
         if self.world == 1:
             return y
+        if self.exchange is not None:
+            fast = self.exchange.gather_rows([y.reshape(1, -1)])
+            return fast[0] if fast is not None else self.exchange(y.reshape(1, -1)).reshape(1, n_total)
         import torch.distributed as dist
 
         out = torch.empty((self.world, y.shape[-1]), dtype=y.dtype, device=y.device)
