@@ -10,7 +10,9 @@ Same roles and names as the reference's binade/mlx/r4.py, on torch:
   convert(model)      swap every BinadeLinear holder for an R4Linear in place (r4.py:375-410)
 
 Row counts: 1..FUSED_MAX_ROWS input rows run the fused decode kernel (weights stream once, fp32
-accumulation in the documented lane order; `fused_rows` forces it up to 16 rows); more rows
+accumulation in the documented lane order; `fused_rows` forces it up to 16 rows); up to
+MMA_MAX_ROWS rows run the tensor-core decode GEMM (weights stream once, the hardware's summation
+order; the reference's counterpart is its fused GEMM for 1 < M <= 128, r4.py:254-268); more rows
 rebuild the BF16 weight with the decode kernel and call torch.matmul, as the reference does for
 long prompts (r4.py:288).
 """
@@ -24,7 +26,7 @@ from torch import nn
 from ..format import TILE
 from . import kernels as ck
 
-FUSED_MAX_ROWS = 8  # input rows served by the fused decode kernel; beyond, rebuilding BF16 and calling cuBLAS is faster on B200 (measured on 15360 x 3840: fused 38 / 73 us at 2 / 8 rows and 252 us at 16, rebuild 92 us)
+FUSED_MAX_ROWS = 4  # input rows served by the fused decode kernel in the documented order (15360 x 3840: 37 / 49 / 75 us at 2 / 4 / 8 rows); from 5 rows the tensor-core decode GEMM is faster (46 us)
 
 
 MMA_MAX_ROWS = 128  # input rows served by the tensor-core decode GEMM (one pass over the weights); beyond, rebuild + cuBLAS
