@@ -25,6 +25,11 @@ struct RiceArgs {
   // lookups (RICE_UNPACK only): output row i decodes stream row ids[i] of a table of `rows` rows
   const uint32_t *ids;
   int64_t rows;
+  // format 1 (fixed-width codes, FMT == 1): `bits` is the index stream, `roff` the first word of
+  // each row (bn_f1_offsets), f1_esc the file's escape bytes, f1_eoff the escapes before each row
+  const uint8_t *f1_esc;
+  uint64_t f1_nesc;
+  const uint32_t *f1_eoff;
   // outputs
   uint32_t *ranks;   // RICE_RANKS: [R, T*32] four 8-bit ranks per word
   uint32_t *rend;    // RICE_RANKS / RICE_UNPACK: word after each row's last bit
@@ -68,9 +73,19 @@ __device__ __forceinline__ void warp_scan_count(uint32_t cnt, uint32_t lt, uint3
 
 constexpr int RICE_THREADS = 256;
 
-template <int MODE>
+// MODE: what is written (ranks, BF16 words, R4 arrays). FMT: how a tile is coded on file: 2 =
+// Rice planes (binade/rice.py), 1 = fixed-width codes with escapes (binade/format.py:1-12: meta =
+// b | escape << 4; a tile is exactly 4 b words, code i at bits i b ..; in escape mode the code
+// 2^b - 1 stands for "next byte of the escape stream", an exponent, whose rank is looked up).
+template <int MODE, int FMT = 2>
 __global__ void __launch_bounds__(RICE_THREADS) rice_kernel(RiceArgs a) {
   __shared__ uint8_t tbl[256];
+  __shared__ uint32_t inv[FMT == 1 ? 256 : 1];  // format 1: rank of an exponent (smallest rank listing it)
+  if (FMT == 1) {
+    inv[threadIdx.x] = 255u;
+    __syncthreads();
+    atomicMin(&inv[a.table[threadIdx.x]], threadIdx.x);
+  }
   // deposit table: entry alive | bits << 4 spreads the low bits of `bits`, in order, over the
   // set positions of the 4-bit mask `alive` (a 4-bit pdep)
   __shared__ uint8_t deposit[256];
@@ -80,7 +95,7 @@ __global__ void __launch_bounds__(RICE_THREADS) rice_kernel(RiceArgs a) {
     for (int i = 0; i < 4; i++)
       if ((al >> i) & 1u) out |= (b & 1u) << i, b >>= 1;
     deposit[threadIdx.x] = (uint8_t)out;
-    if (MODE != RICE_RANKS) tbl[threadIdx.x] = a.table[threadIdx.x];
+    if (MODE != RICE_RANKS || FMT == 1) tbl[threadIdx.x] = a.table[threadIdx.x];
     __syncthreads();
   }
   const uint32_t lane = lane_id(), lt = lanemask_lt();
@@ -104,6 +119,7 @@ __global__ void __launch_bounds__(RICE_THREADS) rice_kernel(RiceArgs a) {
     const uint32_t *row_words = a.bits + w0;
     const uint32_t avail = (uint64_t)w0 < a.nwords ? (uint32_t)min(a.nwords - w0, (uint64_t)0xFFFFFFFFu) : 0u;
     uint32_t cur = 0;  // bits from the row's first word
+    uint32_t f1_cur = FMT == 1 ? a.f1_eoff[srow] : 0u;  // format 1: cursor into the file's escape bytes
     uint32_t row_escapes = 0;
     uint64_t esc_base = 0;
     bool esc_room = false;
@@ -113,7 +129,8 @@ __global__ void __launch_bounds__(RICE_THREADS) rice_kernel(RiceArgs a) {
       uint32_t bound = 0;
       for (int t = lane; t < T; t += 32) {
         const uint32_t m = a.meta[row * T + t], k = m & 3u, qmax = m >> 2;
-        if (((qmax << k) | ((1u << k) - 1u)) >= 15u) bound += (uint32_t)min(BN_TILE, (int)K - t * BN_TILE);
+        // format 1: a fixed tile reaches rank 15 from 4 bits on; an escaped weight may have any rank
+        if (FMT == 1 ? ((m & 15u) >= 4u || (m & 16u)) : (((qmax << k) | ((1u << k) - 1u)) >= 15u)) bound += (uint32_t)min(BN_TILE, (int)K - t * BN_TILE);
       }
 #pragma unroll
       for (int o = 16; o >= 1; o >>= 1) bound += __shfl_xor_sync(BN_FULL, bound, o);
@@ -131,9 +148,34 @@ __global__ void __launch_bounds__(RICE_THREADS) rice_kernel(RiceArgs a) {
       for (int u = 0; u < tn; u++) {
         const int t = t0 + u;
         const uint32_t m = __shfl_sync(BN_FULL, my_meta, u);
-        const uint32_t k = m & 3u, qmax = m >> 2;
         const int n = min(BN_TILE, (int)K - t * BN_TILE);
         const uint32_t nv = (uint32_t)max(0, min(4, n - (int)lane * 4));
+        uint32_t r4 = 0;  // ranks of the lane's four weights, one per byte
+        if (FMT == 1) {
+          const uint32_t b = m & 15u, cm = (1u << b) - 1u;
+          const uint32_t v = b ? row_bits(row_words, avail, cur + lane * 4u * b, 4u * b) : 0u;  // padding weights are coded too (as 0)
+          cur += (uint32_t)BN_TILE * b;
+          uint32_t c[4], hit = 0;
+#pragma unroll
+          for (int i = 0; i < 4; i++) {
+            c[i] = (v >> (i * b)) & cm;
+            if ((m & 16u) && c[i] == cm) hit |= 1u << i;
+          }
+          if (__any_sync(BN_FULL, hit != 0)) {
+            uint32_t pre, tot;
+            warp_scan_count(__popc(hit), lt, pre, tot);
+            uint64_t q = (uint64_t)f1_cur + pre;
+#pragma unroll
+            for (int i = 0; i < 4; i++)
+              if ((hit >> i) & 1u) {
+                c[i] = q < a.f1_nesc ? inv[a.f1_esc[q]] : 0u;  // a short escape stream cannot be read past
+                q++;
+              }
+            f1_cur += tot;
+          }
+          r4 = (c[0] & 0xFFu) | ((c[1] & 0xFFu) << 8) | ((c[2] & 0xFFu) << 16) | ((c[3] & 0xFFu) << 24);
+        } else {
+        const uint32_t k = m & 3u, qmax = m >> 2;
         uint32_t lo = 0;
         if (nv * k) lo = row_bits(row_words, avail, cur + lane * 4u * k, nv * k);
         cur += (uint32_t)n * k;
@@ -172,11 +214,11 @@ __global__ void __launch_bounds__(RICE_THREADS) rice_kernel(RiceArgs a) {
         }
         // ranks of the lane's four weights, one per byte: q << k | low bits
         const uint32_t km = (1u << k) - 1u;
-        uint32_t r4 = 0;
 #pragma unroll
         for (int i = 0; i < 4; i++) {
           const uint32_t r = ((((q4 >> (8 * i)) & 0xFFu) << k) | ((lo >> (i * k)) & km)) & 0xFFu;
           r4 |= r << (8 * i);
+        }
         }
         if (MODE == RICE_RANKS) {
           a.ranks[(row * T + t) * 32 + lane] = r4;
@@ -268,6 +310,46 @@ __global__ void __launch_bounds__(256) compact_esc_kernel(const uint32_t *__rest
     for (uint64_t i = lane; b + i < e; i += 32) esc[b + i] = src[i];
   }
   if (blockIdx.x == 0 && threadIdx.x == 0) esc[esc_bytes - 1] = 0;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Format 1 carries no row offsets: a tile of width b is 4 b words, escapes are one stream for the
+// whole tensor. Two small passes rebuild, per row, the first index word and the escapes before it.
+// ---------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) f1_row_words_kernel(const uint8_t *__restrict__ meta, int64_t R, int T, uint32_t *__restrict__ words) {
+  const uint32_t lane = lane_id();
+  for (int64_t row = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5); row < R; row += (int64_t)gridDim.x * 8) {
+    uint32_t n = 0;
+    for (int t = lane; t < T; t += 32) n += 4u * (meta[row * T + t] & 15u);
+    n = __reduce_add_sync(BN_FULL, n);
+    if (lane == 0) words[row] = n;
+  }
+}
+
+__global__ void __launch_bounds__(256) f1_row_escapes_kernel(const uint8_t *__restrict__ meta, const uint32_t *__restrict__ idx, uint64_t nwords, const uint32_t *__restrict__ woff, int64_t R, int T, uint32_t *__restrict__ count) {
+  const uint32_t lane = lane_id();
+  for (int64_t row = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5); row < R; row += (int64_t)gridDim.x * 8) {
+    const uint32_t w0 = woff[row];
+    const uint32_t avail = (uint64_t)w0 < nwords ? (uint32_t)min(nwords - w0, (uint64_t)0xFFFFFFFFu) : 0u;
+    uint32_t cur = 0, n = 0;
+    for (int t = 0; t < T; t++) {
+      const uint32_t m = meta[row * T + t], b = m & 15u, cm = (1u << b) - 1u;
+      if ((m & 16u) && b) {
+        const uint32_t v = row_bits(idx + w0, avail, cur + lane * 4u * b, 4u * b);
+#pragma unroll
+        for (int i = 0; i < 4; i++) n += ((v >> (i * b)) & cm) == cm;
+      }
+      cur += (uint32_t)BN_TILE * b;
+    }
+    n = __reduce_add_sync(BN_FULL, n);
+    if (lane == 0) count[row] = n;
+  }
+}
+
+// totals[0] = index words, totals[1] = escapes the meta bytes and the index stream imply
+__global__ void f1_totals_kernel(const uint32_t *woff, const uint32_t *words, const uint32_t *eoff, const uint32_t *count, int64_t R, uint32_t *totals) {
+  totals[0] = woff[R - 1] + words[R - 1];
+  totals[1] = eoff[R - 1] + count[R - 1];
 }
 
 static int rice_grid(int64_t R) {
@@ -435,4 +517,75 @@ extern "C" int bn_rice_to_r4_static(const uint8_t *meta, const uint32_t *bits, u
   if (blocks < 1) blocks = 1;
   compact_esc_static_kernel<<<(unsigned)blocks, 256, 0, s>>>(row_esc, esc_tmp, tmp_off, counters, R, esc, esc_cap, info);
   return launched("compact_esc_static_kernel");
+}
+
+// ---------------------------------------------------------------------------------------------
+// Format 1 entry points
+// ---------------------------------------------------------------------------------------------
+static int f1_grid(int64_t R) {
+  const int64_t blocks = (R + 7) / 8;
+  return (int)(blocks < 148 * 8 ? blocks : 148 * 8);
+}
+
+extern "C" int bn_f1_offsets(const uint8_t *meta, const uint32_t *idx, uint64_t nwords, int64_t R, int64_t K, uint32_t *woff, uint32_t *eoff, uint32_t *scratch, uint32_t *totals, void *stream) {
+  if (!meta || !idx || !woff || !eoff || !scratch || !totals || R < 0 || K <= 0) return fail(BN_ERR_ARG, "bn_f1_offsets: null pointer or bad size");
+  if (R == 0) return BN_OK;
+  cudaStream_t s = (cudaStream_t)stream;
+  const int T = (int)tiles(K);
+  uint32_t *words = scratch, *count = scratch + R;  // scratch: 2 R words
+  f1_row_words_kernel<<<f1_grid(R), 256, 0, s>>>(meta, R, T, words);
+  if (int e = launched("f1_row_words_kernel")) return e;
+  scan_rows_kernel<<<1, 1024, 0, s>>>(words, R, woff);
+  if (int e = launched("scan_rows_kernel")) return e;
+  f1_row_escapes_kernel<<<f1_grid(R), 256, 0, s>>>(meta, idx, nwords, woff, R, T, count);
+  if (int e = launched("f1_row_escapes_kernel")) return e;
+  scan_rows_kernel<<<1, 1024, 0, s>>>(count, R, eoff);
+  if (int e = launched("scan_rows_kernel")) return e;
+  f1_totals_kernel<<<1, 1, 0, s>>>(woff, words, eoff, count, R, totals);
+  return launched("f1_totals_kernel");
+}
+
+static RiceArgs f1_args(const uint8_t *meta, const uint32_t *idx, uint64_t nwords, const uint32_t *woff, const uint8_t *esc, uint64_t n_esc, const uint32_t *eoff, const uint8_t *table, int64_t R, int64_t K) {
+  RiceArgs a{};
+  a.meta = meta, a.bits = idx, a.nwords = nwords, a.roff = woff, a.table = table, a.R = R, a.K = K, a.T = (int)tiles(K);
+  a.f1_esc = esc, a.f1_nesc = n_esc, a.f1_eoff = eoff;
+  return a;
+}
+
+static int check_f1(const uint8_t *meta, const uint32_t *idx, const uint32_t *woff, const uint8_t *esc, const uint32_t *eoff, const uint8_t *table, int64_t R, int64_t K) {
+  if (!meta || !idx || !woff || !esc || !eoff || !table) return fail(BN_ERR_ARG, "null format-1 array");
+  if (R < 0 || K <= 0) return fail(BN_ERR_ARG, "bad matrix size");
+  return BN_OK;
+}
+
+extern "C" int bn_f1_ranks(const uint8_t *meta, const uint32_t *idx, uint64_t nwords, const uint32_t *woff, const uint8_t *esc, uint64_t n_esc, const uint32_t *eoff, const uint8_t *table, int64_t R, int64_t K, uint8_t *ranks, void *stream) {
+  if (int e = check_f1(meta, idx, woff, esc, eoff, table, R, K)) return e;
+  if (!ranks) return fail(BN_ERR_ARG, "bn_f1_ranks: null output");
+  if (R == 0) return BN_OK;
+  RiceArgs a = f1_args(meta, idx, nwords, woff, esc, n_esc, eoff, table, R, K);
+  a.ranks = reinterpret_cast<uint32_t *>(ranks), a.rend = nullptr;
+  rice_kernel<RICE_RANKS, 1><<<rice_grid(R), RICE_THREADS, 0, (cudaStream_t)stream>>>(a);
+  return launched("rice_kernel<ranks, format 1>");
+}
+
+extern "C" int bn_f1_unpack(const uint8_t *meta, const uint32_t *idx, uint64_t nwords, const uint32_t *woff, const uint8_t *esc, uint64_t n_esc, const uint32_t *eoff, const uint8_t *table, const uint8_t *raw, int64_t R, int64_t K, uint16_t *out, void *stream) {
+  if (int e = check_f1(meta, idx, woff, esc, eoff, table, R, K)) return e;
+  if (!raw || !out) return fail(BN_ERR_ARG, "bn_f1_unpack: null pointer");
+  if (R == 0) return BN_OK;
+  RiceArgs a = f1_args(meta, idx, nwords, woff, esc, n_esc, eoff, table, R, K);
+  a.raw = raw, a.out = out, a.rend = nullptr;
+  rice_kernel<RICE_UNPACK, 1><<<rice_grid(R), RICE_THREADS, 0, (cudaStream_t)stream>>>(a);
+  return launched("rice_kernel<unpack, format 1>");
+}
+
+extern "C" int bn_f1_to_r4(const uint8_t *meta, const uint32_t *idx, uint64_t nwords, const uint32_t *woff, const uint8_t *esc, uint64_t n_esc, const uint32_t *eoff, const uint8_t *table, int64_t R, int64_t K, uint16_t *codes, uint8_t *flags, uint32_t *row_cnt, uint8_t *esc_tmp, uint64_t esc_cap, uint32_t *tmp_off, uint32_t *counters, void *stream) {
+  if (int e = check_f1(meta, idx, woff, esc, eoff, table, R, K)) return e;
+  if (!codes || !flags || !row_cnt || !esc_tmp || !tmp_off || !counters) return fail(BN_ERR_ARG, "bn_f1_to_r4: null output");
+  if (K % 4) return fail(BN_ERR_ARG, "R4 needs K % 4 == 0");
+  BN_CUDA(cudaMemsetAsync(counters, 0, 8 * sizeof(uint32_t), (cudaStream_t)stream));
+  if (R == 0) return BN_OK;
+  RiceArgs a = f1_args(meta, idx, nwords, woff, esc, n_esc, eoff, table, R, K);
+  a.codes = codes, a.flags = flags, a.row_cnt = row_cnt, a.esc_tmp = esc_tmp, a.esc_cap = esc_cap, a.tmp_off = tmp_off, a.counters = counters;
+  rice_kernel<RICE_R4, 1><<<rice_grid(R), RICE_THREADS, 0, (cudaStream_t)stream>>>(a);
+  return launched("rice_kernel<r4, format 1>");
 }

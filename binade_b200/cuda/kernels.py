@@ -115,6 +115,89 @@ def rice_to_r4(meta, bits, roff, table, R: int, K: int, esc_cap: int | None = No
     return codes, flags, esc, row_cnt, bad_row
 
 
+class Format1:
+    """Format-1 file arrays of one tensor on the device plus the row offsets the format does not
+    store (rebuilt by bn_f1_offsets). Raises ValueError when meta and idx disagree with the array
+    sizes, as format.decode does (binade/format.py:128-133)."""
+
+    def __init__(self, meta, idx, esc, table, R: int, K: int):
+        self.R, self.K = R, K
+        T = -(-K // TILE)
+        self.meta, self.table = to_device(meta).reshape(-1), to_device(table)
+        dev = self.meta.device
+        if self.meta.numel() != R * T:
+            raise ValueError(f"{self.meta.numel()} tiles for {R} rows of {K}")
+        idx, esc = to_device(idx).reshape(-1), to_device(esc).reshape(-1)
+        self.nwords, self.n_esc = idx.numel(), esc.numel()
+        self.idx = idx if self.nwords else torch.zeros(1, dtype=torch.int32, device=dev)
+        self.esc = esc if self.n_esc else torch.zeros(1, dtype=torch.uint8, device=dev)
+        self.woff = torch.empty(max(R, 1), dtype=torch.int32, device=dev)
+        self.eoff = torch.empty(max(R, 1), dtype=torch.int32, device=dev)
+        if R:
+            scratch = torch.empty(2 * R, dtype=torch.int32, device=dev)
+            totals = torch.zeros(2, dtype=torch.int32, device=dev)
+            _call("bn_f1_offsets", _p(self.meta), _p(self.idx), self.nwords, R, K, _p(self.woff), _p(self.eoff), _p(scratch), _p(totals))
+            words, escapes = (int(v) for v in totals.cpu().numpy().view(np.uint32))
+            if words != self.nwords or escapes != self.n_esc:
+                raise ValueError(f"format-1 streams do not fit their tiles: {words} index words and {escapes} escapes expected, {self.nwords} and {self.n_esc} given")
+
+    @staticmethod
+    def rows_of(whole: "Format1", r0: int, r1: int) -> "Format1":
+        """Rows r0 .. r1 - 1 of an already indexed tensor, sharing its arrays: the row offsets are
+        absolute, so a row range is a view of meta, woff and eoff."""
+        T = -(-whole.K // TILE)
+        part = object.__new__(Format1)
+        part.R, part.K = r1 - r0, whole.K
+        part.meta, part.table = whole.meta[r0 * T : r1 * T], whole.table
+        part.idx, part.esc, part.nwords, part.n_esc = whole.idx, whole.esc, whole.nwords, whole.n_esc
+        part.woff, part.eoff = whole.woff[r0:r1], whole.eoff[r0:r1]
+        return part
+
+    def _head(self):
+        return (_p(self.meta), _p(self.idx), self.nwords, _p(self.woff), _p(self.esc), self.n_esc, _p(self.eoff), _p(self.table))
+
+    def ranks(self) -> torch.Tensor:
+        """8-bit ranks [R, T*128] (padding columns 0)."""
+        T = -(-self.K // TILE)
+        out = torch.empty((self.R, T * TILE), dtype=torch.uint8, device=self.meta.device)
+        if self.R:
+            _call("bn_f1_ranks", *self._head(), self.R, self.K, _p(out))
+        return out
+
+    def unpack(self, raw) -> torch.Tensor:
+        """BF16 rows [R, K] from the raw sign+mantissa bytes."""
+        out = torch.empty((self.R, self.K), dtype=torch.bfloat16, device=self.meta.device)
+        if self.R:
+            _call("bn_f1_unpack", *self._head(), _p(to_device(raw)), self.R, self.K, _p(out))
+        return out
+
+    def to_r4(self, esc_cap: int | None = None):
+        """(codes, flags, esc, row_esc) of the R4 layout: the expander for format-1 files."""
+        dev, R, K = self.meta.device, self.R, self.K
+        T = -(-K // TILE)
+        codes = torch.empty(R * T * 32, dtype=torch.int16, device=dev)
+        flags = torch.empty(R * T, dtype=torch.uint8, device=dev)
+        row_cnt = torch.empty(R, dtype=torch.int32, device=dev)
+        tmp_off = torch.empty(R, dtype=torch.int32, device=dev)
+        counters = torch.empty(8, dtype=torch.int32, device=dev)
+        cap = esc_cap if esc_cap is not None else 4096 + R * K // 4
+        while True:
+            cap = min(cap, (1 << 32) - 1)
+            esc_tmp = torch.empty(cap, dtype=torch.uint8, device=dev)
+            _call("bn_f1_to_r4", *self._head(), R, K, _p(codes), _p(flags), _p(row_cnt), _p(esc_tmp), cap, _p(tmp_off), _p(counters))
+            c = counters.cpu().numpy().view(np.uint32)
+            claimed = int(c[4]) | int(c[5]) << 32
+            if claimed <= cap:
+                break
+            if claimed >= 1 << 32:
+                raise ValueError("escape scratch of one call exceeds 4 GiB: expand the tensor in row chunks")
+            cap = claimed
+        n_esc = int(c[2])
+        esc = torch.empty(n_esc + 1, dtype=torch.uint8, device=dev)
+        _call("bn_r4_finish", _p(row_cnt), _p(esc_tmp), _p(tmp_off), R, _p(row_cnt), _p(esc), n_esc + 1)
+        return codes, flags, esc, row_cnt
+
+
 def r4_decode(a: dict, N: int, K: int, nb: int | None = None, rs: int | None = None, r0: int = 0) -> torch.Tensor:
     """BF16 [N, K] from R4; output row r is storage row (r // nb) * rs + r0 + r % nb."""
     out = torch.empty((N, K), dtype=torch.bfloat16, device=a["raw"].device)

@@ -59,19 +59,23 @@ class BinadeEmbedding(nn.Module):
 
 
 def transcode(module) -> dict:
-    """R4 arrays for a format-2 module (anything with a `.weight` dict, or the dict itself).
+    """R4 arrays for a format-2 or format-1 module (anything with a `.weight` dict, or the dict).
     Rows of K weights, K % 4 == 0 (raw bytes are read four at a time); a last tile with K % 128
     weights is padded with code 0. Raises ValueError if a row's stream does not end where the
     next one starts."""
     w = module.weight if hasattr(module, "weight") else module
-    if "bits" not in w:
-        raise ValueError("only format 2 (Rice) arrays can be transcoded; format 1 is not implemented")
     raw = ck.to_device(w["raw"])
     K = raw.shape[-1]
     R = raw.numel() // K if K else 0
     if K % 4:
         raise ValueError(f"R4 needs K % 4 == 0, got {K}")
     T = -(-K // TILE)
+    if "bits" not in w:  # format 1: fixed-width codes {raw, table, meta, idx, esc} (reference r4.py:134-140)
+        if "idx" not in w:
+            raise ValueError("neither format 2 (bits, roff) nor format 1 (idx, esc) arrays")
+        f1 = ck.Format1(w["meta"], w["idx"], w["esc"], w["table"], R, K)
+        codes, flags, esc, row_esc = f1.to_r4()
+        return {"raw": raw.reshape(R, K), "table": f1.table, "codes": codes, "flags": flags, "esc": esc, "row_esc": row_esc, "shape": tuple(raw.shape)}
     meta, bits, roff, table = (ck.to_device(w[k]) for k in ("meta", "bits", "roff", "table"))
     if meta.numel() != R * T or roff.numel() != R:
         raise ValueError(f"{meta.numel()} tiles and {roff.numel()} row offsets for {R} x {K}")
@@ -250,7 +254,6 @@ def holders(packed) -> dict:
     pm = packed if isinstance(packed, PackedModel) else PackedModel(packed)
     out = {}
     for name in pm.packed:
-        if f"{name}.bits" not in pm.infos:
-            raise ValueError(f"{name}: format 1 is not implemented")
-        out[name] = BinadeLinear({k: st.read(pm.infos[f"{name}.{k}"]) for k in ("raw", "table", "meta", "bits", "roff")})
+        parts = ("raw", "table", "meta", "bits", "roff") if f"{name}.bits" in pm.infos else ("raw", "table", "meta", "idx", "esc")
+        out[name] = BinadeLinear({k: st.read(pm.infos[f"{name}.{k}"]) for k in parts})
     return out

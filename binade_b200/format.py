@@ -2,7 +2,8 @@
 
 A tensor's 256-entry table lists its exponent bytes by descending frequency; every weight
 stores the rank of its exponent (reference: binade/format.py:17,34-42). Format 1 (fixed-width
-codes with escapes) is not implemented in this package; format 2 lives in `rice`.
+codes with escapes) is read on the GPU (`cuda.kernels.Format1`) but not written; format 2 lives
+in `rice`.
 """
 
 from __future__ import annotations

@@ -84,9 +84,17 @@ class PackedModel:
         """Yield (r0, r1, uint16 [r1 - r0, K]) over a packed tensor's 2-D view."""
         from .cuda import kernels as ck
 
-        if f"{name}.bits" not in self.infos:
-            raise NotImplementedError(f"{name}: format 1 is not implemented")
         raw = self.infos[f"{name}.raw"]
+        if f"{name}.bits" not in self.infos:  # format 1: fixed-width codes, one escape stream per tensor
+            table, meta, idx, esc = (st.read(self.infos[f"{name}.{s}"]) for s in ("table", "meta", "idx", "esc"))
+            R, K = raw.rows, raw.shape[-1]
+            f1 = ck.Format1(meta, idx, esc, table, R, K)  # offsets of every row, on the device
+            step = max(1, chunk // K)
+            for r0 in range(0, R, step):
+                r1 = min(R, r0 + step)
+                part = ck.Format1.rows_of(f1, r0, r1)
+                yield r0, r1, part.unpack(st.read(raw, (r0, r1))).view(torch_int16()).cpu().numpy().view(np.uint16)
+            return
         table, meta, words, roff = (st.read(self.infos[f"{name}.{s}"]) for s in ("table", "meta", "bits", "roff"))
         R, K = raw.rows, raw.shape[-1]
         per_row = math.ceil(K / TILE)
@@ -104,6 +112,12 @@ class PackedModel:
         if name not in self.packed:
             return st.read(self.infos[name])
         return np.concatenate([u for _, _, u in self.rows(name)]).reshape(self.info(name).shape)
+
+
+def torch_int16():
+    import torch
+
+    return torch.int16
 
 
 def main():

@@ -124,6 +124,30 @@ int bn_rice_to_r4_static(const uint8_t *meta, const uint32_t *bits, uint64_t nwo
 int bn_r4_decode(const bn_r4 *w, int64_t N, int64_t K, int64_t NB, int64_t RS, int64_t R0,
                  uint16_t *out, void *stream);
 
+/* ---- format 1 (fixed-width codes with escapes, binade/format.py): file arrays meta [R*T]
+ * (b | escape << 4), idx (uint32 words, a tile of width b is 4 b words), esc (exponent bytes of
+ * the escaped weights, tensor order), table [256]. The format stores no row offsets, so
+ * bn_f1_offsets rebuilds them on the device: woff [R] first index word of each row, eoff [R]
+ * escapes before each row, totals [2] = (index words, escapes) implied by meta and idx, which the
+ * caller compares with the array sizes (the check of format.decode, binade/format.py:128-133).
+ * scratch: 2 R uint32. The three decoders then mirror the format-2 ones (same kernels behind
+ * them, a different tile front end): 8-bit ranks, BF16 words, R4 arrays (followed by
+ * bn_r4_finish). Replace format.decode_tiles (binade/format.py:104-124) and the format-1 branch
+ * of _rank_chunks (binade/mlx/r4.py:134-140), which decode on the host CPU with numpy. */
+int bn_f1_offsets(const uint8_t *meta, const uint32_t *idx, uint64_t nwords, int64_t R, int64_t K,
+                  uint32_t *woff, uint32_t *eoff, uint32_t *scratch, uint32_t *totals, void *stream);
+int bn_f1_ranks(const uint8_t *meta, const uint32_t *idx, uint64_t nwords, const uint32_t *woff,
+                const uint8_t *esc, uint64_t n_esc, const uint32_t *eoff, const uint8_t *table,
+                int64_t R, int64_t K, uint8_t *ranks, void *stream);
+int bn_f1_unpack(const uint8_t *meta, const uint32_t *idx, uint64_t nwords, const uint32_t *woff,
+                 const uint8_t *esc, uint64_t n_esc, const uint32_t *eoff, const uint8_t *table,
+                 const uint8_t *raw, int64_t R, int64_t K, uint16_t *out, void *stream);
+int bn_f1_to_r4(const uint8_t *meta, const uint32_t *idx, uint64_t nwords, const uint32_t *woff,
+                const uint8_t *esc, uint64_t n_esc, const uint32_t *eoff, const uint8_t *table,
+                int64_t R, int64_t K, uint16_t *codes, uint8_t *flags, uint32_t *row_cnt,
+                uint8_t *esc_tmp, uint64_t esc_cap, uint32_t *tmp_off, uint32_t *counters,
+                void *stream);
+
 /* Fused R4-decode GEMM on the tensor cores for 1 <= M <= 128 input rows (meant for 16 and more):
  * Y [M,N] = X [M,K] . W^T with the weights decoded to BF16 inside the kernel (tcgen05 MMA, fp32
  * accumulators in tensor memory); the weights are read once whatever M. K % 8 == 0, rows of X

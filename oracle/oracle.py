@@ -165,6 +165,78 @@ def np_rice_decode(table, meta, words, roff, R: int, K: int) -> np.ndarray:
     return table[ranks]
 
 
+# ---------------------------------------------------------------------------------------------
+# Format 1: fixed-width codes with escapes (binade/format.py)
+# ---------------------------------------------------------------------------------------------
+F1_ESCAPE = 0x10
+
+
+def np_f1_choose(r: np.ndarray):
+    """binade/format.py:46-60: per tile (b, escape mode) minimising index + escape bits; ties go
+    to fixed width, then to the smaller escape width. r: [tiles, 128] ranks."""
+    T = r.shape[1]
+    rmax = r.max(axis=1).astype(np.int64)
+    fixed_b = np.array([int(v).bit_length() for v in rmax], np.int64)
+    costs = [T * fixed_b]
+    for b in (1, 2, 3, 4):
+        costs.append(T * b + 8 * (r >= (1 << b) - 1).sum(axis=1).astype(np.int64))
+    pick = np.argmin(np.stack(costs), axis=0)
+    return np.where(pick == 0, fixed_b, pick).astype(np.int64), pick > 0
+
+
+def np_f1_encode(exps: np.ndarray, table: np.ndarray, rank: np.ndarray):
+    """binade/format.py:88-101: exponents [R,K] -> (meta uint8 [tiles], idx uint32 words, esc
+    uint8). Rows are padded to whole tiles with the most common exponent (rank 0); code i of a
+    tile of width b sits at bits i*b .. of the tile's 4*b words, LSB first; in escape mode the
+    code 2^b - 1 marks a weight whose exponent byte goes to esc."""
+    R, K = exps.shape
+    T = -(-K // TILE)
+    e = np.full((R, T * TILE), table[0], np.uint8)
+    e[:, :K] = exps
+    e = e.reshape(-1, TILE)
+    r = rank[e].astype(np.int64)
+    b, esc_mode = np_f1_choose(r)
+    cmax = (1 << b) - 1
+    escaped = esc_mode[:, None] & (r >= cmax[:, None])
+    codes = np.where(escaped, cmax[:, None], r)
+    start = 4 * (np.cumsum(b) - b)  # first word of each tile
+    words = np.zeros(4 * int(b.sum()), np.uint64)
+    w_idx = np.arange(TILE)
+    for t in range(codes.shape[0]):
+        if b[t] == 0:
+            continue
+        pos = w_idx * b[t]
+        for bit in range(int(b[t])):
+            p = pos + bit
+            np.bitwise_or.at(words, start[t] + (p >> 5), ((codes[t] >> bit) & 1).astype(np.uint64) << (p & 31).astype(np.uint64))
+    meta = (b | np.where(esc_mode, F1_ESCAPE, 0)).astype(np.uint8)
+    return meta, words.astype(np.uint32), e[escaped]
+
+
+def np_f1_decode(meta, idx, esc, table, R: int, K: int) -> np.ndarray:
+    """binade/format.py:104-138: -> exponents [R,K]; ValueError unless the streams are used up
+    exactly."""
+    T = -(-K // TILE)
+    meta = np.asarray(meta).astype(np.int64)
+    b, esc_mode = meta & 0x0F, (meta & F1_ESCAPE) != 0
+    if meta.size != R * T or 32 * np.asarray(idx).size != TILE * int(b.sum()):
+        raise ValueError("format-1 index stream does not fit its tiles")
+    start = 32 * 4 * (np.cumsum(b) - b)  # first bit of each tile
+    w_idx = np.arange(TILE)
+    pos = start[:, None] + w_idx[None, :] * b[:, None]
+    codes = np.zeros((meta.size, TILE), np.int64)
+    words = np.ascontiguousarray(idx, dtype=np.uint32)
+    for bit in range(int(b.max()) if b.size else 0):
+        sel = b > bit
+        codes[sel] |= _bits_at(words, pos[sel] + bit) << bit
+    escaped = esc_mode[:, None] & (codes == ((1 << b) - 1)[:, None])
+    if int(escaped.sum()) != np.asarray(esc).size:
+        raise ValueError("format-1 escape stream does not fit its tiles")
+    e = np.asarray(table)[codes]
+    e[escaped] = esc
+    return e.reshape(R, T * TILE)[:, :K].astype(np.uint8)
+
+
 def np_r4_transcode(ranks: np.ndarray, table: np.ndarray) -> dict:
     """binade/mlx/r4.py:143-175 (and its numpy twin binade/mlx/kernel.py:574-598): codes uint16
     [R*T*32] with nibble j = min(rank, 15) of weight 4l+j, flags uint8 [R*T], esc = table[rank]

@@ -217,6 +217,83 @@ def test_dense_row_remap():
     assert np.array_equal(words(m.dense()), u)
 
 
+# ------------------------------------------------------------------------------ format 1
+@pytest.mark.parametrize("name", ["bench_16x512", "bench_8x128", "wide_6x1280"])
+def test_format1_golden_to_r4_and_bf16(name):
+    """The reference's own format-1 encode output (golden) expands on the GPU to the R4 arrays
+    the reference builds from it (binade/mlx/kernel.py R4Matrix) and unpacks to the tensor."""
+    from binade_b200.cuda import kernels as ck
+    from binade_b200.cuda import r4
+
+    f1, lay = golden("format1.npz")[name], golden("r4_layout.npz")[name]
+    w = lay["w"]
+    R, K = w.shape
+    a = r4.transcode({"raw": lay["raw"], "table": lay["table"], "meta": f1["meta"], "idx": f1["idx"], "esc": f1["esc"]})
+    for k in ("codes", "flags", "esc", "row_esc"):
+        got = a[k].cpu().numpy().view(lay[k].dtype).reshape(-1)
+        assert np.array_equal(got, lay[k].reshape(-1)), k
+    f = ck.Format1(f1["meta"], f1["idx"], f1["esc"], lay["table"], R, K)
+    assert np.array_equal(words(f.unpack(lay["raw"])), w)
+    assert np.array_equal(f.ranks().cpu().numpy()[:, :K], lay["rank"][o.np_split(w)[1]])
+
+
+@pytest.mark.parametrize("R,K", [(40, 100), (7, 4), (33, 704), (12, 3840), (64, 128)])
+def test_format1_shapes_against_oracle(R, K):
+    """Ragged rows, zero-width tiles (a constant tile), fixed and escape tiles, all decoded like
+    the oracle's restatement of format.decode; R4 arrays equal those of the format-2 path."""
+    from binade_b200 import bf16
+    from binade_b200.cuda import kernels as ck
+    from binade_b200.cuda import r4
+    from binade_b200.format import rank_table
+
+    rng = np.random.default_rng(R * 1000 + K)
+    u = weights(rng, (R, K))
+    u[R // 2] = 0x3C00  # a constant row: its tiles need 0 bits
+    raw, exps = o.np_split(u)
+    table, rank = rank_table(np.bincount(exps.reshape(-1), minlength=256))
+    meta, idx, esc = o.np_f1_encode(exps, table, rank)
+    assert np.array_equal(o.np_f1_decode(meta, idx, esc, table, R, K), exps)
+    f = ck.Format1(meta, idx, esc, table, R, K)
+    assert np.array_equal(words(f.unpack(raw)), u)
+    assert np.array_equal(f.ranks().cpu().numpy()[:, :K], rank[exps])
+    if K % 4 == 0:
+        a1 = r4.transcode({"raw": raw, "table": table, "meta": meta, "idx": idx, "esc": esc})
+        a2 = r4.transcode(packed_arrays(u))
+        for k in ("raw", "codes", "flags", "esc", "row_esc", "table"):
+            assert torch.equal(a1[k].reshape(-1), a2[k].reshape(-1)), k
+    with pytest.raises(ValueError):
+        ck.Format1(meta, idx, esc[:-1] if esc.size else np.ones(1, np.uint8), table, R, K)
+    with pytest.raises(ValueError):
+        ck.Format1(meta, np.concatenate([idx, np.zeros(4, np.uint32)]), esc, table, R, K)
+
+
+def test_format1_packed_file_unpacks_and_converts(tmp_path):
+    """A packed shard in format 1 (name.raw/.table/.meta/.idx/.esc, as binade pack --format 1
+    writes it): PackedModel restores the tensor and the hook runs on it."""
+    from binade_b200 import st
+    from binade_b200.cuda import r4
+    from binade_b200.format import rank_table
+    from binade_b200.unpack import PackedModel
+
+    rng = np.random.default_rng(77)
+    u = weights(rng, (3, 40, 256))
+    raw, exps = o.np_split(u)
+    table, rank = rank_table(np.bincount(exps.reshape(-1), minlength=256))
+    meta, idx, esc = o.np_f1_encode(exps.reshape(-1, 256), table, rank)
+    w = st.Writer(tmp_path / "model.safetensors", 4096)
+    name = "model.layers.0.experts.down_proj"
+    for suffix, arr in (("raw", raw), ("table", table), ("meta", meta), ("idx", idx), ("esc", esc)):
+        w.add(f"{name}.{suffix}", arr)
+    w.add("model.norm.weight", np.ones(8, np.float32))
+    w.close()
+    pm = PackedModel(tmp_path)
+    assert pm.packed == [name] and np.array_equal(pm.tensor(name), u)
+    assert len(list(pm.rows(name, chunk=256 * 16))) > 1
+    h = r4.holders(pm)[name]
+    m = r4.R4Linear(r4.transcode(h))
+    assert np.array_equal(words(m.dense()), u)
+
+
 # ------------------------------------------------------------------------------ embedding lookups
 @pytest.mark.parametrize("N,K", [(1000, 384), (257, 100), (64, 4096), (33, 4)])
 def test_embedding_lookups(N, K):

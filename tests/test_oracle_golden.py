@@ -125,3 +125,20 @@ def test_summation_order_is_observable():
     ones = np.full((1, K), 0x3F80, np.uint16)
     assert o.c_dense_rows(ones, wb)[0, 0] == 0
     assert float(w.astype(np.float64).sum()) == 6.0
+
+
+@pytest.mark.parametrize("name", ["bench_16x512", "bench_8x128", "wide_6x1280"])
+def test_format1_oracle_against_reference_vectors(name):
+    """The numpy restatement of format 1 (binade/format.py) writes the reference's own encode
+    output for the golden tensors and decodes it back; a stream that is too short is refused."""
+    f1, lay = golden("format1.npz"), golden("r4_layout.npz")
+    w, table, rank = lay[name]["w"], lay[name]["table"], lay[name]["rank"]
+    raw, exps = o.np_split(w)
+    meta, idx, esc = o.np_f1_encode(exps, table, rank)
+    assert np.array_equal(meta, f1[name]["meta"]) and np.array_equal(idx, f1[name]["idx"]) and np.array_equal(esc, f1[name]["esc"])
+    back = o.np_f1_decode(meta, idx, esc, table, *w.shape)
+    assert np.array_equal(back, exps) and np.array_equal(o.np_join(raw, back), w)
+    with pytest.raises(ValueError):
+        o.np_f1_decode(meta, idx, esc[:-1], table, *w.shape)
+    with pytest.raises(ValueError):
+        o.np_f1_decode(meta, idx[:-4], esc, table, *w.shape)
