@@ -256,15 +256,14 @@ def run_ours(args) -> dict | None:
         # sharded hook multiplies locally and all-gathers the slices (NCCL) in rank order.
         # Projections that share their input in a decoder layer share one collective (q, k, v;
         # gate, up), as the sharded decoder does: four all-gathers per step.
-        from binade_b200.cuda.dist import PushGather, RowShardedGroup
-
-        use_push = os.environ.get("BINADE_B200_GATHER", "push") != "nccl"  # the library's peer-store all-gather, or NCCL
+        from binade_b200.cuda.dist import RowShardedGroup, make_exchange  # the library's peer-store all-gather, or NCCL
 
         by_name = {name: (n, k, mods) for name, n, k, mods, _ in layers}
         groups = [[nm for nm in grp if nm in by_name] for grp in (("q", "k", "v"), ("o",), ("gate", "up"), ("down",))]
         groups = [g for g in groups if g]
-        sharded = [[RowShardedGroup([by_name[nm][2][c] for nm in g], [world * by_name[nm][0] for nm in g], exchange=PushGather(max_bytes=2 * sum(by_name[nm][0] for nm in g)) if use_push else None) for g in groups] for c in range(copies)]
+        sharded = [[RowShardedGroup([by_name[nm][2][c] for nm in g], [world * by_name[nm][0] for nm in g], exchange=make_exchange(max_bytes=2 * sum(by_name[nm][0] for nm in g))) for g in groups] for c in range(copies)]
         group_k = [by_name[g[0]][1] for g in groups]
+        pushed = sharded[0][0].exchange is not None
 
         def step(i: int, inputs=None):
             inputs = inputs or xs
@@ -446,7 +445,7 @@ def run_ours(args) -> dict | None:
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
         "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16 weights (R4 coded), fp32 accumulate", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "copies_rotated": copies, "bytes_per_step": step_bytes, "l2": f"each step streams {step_bytes / 1e6:.0f} MB of distinct weights (> 126 MB L2), {copies} copies rotated", "timing": "CUDA-graph replays (one step per weight copy per graph), CUDA events, max over ranks", "collective": ("peer-store all-gather kernel over NVLink (bn_push_gather)" if os.environ.get("BINADE_B200_GATHER", "push") != "nccl" else "NCCL all-gather") + " of the projection outputs, one per group sharing an input (q k v | o | gate up | down)" if world > 1 else "none"},
+        "config": {"workload": WORKLOAD, "copies_rotated": copies, "bytes_per_step": step_bytes, "l2": f"each step streams {step_bytes / 1e6:.0f} MB of distinct weights (> 126 MB L2), {copies} copies rotated", "timing": "CUDA-graph replays (one step per weight copy per graph), CUDA events, max over ranks", "collective": ("peer-store all-gather kernel over NVLink (bn_push_gather)" if pushed else "NCCL all-gather") + " of the projection outputs, one per group sharing an input (q k v | o | gate up | down)" if world > 1 else "none"},
         "pct_of_nominal_8tbs": round(100 * value / world / NOMINAL_HBM_GBS, 2),
         "bits_per_weight": {"file_format2": round(bits_file / numel, 3), "r4_in_memory": round(bits_r4 / numel, 3)},
         "shapes": per_shape,
@@ -505,7 +504,8 @@ def prefill_leg(torch, dev, graph_us, rows=(2, 4, 8, 16, 32, 128, 2048)) -> dict
 
 def moe_path_leg(torch, dev, graph_us) -> dict:
     """Expert path of a 26B-A4B-style layer: 128 experts, top-8 of uniform random logits, hidden
-    2816, expert FFN 704, token batches 1/8/64; fused gate+up gather, SwiGLU, down gather."""
+    2816, expert FFN 704, token batches 1/8/64; fused gate+up gather, SwiGLU, down gather; a
+    batch with more slots than twice the experts is grouped by expert (weights read once)."""
     from binade_b200.cuda import moe, r4
 
     E, n, D = 128, 704, 2816
@@ -521,7 +521,8 @@ def moe_path_leg(torch, dev, graph_us) -> dict:
         idx = torch.topk(torch.softmax(torch.rand((B, E), device=dev, generator=g), dim=-1), 8, dim=-1).indices
         us = graph_us(lambda i: layer(x, idx), iters=10)
         active = int(torch.unique(idx).numel())
-        out[str(B)] = {"us": round(us, 1), "slots": B * 8, "active_experts": active, "gbs_of_slot_bytes": round(B * 8 * per_expert / us / 1e3, 1), "gbs_of_distinct_expert_bytes": round(active * per_expert / us / 1e3, 1)}
+        grouped = B * 8 >= layer.GROUP_MIN_SLOTS * E  # slots grouped by expert: every active expert is read once
+        out[str(B)] = {"us": round(us, 1), "slots": B * 8, "active_experts": active, "path": "grouped by expert" if grouped else "slot by slot", "gbs_of_slot_bytes": round(B * 8 * per_expert / us / 1e3, 1), "gbs_of_distinct_expert_bytes": round(active * per_expert / us / 1e3, 1)}
     return out
 
 

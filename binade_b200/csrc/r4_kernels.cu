@@ -287,6 +287,15 @@ extern "C" int bn_r4_lookup(const bn_r4 *w, int64_t rows, const uint32_t *ids, i
   return launched("r4_decode_kernel");
 }
 
+extern "C" int bn_r4_gather_grouped(const uint16_t *x, const bn_r4 *w, const uint32_t *xi, const uint32_t *seg, const uint32_t *order, int64_t E, int64_t G, int64_t max_per_expert, int64_t n, int64_t K, int64_t RS, int64_t R0, int64_t split, uint16_t *y, uint16_t *y2, void *stream) {
+  if (int e = check_r4(w)) return e;
+  if (!x || !xi || !seg || !order || !y || E < 1 || G < 0 || max_per_expert < 1 || n < 0 || K <= 0 || split < 0 || split >= (n > 0 ? n : 1)) return fail(BN_ERR_ARG, "bn_r4_gather_grouped: bad size or null pointer");
+  if (split > 0 && !y2) return fail(BN_ERR_ARG, "bn_r4_gather_grouped: split needs y2");
+  if (G == 0 || n == 0) return BN_OK;
+  const int e = stream_gather_grouped(w, x, xi, seg, order, E, G, max_per_expert, n, K, RS, R0, split, y, y2, (cudaStream_t)stream);
+  return e == -1 ? fail(BN_ERR_ARG, "bn_r4_gather_grouped: shape outside the streaming kernel (K % 16, row length, group count): use bn_r4_gather") : e;
+}
+
 extern "C" int bn_r4_rows(const uint16_t *x, int64_t x_stride, const bn_r4 *w, int64_t M, int64_t N, int64_t K, uint16_t *y, int64_t y_stride, void *stream) {
   if (int e = check_r4(w)) return e;
   if (!x || !y || N < 0 || K <= 0 || M < 1 || M > 16) return fail(BN_ERR_ARG, "bn_r4_rows: bad size (1 <= M <= 16) or null pointer");

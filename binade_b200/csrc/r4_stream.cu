@@ -104,6 +104,11 @@ struct StreamArgs {
   const uint32_t *xi, *ei;
   int64_t RS, R0, split;
   uint16_t *y2;
+  // grouped expert gather (M > 1, seg != nullptr): blockIdx.y = expert * chunks + chunk; the
+  // expert's slots are order[seg[e] .. seg[e+1]) (slot numbers sorted by expert), this block
+  // multiplies slots 8 * chunk .. of them (up to M): inputs x[xi[slot]], outputs row `slot`
+  const uint32_t *seg, *order;
+  int chunks;
 };
 
 // Where everything sits in the shared window, by absolute shared address (base = start of the
@@ -282,7 +287,16 @@ __global__ void __launch_bounds__(WARPS * 32, 1) r4_stream_kernel(StreamArgs a) 
   const int64_t workers = (int64_t)gridDim.x * WARPS, me = (int64_t)blockIdx.x * WARPS + warp;
   const int64_t o_begin = a.N * me / workers, o_end = a.N * (me + 1) / workers;  // output rows of this warp
   const int64_t slot = blockIdx.y;
-  const int64_t row0 = a.ei ? (int64_t)a.ei[slot] * a.RS + a.R0 : 0;  // storage row of output row 0
+  // grouped gather: this block's expert, its first slot in `order` and how many slots it takes
+  int64_t g_first = 0;
+  int g_count = a.m;
+  if (a.seg) {
+    const int64_t e = slot / a.chunks, c = slot % a.chunks;
+    g_first = (int64_t)a.seg[e] + c * M;
+    g_count = (int)max((int64_t)0, min((int64_t)M, (int64_t)a.seg[e + 1] - g_first));
+    if (g_count == 0) return;  // whole block: nothing routed here
+  }
+  const int64_t row0 = a.seg ? (slot / a.chunks) * a.RS + a.R0 : a.ei ? (int64_t)a.ei[slot] * a.RS + a.R0 : 0;  // storage row of output row 0
   const int64_t r_begin = row0 + o_begin;
   const int nrows = (int)(o_end - o_begin);
   const int nfull = nrows / RW, ngroups = nfull + (nrows - nfull * RW);
@@ -348,8 +362,10 @@ __global__ void __launch_bounds__(WARPS * 32, 1) r4_stream_kernel(StreamArgs a) 
   const int x_words = M * T * 16;  // 16-byte pieces of x
   auto x_piece = [&](int i) {
     const int m = i / (T * 16), j = i - m * (T * 16);
-    const uint4 *x8 = reinterpret_cast<const uint4 *>(a.x + (a.ei ? (int64_t)a.xi[slot] * K : (int64_t)m * a.x_stride));
-    return (m < a.m && (int64_t)j * 8 < K) ? __ldg(x8 + j) : make_uint4(0, 0, 0, 0);  // K % 16 == 0
+    if (m >= g_count || (int64_t)j * 8 >= K) return make_uint4(0, 0, 0, 0);  // K % 16 == 0
+    const int64_t xrow = a.seg ? (int64_t)a.xi[a.order[g_first + m]] : a.ei ? (int64_t)a.xi[slot] : -1;
+    const uint4 *x8 = reinterpret_cast<const uint4 *>(a.x + (xrow >= 0 ? xrow * K : (int64_t)m * a.x_stride));
+    return __ldg(x8 + j);
   };
   const uint32_t tab_byte = threadIdx.x < 15 ? (uint32_t)__ldg(a.w.table + threadIdx.x) : 0u;
   const uint4 x_first = (int)threadIdx.x < x_words ? x_piece(threadIdx.x) : make_uint4(0, 0, 0, 0);
@@ -451,10 +467,14 @@ __global__ void __launch_bounds__(WARPS * 32, 1) r4_stream_kernel(StreamArgs a) 
         if ((int)lane == i * M + m) mine = s;
       }
     const int li = (int)lane / M, lm = (int)lane % M;  // this lane's (row, input)
-    if (li < (wide ? RW : 1) && lm < a.m) {
+    if (li < (wide ? RW : 1) && lm < g_count) {
       const int64_t r = row - row0 + li;  // output row within the slot
       const uint16_t v = f32_to_bf16_bits(mine);
-      if (M > 1) a.y[(int64_t)lm * a.y_stride + r] = v;
+      if (a.seg) {
+        const int64_t o = a.order[g_first + lm];  // the slot this input row belongs to
+        if (a.split > 0 && r >= a.split) a.y2[o * (a.N - a.split) + (r - a.split)] = v;
+        else a.y[o * (a.split > 0 ? a.split : a.N) + r] = v;
+      } else if (M > 1) a.y[(int64_t)lm * a.y_stride + r] = v;
       else if (a.split > 0 && r >= a.split) a.y2[slot * (a.N - a.split) + (r - a.split)] = v;
       else a.y[slot * (a.split > 0 ? a.split : a.N) + r] = v;
     }
@@ -483,7 +503,7 @@ static int stream_stages(int warps, uint32_t stage, int T, int M, uint32_t base)
 }
 
 template <int WARPS, int RW, int KC, int M = 1>
-static int launch_stream(StreamArgs a, cudaStream_t s, int64_t slots = 1) {
+static int launch_stream(StreamArgs a, cudaStream_t s, int64_t slots = 1, int64_t active = 0) {
   // worst case of the two extremes of the window's start; the kernel re-derives the layout
   // from the real start and refuses to run if it does not fit
   const int stages = min(stream_stages(WARPS, RW * KC * 192, a.T, M, 0), stream_stages(WARPS, RW * KC * 192, a.T, M, ST_BASE_MAX));
@@ -493,7 +513,8 @@ static int launch_stream(StreamArgs a, cudaStream_t s, int64_t slots = 1) {
   if (a.m < 1) a.m = 1;
   auto kern = r4_stream_kernel<WARPS, RW, KC, M>;
   BN_CUDA(allow_smem(kern, a.smem));
-  int64_t blocks = (stream_sms() + slots - 1) / slots;  // blocks per slot: about one block per SM in all
+  if (active < 1 || active > slots) active = slots;  // slots expected to have work (a grouped gather leaves many empty)
+  int64_t blocks = (stream_sms() + active - 1) / active;  // blocks per slot: about one block per SM in all
   const int64_t need = (a.N + WARPS - 1) / WARPS;
   if (blocks > need) blocks = need;
   kern<<<dim3((unsigned)blocks, (unsigned)slots), WARPS * 32, a.smem, s>>>(a);
@@ -527,6 +548,28 @@ int stream_gather(const bn_r4 *w, const uint16_t *x, const uint32_t *xi, const u
   if (e == -1) e = launch_stream<16, 2, 8>(a, s, G);
   if (e == -1) e = launch_stream<8, 2, 8>(a, s, G);
   return e;
+}
+
+// Grouped expert gather: every expert's slots in blocks of M input rows; -1 outside coverage.
+template <int M>
+static int stream_grouped_m(StreamArgs a, cudaStream_t s, int64_t groups, int64_t active) {
+  int e = launch_stream<16, 2, 8, M>(a, s, groups, active);
+  if (e == -1) e = launch_stream<12, 2, 8, M>(a, s, groups, active);
+  if (e == -1) e = launch_stream<8, 2, 8, M>(a, s, groups, active);
+  return e;
+}
+
+int stream_gather_grouped(const bn_r4 *w, const uint16_t *x, const uint32_t *xi, const uint32_t *seg, const uint32_t *order, int64_t E, int64_t G, int64_t max_per_expert, int64_t n, int64_t K, int64_t RS, int64_t R0, int64_t split, uint16_t *y, uint16_t *y2, cudaStream_t s) {
+  const int64_t T = tiles(K);
+  if (K % 16 || n < 1 || T > 200 || E < 1 || max_per_expert < 1) return -1;
+  const int m = max_per_expert <= 4 ? 4 : 8;
+  const int64_t chunks = (max_per_expert + m - 1) / m;
+  if (E * chunks > 65535) return -1;
+  StreamArgs a{};
+  a.w = *w, a.x = x, a.y = y, a.y2 = y2, a.N = n, a.K = K, a.T = (int)T, a.m = m;
+  a.xi = xi, a.RS = RS, a.R0 = R0, a.split = split, a.seg = seg, a.order = order, a.chunks = (int)chunks;
+  const int64_t active = G < E ? G : E;  // experts with work: at most one per slot
+  return m == 4 ? stream_grouped_m<4>(a, s, E * chunks, active) : stream_grouped_m<8>(a, s, E * chunks, active);
 }
 
 // 2..8 input rows through the streaming kernel (weights stream once, M accumulators per weight

@@ -11,6 +11,7 @@ reference is single-device; this module is the multi-GPU form of its linear-laye
   RowShardedGroup(locals, Ns, ...) several projections of the same input (q, k, v; gate, up)
                                    with one all-gather for all of them
 
+  make_exchange(group, max_bytes)  a PushGather, or None when the ranks should stay on NCCL
   PushGather(group, max_bytes)     the all-gather as one kernel of this library over NVLink peer
                                    memory (symmetric buffers from torch.distributed); the sharded
                                    modules take it as `exchange=` in place of the NCCL call
@@ -164,6 +165,29 @@ class PushGather:
             src = flat
         data = self._push([src])[0][:, :nbytes]
         return data.reshape(self.world, nbytes).view(flat.dtype).view(self.world, *flat.shape)
+
+
+def make_exchange(group=None, max_bytes: int = 1 << 20):
+    """A PushGather for the group, or None (the sharded modules then use the library collective)
+    when BINADE_B200_GATHER=nccl, when the ranks are not CUDA ranks, or when any rank could not set
+    the symmetric buffers up; the ranks agree on the outcome with one all-reduce, so they never
+    end up on different collectives. Collective: every rank of the group calls it."""
+    import os
+    import sys
+
+    import torch.distributed as dist
+
+    if os.environ.get("BINADE_B200_GATHER", "push") == "nccl" or not torch.cuda.is_available() or dist.get_backend(group) != "nccl":
+        return None
+    ex, ok = None, 1
+    try:
+        ex = PushGather(group, max_bytes)
+    except Exception as e:  # noqa: BLE001 - any set-up failure means "use the library collective"
+        print(f"[binade_b200] peer-store exchange unavailable ({type(e).__name__}: {e}); using NCCL all-gather", file=sys.stderr, flush=True)
+        ok = 0
+    flag = torch.tensor([ok], device="cuda", dtype=torch.int32)
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=group)
+    return ex if int(flag.item()) == 1 else None
 
 
 def _all_gather(flat: torch.Tensor, world: int, group, exchange) -> torch.Tensor:

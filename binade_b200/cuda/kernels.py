@@ -43,7 +43,9 @@ def _p(t):
 
 
 def _stream():
-    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    """The current CUDA stream's handle (the raw query: building a torch Stream object per kernel
+    call costs more host time than the launch)."""
+    return ctypes.c_void_p(torch._C._cuda_getCurrentRawStream(torch.cuda.current_device()))
 
 
 def _call(fn, *args):
@@ -206,6 +208,26 @@ def r4_decode(a: dict, N: int, K: int, nb: int | None = None, rs: int | None = N
     return out
 
 
+def r4_gather_grouped(a: dict, x: torch.Tensor, xi: torch.Tensor, ei: torch.Tensor, E: int, max_per_expert: int, n: int, rs: int, r0: int, K: int, split: int | None = None):
+    """r4_gather's outputs with every expert's rows read once for all its slots: the slots are
+    sorted by expert on the device (no host sync) and each expert multiplies up to 8 input rows
+    per pass. ei: int32 [G] expert of each slot (0 <= ei < E); max_per_expert bounds the slots of
+    one expert (the token count when a token names an expert at most once). K % 16 == 0."""
+    G = ei.numel()
+    dev = x.device
+    order = torch.argsort(ei, stable=True).to(torch.int32)
+    counts = torch.zeros(E, dtype=torch.int32, device=dev).scatter_add_(0, ei.to(torch.int64), torch.ones(G, dtype=torch.int32, device=dev))  # (bincount would synchronise)
+    seg = torch.zeros(E + 1, dtype=torch.int32, device=dev)
+    seg[1:] = torch.cumsum(counts, 0).to(torch.int32)
+    if split:
+        y = torch.empty((G, split), dtype=torch.bfloat16, device=dev)
+        y2 = torch.empty((G, n - split), dtype=torch.bfloat16, device=dev)
+    else:
+        y, y2 = torch.empty((G, n), dtype=torch.bfloat16, device=dev), None
+    _call("bn_r4_gather_grouped", _p(x), ctypes.byref(r4_struct(a)), _p(xi), _p(seg), _p(order), E, G, max_per_expert, n, K, rs, r0, split or 0, _p(y), _p(y2))
+    return (y, y2) if split else y
+
+
 def r4_mma(a: dict, x: torch.Tensor, N: int, K: int) -> torch.Tensor:
     """x [M, K] (1 <= M <= 128, bfloat16, contiguous rows, K % 8 == 0) -> [M, N] through the fused
     decode GEMM on the tensor cores (tcgen05); accumulation order is the hardware's."""
@@ -246,10 +268,11 @@ def r4_rows(a: dict, x: torch.Tensor, N: int, K: int) -> torch.Tensor:
     return y
 
 
-def r4_matvec(a: dict, x: torch.Tensor, N: int, K: int) -> torch.Tensor:
-    """x [..., K] holding one row -> [..., N] (reference: r4_matvec, cuda_kernels.py:118-130)."""
+def r4_matvec(a: dict, x: torch.Tensor, N: int, K: int, struct=None) -> torch.Tensor:
+    """x [..., K] holding one row -> [..., N] (reference: r4_matvec, cuda_kernels.py:118-130).
+    `struct`: the bn_r4 of `a` when the caller keeps one (saves rebuilding it per call)."""
     y = torch.empty((*x.shape[:-1], N), dtype=torch.bfloat16, device=x.device)
-    _call("bn_r4_rows", _p(x), K, ctypes.byref(r4_struct(a)), 1, N, K, _p(y), N)
+    _call("bn_r4_rows", _p(x), K, ctypes.byref(struct if struct is not None else r4_struct(a)), 1, N, K, _p(y), N)
     return y
 
 

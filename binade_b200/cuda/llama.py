@@ -16,14 +16,13 @@ BINADE_B200_GATHER=nccl.
 from __future__ import annotations
 
 import math
-import os
 from dataclasses import dataclass
 
 import torch
 from torch import nn
 
 from . import r4
-from .dist import PushGather, RowShardedLinear, row_range
+from .dist import RowShardedLinear, make_exchange, row_range
 
 
 @dataclass
@@ -72,9 +71,7 @@ class Decoder(nn.Module):
         # the all-gathers go through this library's peer-store kernel (one shared buffer: every
         # gathered vector is consumed before the next exchange in stream order);
         # BINADE_B200_GATHER=nccl keeps them on the library collective
-        self.exchange = None
-        if world > 1 and dev.type == "cuda" and os.environ.get("BINADE_B200_GATHER", "push") != "nccl":
-            self.exchange = PushGather(group, max_bytes=2 * max(s.vocab, s.ffn, s.heads * d, s.hidden) // world + 64)
+        self.exchange = make_exchange(group, max_bytes=2 * max(s.vocab, s.ffn, s.heads * d, s.hidden) // world + 64) if world > 1 and dev.type == "cuda" else None
 
         def lin(w_rows: torch.Tensor, n_total: int):
             local = r4.R4Linear(r4.from_dense(w_rows)) if kind == "r4" else DenseLinear(w_rows)

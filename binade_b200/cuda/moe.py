@@ -37,12 +37,26 @@ class R4SwitchGLU(nn.Module):
             raise ValueError("gate_up must keep its [E, 2n, D] shape")
         self.n, self.D = shape_gu[1] // 2, shape_dn[1]
 
-    def slots(self, x: torch.Tensor, xi: torch.Tensor, ei: torch.Tensor) -> torch.Tensor:
-        """[G, D] outputs of G (token row xi[g], expert ei[g]) slots; x [tokens, D]."""
-        n = self.n
+    GROUP_MIN_SLOTS = 2  # from this many slots per expert on average, group the slots by expert
+
+    def slots(self, x: torch.Tensor, xi: torch.Tensor, ei: torch.Tensor, max_per_expert: int | None = None) -> torch.Tensor:
+        """[G, D] outputs of G (token row xi[g], expert ei[g]) slots; x [tokens, D]. With more
+        slots than experts (a batch of tokens), the slots are grouped by expert so that every
+        active expert's weights are read once (same bits as slot by slot); max_per_expert bounds
+        the slots of one expert (default: the token count, right when a token names an expert at
+        most once, as top-k routing does)."""
+        n, G = self.n, ei.numel()
+        rows = torch.arange(G, dtype=torch.int32, device=x.device)
+        if G >= self.GROUP_MIN_SLOTS * self.E:
+            cap = max_per_expert or x.shape[0]
+            gu = self._gu._gather_grouped(x, xi, ei, self.E, cap, 2 * n, 2 * n, split=n)
+            if gu is not None:
+                h = self._activation(gu[1], gu[0])
+                out = self._down._gather_grouped(h, rows, ei, self.E, cap, self.D, self.D)
+                if out is not None:
+                    return out
         gate, up = self._gu._gather(x, xi, ei, 2 * n, 2 * n, split=n)
         h = self._activation(up, gate)
-        rows = torch.arange(ei.numel(), dtype=torch.int32, device=x.device)
         return self._down._gather(h, rows, ei, self.D, self.D)
 
     def forward(self, x: torch.Tensor, indices: torch.Tensor) -> torch.Tensor:

@@ -132,15 +132,23 @@ class _R4:
         self._a = a
         self.N, self.K = a["raw"].shape
         self.T = -(-self.K // TILE)
+        self._struct = ck.r4_struct(a)  # device addresses of the arrays above, which this object keeps alive
 
     def _matvec(self, x: torch.Tensor) -> torch.Tensor:
         """x [..., K] holding one row -> [..., N]."""
-        return ck.r4_matvec(self._a, x.contiguous(), self.N, self.K)
+        return ck.r4_matvec(self._a, x.contiguous(), self.N, self.K, self._struct)
 
     def _gather(self, x, xi, ei, n: int, rs: int, r0: int = 0, *, split: int | None = None, shape: tuple | None = None):
         """[G, n] outputs (or `shape`): pair g multiplies input row xi[g] of x [.., K] by storage
         rows ei[g] * rs + r0 .. + n. With split, the pair [G, split], [G, n - split]."""
         return ck.r4_gather(self._a, x.contiguous(), xi.to(torch.int32), ei.reshape(-1).to(torch.int32), n, rs, r0, self.K, split, shape)
+
+    def _gather_grouped(self, x, xi, ei, E: int, max_per_expert: int, n: int, rs: int, r0: int = 0, *, split: int | None = None):
+        """_gather's outputs with every expert's rows read once for all the slots routed to it
+        (bit-identical results); None when the shape is outside the grouped kernel (K % 16)."""
+        if self.K % 16 or self.T > 200:
+            return None
+        return ck.r4_gather_grouped(self._a, x.contiguous(), xi.to(torch.int32), ei.reshape(-1).to(torch.int32), E, max_per_expert, n, rs, r0, self.K, split)
 
     def dense(self, n: int | None = None, rs: int | None = None, r0: int = 0) -> torch.Tensor:
         """The BF16 weight, rebuilt from R4. With n, rs, r0: rows r0 .. r0 + n - 1 of every block of

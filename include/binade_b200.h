@@ -190,6 +190,19 @@ int bn_r4_gather(const uint16_t *x, const bn_r4 *w, const uint32_t *xi, const ui
                  int64_t n, int64_t K, int64_t RS, int64_t R0, int64_t split, uint16_t *y,
                  uint16_t *y2, void *stream);
 
+/* The same products as bn_r4_gather for G slots, grouped by expert so that an expert's rows are
+ * read once for all the slots routed to it (prefill / batched decode of an MoE layer; reference:
+ * _gather_mm, binade/mlx/r4.py:225-243, which sorts the slots by expert for its gather GEMM).
+ * order [G]: slot numbers sorted by expert; seg [E+1]: expert e owns order[seg[e] .. seg[e+1]);
+ * xi [G]: input row of each slot; max_per_expert: an upper bound of seg[e+1] - seg[e] (the token
+ * count, when a token names an expert at most once). Outputs as bn_r4_gather, row = slot number.
+ * Every output keeps the documented summation order: results are bit-identical to bn_r4_gather.
+ * Needs K % 16 == 0. */
+int bn_r4_gather_grouped(const uint16_t *x, const bn_r4 *w, const uint32_t *xi, const uint32_t *seg,
+                         const uint32_t *order, int64_t E, int64_t G, int64_t max_per_expert,
+                         int64_t n, int64_t K, int64_t RS, int64_t R0, int64_t split, uint16_t *y,
+                         uint16_t *y2, void *stream);
+
 /* All-gather of small slices over NVLink peer memory, one kernel per rank (multi-GPU form of the
  * hook; the reference is single-device, so there is no counterpart). Every rank calls it with
  * 1..4 segments (one per projection): `locals[g]` is this rank's slice of segment g, `bytes[g]`

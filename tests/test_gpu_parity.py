@@ -500,6 +500,32 @@ def test_order_sensitive_gather():
     assert np.array_equal(words(got), want)
 
 
+@pytest.mark.parametrize("tokens,E,topk", [(16, 8, 2), (40, 6, 3), (9, 4, 4)])
+def test_grouped_gather_equals_slot_by_slot(tokens, E, topk):
+    """Slots grouped by expert (each expert's rows read once for all its tokens) give the bits
+    of the slot-by-slot gather, through the kernels and through R4SwitchGLU."""
+    from binade_b200.cuda import moe, r4
+
+    n, D = 48, 256
+    rng = np.random.default_rng(tokens + E)
+    gu = r4.R4Linear(r4.transcode(packed_arrays(weights(rng, (E, 2 * n, D)))))
+    dn = r4.R4Linear(r4.transcode(packed_arrays(weights(rng, (E, D, n), escapes=False))))
+    x = dev(bf16_words(rng.standard_normal((tokens, D)))).view(torch.bfloat16)
+    idx = torch.stack([torch.randperm(E, generator=torch.Generator().manual_seed(t))[:topk] for t in range(tokens)]).cuda()
+    ei = idx.reshape(-1).to(torch.int32)
+    xi = torch.arange(ei.numel(), dtype=torch.int32, device="cuda") // topk
+    g1, u1 = gu._gather(x, xi, ei, 2 * n, 2 * n, split=n)
+    g2, u2 = gu._gather_grouped(x, xi, ei, E, tokens, 2 * n, 2 * n, split=n)
+    assert np.array_equal(words(g1), words(g2)) and np.array_equal(words(u1), words(u2))
+    plain = gu._gather(x, xi, ei, 2 * n, 2 * n)
+    assert np.array_equal(words(gu._gather_grouped(x, xi, ei, E, tokens, 2 * n, 2 * n)), words(plain))
+    glu = moe.R4SwitchGLU(gu, dn)
+    assert tokens * topk >= glu.GROUP_MIN_SLOTS * E  # the grouped path is the one taken
+    y = glu(x, idx)
+    glu.GROUP_MIN_SLOTS = 1 << 30  # slot by slot
+    assert np.array_equal(words(y), words(glu(x, idx)))
+
+
 def test_convert_swaps_holders():
     from binade_b200.cuda import r4
 
