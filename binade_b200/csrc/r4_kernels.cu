@@ -2,6 +2,8 @@
 // expert gather). One warp owns whole weight rows; lane l owns weights 128t + 4l + j of every
 // tile t, which is both the layout of an R4 lane word (4 raw bytes + one uint16 of codes) and
 // the documented summation order.
+#include <stdlib.h>
+
 #include "common.cuh"
 #include "decode.cuh"
 
@@ -310,7 +312,8 @@ extern "C" int bn_r4_rows(const uint16_t *x, int64_t x_stride, const bn_r4 *w, i
   if (M == 1) {
     // long rows: the register-pipelined kernel (its x and table leave no room for deep rings
     // anyway); otherwise the streaming kernel, which needs K % 16 == 0; then whichever is left
-    int e = K >= 8192 ? direct_matvec(w, x, N, K, y, s) : -1;
+    static const bool stream_long = getenv("BINADE_B200_STREAM_LONG") != nullptr;  // experiments: long rows through the streaming kernel too
+    int e = (K >= 8192 && !stream_long) ? direct_matvec(w, x, N, K, y, s) : -1;
     if (e == -1) e = stream_matvec(w, x, N, K, y, s);
     if (e == -1) e = direct_matvec(w, x, N, K, y, s);
     if (e >= 0) return e;

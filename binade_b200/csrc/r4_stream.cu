@@ -112,20 +112,24 @@ struct StreamArgs {
 };
 
 // Where everything sits in the shared window, by absolute shared address (base = start of the
-// dynamic allocation): [base, 64K) and [128K, end) hold x, the mbarriers and the per-warp rings,
-// [64K, 128K) the pair table. One input row: x below the table; several: x above it.
+// dynamic allocation): [base, 64K) and [128K, end) hold the mbarriers and the per-warp rings,
+// [64K, 128K) the pair table. An entry of the table is 256 bytes of which the lanes use the first
+// 128: with one input row, x lives in the other halves (tile t's 256 bytes in the halves of
+// entries 2t and 2t + 1, so a lane's address still grows by a constant per tile: 512 bytes, and
+// K <= 16384); with several input rows, x sits above the table.
 struct StreamLayout {
-  uint32_t x_at, bar_at, pool_a, pool_c, in_a, end;
+  uint32_t x_at, bar_at, tab_at, pool_a, pool_c, in_a, end;
 };
 __host__ __device__ inline StreamLayout stream_layout(uint32_t base, int T, int M, int warps, int S, uint32_t stage) {
   StreamLayout L;
   const uint32_t a0 = (base + 15u) & ~15u, xbytes = (uint32_t)M * (uint32_t)T * 256u, ring = (uint32_t)S * stage;
   if (M == 1) {
-    L.x_at = a0, L.bar_at = a0 + xbytes, L.pool_c = 131072u;
+    L.x_at = 65536u + 128u, L.bar_at = a0, L.pool_c = 131072u;  // x in the unused halves of the table's entries
   } else {
     L.bar_at = a0, L.x_at = 131072u, L.pool_c = (131072u + xbytes + 127u) & ~127u;
   }
-  L.pool_a = (L.bar_at + (uint32_t)warps * S * 8u + 127u) & ~127u;
+  L.tab_at = (L.bar_at + (uint32_t)warps * S * 8u + 15u) & ~15u;  // 16 exponent words while the table is built
+  L.pool_a = (L.tab_at + 64u + 127u) & ~127u;
   L.in_a = L.pool_a < 65536u ? (65536u - L.pool_a) / ring : 0u;  // warps whose rings sit below the table
   if (L.in_a > (uint32_t)warps) L.in_a = warps;
   L.end = L.pool_c + ((uint32_t)warps - L.in_a) * ring;
@@ -166,6 +170,10 @@ __device__ __forceinline__ void escape_patch(uint32_t c, const uint8_t *__restri
   }
 }
 
+// Bytes from one tile's x to the next in shared memory (see StreamLayout).
+template <int M>
+constexpr uint32_t X_TILE = M == 1 ? 512u : 256u;
+
 // The M input rows' four BF16 values of one tile for this lane: row m sits `xrow` bytes after
 // row m-1 in shared memory.
 template <int M, int OFF>
@@ -192,7 +200,7 @@ template <int RWG, int NT, int M, uint32_t RAW_ROW, uint32_t CODE_ROW, int U = 0
 __device__ __forceinline__ void block_fma(uint32_t raw, uint32_t codes, uint32_t xs, uint32_t xrow, uint32_t lut, uint32_t token, float (&acc)[RWG][M]) {
   if constexpr (U < NT) {
     uint2 xv[M];
-    x_tile<M, U * 256>(xs, xrow, token, xv);
+    x_tile<M, U * X_TILE<M>>(xs, xrow, token, xv);
     word_fma<0, U, M, RAW_ROW, CODE_ROW>(raw, codes, lut, token, xv, acc[0]);
     if constexpr (RWG > 1) word_fma<1, U, M, RAW_ROW, CODE_ROW>(raw, codes, lut, token, xv, acc[1]);
     if constexpr (RWG > 2) word_fma<2, U, M, RAW_ROW, CODE_ROW>(raw, codes, lut, token, xv, acc[2]);
@@ -238,7 +246,7 @@ __device__ __forceinline__ void consume_stage(uint32_t raw, uint32_t codes, uint
   for (int b = 0; b < NB; b++) {
     const int left = nt - b * BT;
     if (left <= 0) break;
-    const uint32_t braw = raw + b * BT * 128, bcodes = codes + b * BT * 64, bxs = xs + b * BT * 256;
+    const uint32_t braw = raw + b * BT * 128, bcodes = codes + b * BT * 64, bxs = xs + b * BT * X_TILE<M>;
     const bool tail = partial && left <= BT;  // this block holds the partial tile
     if (left >= BT && !tail && !((any >> (b * BT)) & ((1u << BT) - 1u))) {
       block_fma<RWG, BT, M, RAW_ROW, CODE_ROW>(braw, bcodes, bxs, xrow, lut, token, acc);
@@ -247,7 +255,7 @@ __device__ __forceinline__ void consume_stage(uint32_t raw, uint32_t codes, uint
       for (int k = 0; k < n; k++) {
         const bool in = lane_in_partial || !(tail && k == n - 1);
         uint2 xv[M];
-        x_tile<M, 0>(bxs + k * 256, xrow, token, xv);
+        x_tile<M, 0>(bxs + k * X_TILE<M>, xrow, token, xv);
         careful_tile<RWG, M, RAW_ROW, CODE_ROW>(braw + k * 128, bcodes + k * 64, lut, token, xv, b * BT + k, in, fbits, esc, epos, acc);
       }
     }
@@ -375,11 +383,16 @@ __global__ void __launch_bounds__(WARPS * 32, 1) r4_stream_kernel(StreamArgs a) 
   // x and the pair table into shared memory (whole block). The 15 table bytes go through shared
   // memory first, so the 8192 table words are built from on-chip reads.
   {
-    uint32_t *s_tab = reinterpret_cast<uint32_t *>(smem_raw + (65536u + 128u - base));  // an unused half of table entry 0
+    uint32_t *s_tab = reinterpret_cast<uint32_t *>(smem_raw + (L.tab_at - base));
     if (threadIdx.x < 16) s_tab[threadIdx.x] = tab_byte;
-    uint4 *dst = reinterpret_cast<uint4 *>(smem_raw + (x_at - base));
-    if ((int)threadIdx.x < x_words) dst[threadIdx.x] = x_first;
-    for (int i = threadIdx.x + THREADS; i < x_words; i += THREADS) dst[i] = x_piece(i);
+    // 16-byte piece i of x: input row i / (T * 16), piece j of that row = bytes 16 j .. of it
+    auto x_dst = [&](int i) {
+      if (M > 1) return reinterpret_cast<uint4 *>(smem_raw + (x_at - base)) + i;
+      const uint32_t t = (uint32_t)i >> 4, p = (uint32_t)i & 15u;  // tile, piece of the tile
+      return reinterpret_cast<uint4 *>(smem_raw + (x_at - base) + (2u * t + (p >> 3)) * 256u + (p & 7u) * 16u);
+    };
+    if ((int)threadIdx.x < x_words) *x_dst(threadIdx.x) = x_first;
+    for (int i = threadIdx.x + THREADS; i < x_words; i += THREADS) *x_dst(i) = x_piece(i);
     __syncthreads();
     uint32_t *lut = reinterpret_cast<uint32_t *>(smem_raw + (65536u - base));
 #pragma unroll 4
@@ -409,7 +422,7 @@ __global__ void __launch_bounds__(WARPS * 32, 1) r4_stream_kernel(StreamArgs a) 
       for (int m = 0; m < M; m++) acc[i][m] = 0.0f;
     }
     if (g + 1 < ngroups) prefetch_epos(g + 1);
-    uint32_t xs = x_at + lane * 8;
+    uint32_t xs = M == 1 ? x_at + (lane >> 4) * 256u + (lane & 15u) * 8u : x_at + lane * 8u;
     for (int c = 0; c < nchunks; c++) {
       const int t0 = c * KC;
       if ((t0 & 31) == 0) {
@@ -445,7 +458,7 @@ __global__ void __launch_bounds__(WARPS * 32, 1) r4_stream_kernel(StreamArgs a) 
 #pragma unroll
         for (int m = 0; m < M; m++) acc[0][m] = ac1[0][m];
       }
-      xs += KC * 256;
+      xs += KC * X_TILE<M>;
       // every read of the slot feeds an accumulator: pin them before the slot is refilled
 #pragma unroll
       for (int i = 0; i < RW; i++)
@@ -526,10 +539,15 @@ static int launch_stream(StreamArgs a, cudaStream_t s, int64_t slots = 1, int64_
 // the shared window next to x is taken (24 warps for K = 3840, 20 for K = 15360).
 int stream_matvec(const bn_r4 *w, const uint16_t *x, int64_t N, int64_t K, uint16_t *y, cudaStream_t s) {
   const int64_t T = tiles(K);
-  if (K % 16 || N < 1 || T > 200) return -1;
+  if (K % 16 || N < 1 || T > 128) return -1;  // x lives in the table's 256 half entries, two per tile
   StreamArgs a{};
   a.w = *w, a.x = x, a.y = y, a.N = N, a.K = K, a.T = (int)T;
-  int e = launch_stream<24, 2, 8>(a, s);
+  // 26 warps when that evens the rows out (15360 rows over 148 SMs: 104 per SM = 26 x 4, against
+  // 4 or 5 per warp with 24), else the widest block whose rings fit
+  const int64_t per_sm = (N + stream_sms() - 1) / stream_sms();
+  int e = -1;
+  if ((per_sm + 25) / 26 < (per_sm + 23) / 24) e = launch_stream<26, 2, 8>(a, s);
+  if (e == -1) e = launch_stream<24, 2, 8>(a, s);
   if (e == -1) e = launch_stream<20, 2, 8>(a, s);
   if (e == -1) e = launch_stream<16, 2, 8>(a, s);
   if (e == -1) e = launch_stream<8, 2, 8>(a, s);
@@ -539,7 +557,7 @@ int stream_matvec(const bn_r4 *w, const uint16_t *x, int64_t N, int64_t K, uint1
 // Expert gather through the streaming kernel; -1 when the shape is outside its coverage.
 int stream_gather(const bn_r4 *w, const uint16_t *x, const uint32_t *xi, const uint32_t *ei, int64_t G, int64_t n, int64_t K, int64_t RS, int64_t R0, int64_t split, uint16_t *y, uint16_t *y2, cudaStream_t s) {
   const int64_t T = tiles(K);
-  if (K % 16 || n < 1 || T > 200 || G < 1 || G > 65535) return -1;
+  if (K % 16 || n < 1 || T > 128 || G < 1 || G > 65535) return -1;
   StreamArgs a{};
   a.w = *w, a.x = x, a.y = y, a.y2 = y2, a.N = n, a.K = K, a.T = (int)T;
   a.xi = xi, a.ei = ei, a.RS = RS, a.R0 = R0, a.split = split;
