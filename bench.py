@@ -478,7 +478,7 @@ def run_ours(args) -> dict | None:
     return result
 
 
-def prefill_leg(torch, dev, graph_us, rows=(2, 4, 8, 16, 32, 128, 2048)) -> dict:
+def prefill_leg(torch, dev, graph_us, rows=(2, 4, 8, 16, 32, 128, 256, 512, 2048)) -> dict:
     """Fused decode products for short prompts on the gate projection (15360 x 3840): M rows of
     N(0,1) inputs; up to FUSED_MAX_ROWS rows run the fused kernel in the documented order, up to
     MMA_MAX_ROWS the tensor-core decode GEMM (weights stream once in both), more rows rebuild the
@@ -495,9 +495,9 @@ def prefill_leg(torch, dev, graph_us, rows=(2, 4, 8, 16, 32, 128, 2048)) -> dict
         x = torch.randn((M, k), device=dev, generator=torch.Generator(device=dev).manual_seed(M)).to(torch.bfloat16)
         us = graph_us(lambda i: m(x), iters=10)
         us_ref = graph_us(lambda i: torch.matmul(x, w.T), iters=10)
-        path = "fused rows" if M <= r4.FUSED_MAX_ROWS else "tcgen05 decode GEMM" if M <= r4.MMA_MAX_ROWS else "rebuild + cuBLAS"
+        path = "fused rows" if M <= r4.FUSED_MAX_ROWS else "tcgen05 decode GEMM" if M <= r4.MMA_MAX_ROWS * r4.MMA_MAX_PASSES else "rebuild + cuBLAS"
         out[str(M)] = {"us": round(us, 1), "cublas_bf16_us": round(us_ref, 1), "vs_cublas": round(us_ref / us, 3), "path": path}
-        if M <= r4.MMA_MAX_ROWS:
+        if M <= r4.MMA_MAX_ROWS * r4.MMA_MAX_PASSES:
             out[str(M)]["rebuild_us"] = round(graph_us(lambda i: x @ m.dense().reshape(n, k).T, iters=10), 1)
     return out
 

@@ -1,4 +1,4 @@
-// Fused R4-decode GEMM for 16..128 input rows on the 5th-generation tensor cores (tcgen05):
+// Fused R4-decode GEMM for up to 256 input rows on the 5th-generation tensor cores (tcgen05):
 //   Y[m, n] = sum_k X[m, k] W[n, k]      X [M, K] BF16, W [N, K] in R4, Y [M, N] BF16
 // computed as D = W_tile . X^T so that the few input rows sit in the MMA's N dimension:
 //   A operand  up to 112 weight rows x 128 k, decoded from R4 to BF16 by the CUDA cores straight
@@ -298,9 +298,9 @@ static int mma_sms() {
   return n;
 }
 
-// Fused decode GEMM for up to 128 input rows; -1 when the shape is outside its coverage.
+// Fused decode GEMM for up to 256 input rows (the MMA's largest N); -1 when the shape is outside its coverage.
 int mma_rows(const bn_r4 *w, const uint16_t *x, int64_t x_stride, int64_t M, int64_t N, int64_t K, uint16_t *y, int64_t y_stride, cudaStream_t s) {
-  if (M < 1 || M > 128 || K % 8 || x_stride % 8 || N < 1 || ((uintptr_t)x & 15)) return -1;
+  if (M < 1 || M > 256 || K % 8 || x_stride % 8 || N < 1 || ((uintptr_t)x & 15)) return -1;
   TensorMapEncodeFn encode = tensor_map_encoder();
   if (!encode) return fail(BN_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
   MmaArgs a{};
@@ -354,7 +354,7 @@ int mma_status(int *status) {
 
 extern "C" int bn_r4_mma(const uint16_t *x, int64_t x_stride, const bn_r4 *w, int64_t M, int64_t N, int64_t K, uint16_t *y, int64_t y_stride, void *stream) {
   if (!w || !w->raw || !w->codes || !w->flags || !w->esc || !w->table || !w->row_esc) return bn::fail(BN_ERR_ARG, "bn_r4_mma: null R4 array");
-  if (!x || !y || N < 0 || K <= 0 || M < 1 || M > 128) return bn::fail(BN_ERR_ARG, "bn_r4_mma: bad size (1 <= M <= 128) or null pointer");
+  if (!x || !y || N < 0 || K <= 0 || M < 1 || M > 256) return bn::fail(BN_ERR_ARG, "bn_r4_mma: bad size (1 <= M <= 256) or null pointer");
   if (K % 8 || x_stride % 8) return bn::fail(BN_ERR_ARG, "bn_r4_mma needs K % 8 == 0 and x rows 16-byte aligned");
   if (N == 0) return BN_OK;
   const int e = bn::mma_rows(w, x, x_stride, M, N, K, y, y_stride, (cudaStream_t)stream);

@@ -229,7 +229,7 @@ def r4_gather_grouped(a: dict, x: torch.Tensor, xi: torch.Tensor, ei: torch.Tens
 
 
 def r4_mma(a: dict, x: torch.Tensor, N: int, K: int) -> torch.Tensor:
-    """x [M, K] (1 <= M <= 128, bfloat16, contiguous rows, K % 8 == 0) -> [M, N] through the fused
+    """x [M, K] (1 <= M <= 256, bfloat16, contiguous rows, K % 8 == 0) -> [M, N] through the fused
     decode GEMM on the tensor cores (tcgen05); accumulation order is the hardware's."""
     M = x.shape[0]
     y = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)

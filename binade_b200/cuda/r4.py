@@ -29,7 +29,10 @@ from . import kernels as ck
 FUSED_MAX_ROWS = 4  # input rows served by the fused decode kernel in the documented order (15360 x 3840: 37 / 49 / 75 us at 2 / 4 / 8 rows); from 5 rows the tensor-core decode GEMM is faster (46 us)
 
 
-MMA_MAX_ROWS = 128  # input rows served by the tensor-core decode GEMM (one pass over the weights); beyond, rebuild + cuBLAS
+MMA_MAX_ROWS = 256  # input rows served by the tensor-core decode GEMM (one pass over the weights; 256 is the MMA's widest N); beyond, rebuild + cuBLAS
+
+
+MMA_MAX_PASSES = 2  # passes of MMA_MAX_ROWS rows that still beat rebuild + cuBLAS (15360 x 3840: 55 us a pass against 108 us for the rebuild)
 
 
 class BinadeLinear(nn.Module):
@@ -164,10 +167,15 @@ class _R4:
         return ck.r4_rows(self._a, x.reshape(M, self.K).contiguous(), self.N, self.K).reshape(*x.shape[:-1], self.N)
 
     def mma_rows(self, x: torch.Tensor) -> torch.Tensor:
-        """x [..., K] with up to 128 rows -> [..., N] through the tensor-core decode GEMM (weights
+        """x [..., K] -> [..., N] through the tensor-core decode GEMM, 256 rows a pass (weights
         decoded to BF16 inside the kernel and read once; the sum over K in the hardware's order)."""
         M = x.numel() // self.K
-        return ck.r4_mma(self._a, x.reshape(M, self.K).contiguous(), self.N, self.K).reshape(*x.shape[:-1], self.N)
+        x2 = x.reshape(M, self.K).contiguous()
+        if M <= MMA_MAX_ROWS:
+            y = ck.r4_mma(self._a, x2, self.N, self.K)
+        else:  # a pass over the weights per 256 rows: still cheaper than rebuilding them for a few passes
+            y = torch.cat([ck.r4_mma(self._a, x2[m0 : m0 + MMA_MAX_ROWS], self.N, self.K) for m0 in range(0, M, MMA_MAX_ROWS)])
+        return y.reshape(*x.shape[:-1], self.N)
 
     def _rows(self, x: torch.Tensor) -> torch.Tensor:
         M = x.numel() // self.K
@@ -175,7 +183,7 @@ class _R4:
             return self._matvec(x)
         if M <= FUSED_MAX_ROWS:
             return self.fused_rows(x)
-        if M <= MMA_MAX_ROWS and self.K % 8 == 0:
+        if M <= MMA_MAX_PASSES * MMA_MAX_ROWS and self.K % 8 == 0:
             return self.mma_rows(x)
         return x @ self.dense().reshape(self.N, self.K).T
 

@@ -148,7 +148,7 @@ int bn_f1_to_r4(const uint8_t *meta, const uint32_t *idx, uint64_t nwords, const
                 uint8_t *esc_tmp, uint64_t esc_cap, uint32_t *tmp_off, uint32_t *counters,
                 void *stream);
 
-/* Fused R4-decode GEMM on the tensor cores for 1 <= M <= 128 input rows (meant for 16 and more):
+/* Fused R4-decode GEMM on the tensor cores for 1 <= M <= 256 input rows (meant for 5 and more):
  * Y [M,N] = X [M,K] . W^T with the weights decoded to BF16 inside the kernel (tcgen05 MMA, fp32
  * accumulators in tensor memory); the weights are read once whatever M. K % 8 == 0, rows of X
  * 16-byte aligned. The sum over K is formed by the tensor core in its own order: outputs agree

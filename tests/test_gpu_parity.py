@@ -422,7 +422,7 @@ def test_small_m_rows(M):
     assert np.array_equal(words(got)[0], o.c_dense_rows(xw, u))
 
 
-@pytest.mark.parametrize("M,N,K", [(16, 128, 128), (16, 256, 512), (32, 200, 3840), (128, 384, 1024), (24, 130, 264), (100, 96, 2048), (1, 64, 128)])
+@pytest.mark.parametrize("M,N,K", [(16, 128, 128), (16, 256, 512), (32, 200, 3840), (128, 384, 1024), (24, 130, 264), (100, 96, 2048), (1, 64, 128), (256, 300, 768), (200, 1000, 1280), (300, 128, 256)])
 def test_mma_rows_against_fp32(M, N, K):
     """Tensor-core decode GEMM: the weights it multiplies by are exactly the decoded BF16 weights
     (checked with one-hot inputs, where every output is a single weight), and on random inputs
@@ -453,7 +453,7 @@ def test_mma_rows_against_fp32(M, N, K):
 def test_many_rows_rebuild_path():
     from binade_b200.cuda import r4
 
-    N, K, M = 256, 512, 200  # more rows than the fused kernels take
+    N, K, M = 256, 512, 600  # more rows than the fused kernels take
     rng = np.random.default_rng(5)
     u = weights(rng, (N, K), escapes=False)
     u.reshape(-1)[5::199] = 0x5F80  # 2^64: a rare exponent (escape) that keeps every sum finite
