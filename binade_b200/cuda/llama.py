@@ -134,30 +134,31 @@ class Decoder(nn.Module):
         dist.all_gather_into_tensor(out, y.reshape(1, -1).contiguous(), group=self.group)
         return out.reshape(1, n_total)
 
-    def _rope(self, t: torch.Tensor, pos: torch.Tensor) -> torch.Tensor:
-        """t [heads, d] at position pos (device tensor [1])."""
-        cos, sin = self.cos.index_select(0, pos), self.sin.index_select(0, pos)  # [1, d/2]
+    @staticmethod
+    def _rope(t: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
+        """t [heads, d] rotated by the position's cos / sin [1, d/2] (fp32 arithmetic)."""
         tf = t.float()
         a, b = tf[:, : t.shape[1] // 2], tf[:, t.shape[1] // 2 :]
         return torch.cat([a * cos - b * sin, a * sin + b * cos], dim=1).to(t.dtype)
 
     def step(self, token: torch.Tensor, pos: torch.Tensor) -> torch.Tensor:
-        """One decode step: token, pos are device int64 tensors of one element -> logits [1, vocab]."""
+        """One decode step: token, pos are device int64 tensors of one element -> logits [1, vocab].
+        The glue between the linear layers is kept to few kernels (it is launch-bound at batch 1):
+        the position's rotation is looked up once per step, q and k rotate together, attention is
+        one fused scaled-dot-product call over the static cache with a position mask."""
         s, d = self.shape, self.shape.head_dim
         x = self.embed(token) if isinstance(self.embed, r4.R4Embedding) else self.embed.index_select(0, token)  # [1, hidden]
-        mask = (self.positions <= pos)[None, None, :]  # [1, 1, max_seq]
+        mask = (self.positions <= pos)[None, None, None, :]  # [1, 1, 1, max_seq]
+        cos, sin = self.cos.index_select(0, pos), self.sin.index_select(0, pos)  # [1, d/2]
+        nqk = self.hq + self.hkv
         for l in range(s.layers):
             h = torch.nn.functional.rms_norm(x, (s.hidden,), self.norm1[l], s.eps)
             qkv = self.qkv[l](h)[0]
-            q = self._rope(qkv[: self.hq * d].view(self.hq, d), pos)
-            k = self._rope(qkv[self.hq * d : (self.hq + self.hkv) * d].view(self.hkv, d), pos)
-            v = qkv[(self.hq + self.hkv) * d :].view(self.hkv, d)
-            self.k_cache[l].index_copy_(1, pos, k[:, None, :])
+            qk = self._rope(qkv[: nqk * d].view(nqk, d), cos, sin)
+            v = qkv[nqk * d :].view(self.hkv, d)
+            self.k_cache[l].index_copy_(1, pos, qk[self.hq :, None, :])
             self.v_cache[l].index_copy_(1, pos, v[:, None, :])
-            qg = q.view(self.hkv, self.hq // self.hkv, d)
-            scores = torch.bmm(qg, self.k_cache[l].transpose(1, 2)).float() / math.sqrt(d)  # [hkv, group, max_seq]
-            scores = scores.masked_fill(~mask, float("-inf"))
-            attn = torch.bmm(torch.softmax(scores, dim=-1).to(torch.bfloat16), self.v_cache[l])  # [hkv, group, d]
+            attn = torch.nn.functional.scaled_dot_product_attention(qk[None, : self.hq, None, :], self.k_cache[l][None], self.v_cache[l][None], attn_mask=mask, enable_gqa=True)  # [1, hq, 1, d]
             x = x + self.o[l](self._gather(attn.reshape(1, self.hq * d), s.heads * d))
             h = torch.nn.functional.rms_norm(x, (s.hidden,), self.norm2[l], s.eps)
             gu = self.gate_up[l](h)[0]
