@@ -1,20 +1,23 @@
 // All-gather of small output slices over NVLink peer memory, as one kernel per rank: every rank
 // stores its slice straight into every peer's buffer (plain peer stores, no TMA, no multicast),
-// raises a flag there, and waits for the peers' flags. For the few KB a row-sharded matvec
-// produces, the cost is two flag round trips instead of a library collective's launch latency.
+// raises a flag there, waits for the peers' flags and copies the gathered slices into a local
+// output buffer. For the few KB a row-sharded matvec produces, the cost is one flag round trip
+// instead of a library collective's launch latency.
 //
 // Each rank owns one symmetric buffer (the same layout on every rank, mapped on all of them):
-//   [0, 32)    enter[src]  u32: rank src has entered exchange number enter[src]
-//   [32, 64)   done[src]   u32: rank src's slice of exchange number done[src] has landed here
-//   [256, ...) data: for each of up to 4 segments, world slices of that segment's size, slice r
-//              written by rank r (a segment is one projection's output: its slices end up side
-//              by side in rank order = row order, ready to use, with no copy afterwards)
+//   [0, 32)    done[src]  u32: rank src's slices of exchange number done[src] have landed here
+//   [256, ...) two data areas (exchange q uses area q & 1), each: for each of up to 4 segments,
+//              world slices of that segment's size, slice r written by rank r (a segment is one
+//              projection's output: its slices end up side by side in rank order = row order)
 // Protocol of exchange number q (a per-rank counter in device memory, so a captured graph can
-// replay the launch): (1) tell every peer "I am in q" and wait until every peer is: its readers
-// of exchange q - 1 ran before this kernel in stream order, so the single data area may be
-// overwritten; (2) store the slice into every peer's data area, fence, tell every peer "done q",
-// wait for every peer's done q. Every wait is bounded: on giving up the kernel sets a status flag
-// and returns (the output is then invalid, the context stays usable).
+// replay the launch): store the slices into area q & 1 of every peer, fence, tell every peer
+// "done q", wait for every peer's done q, copy area q & 1 of the own buffer to the local output.
+// Two areas make the stores safe without a handshake: a rank that writes area q & 1 for exchange
+// q + 2 has seen every peer's done q + 1, which a peer raises only after its own exchange q (copy
+// to the output included) has finished in its stream. Readers use the local output buffer, which
+// only this rank's next exchange overwrites, after them in stream order. Every wait is bounded:
+// on giving up the kernel sets a status flag and returns (the output is then invalid, the context
+// stays usable).
 #include "common.cuh"
 
 namespace bn {
@@ -31,7 +34,9 @@ struct PushArgs {
   uint8_t *peer[XCH_MAX_RANKS];  // every rank's symmetric buffer, as mapped on this GPU
   const uint8_t *local[XCH_MAX_SEGMENTS];
   uint64_t bytes[XCH_MAX_SEGMENTS];  // this rank's slice of each segment
-  uint64_t base[XCH_MAX_SEGMENTS];   // where the segment's world slices start in the data area
+  uint64_t base[XCH_MAX_SEGMENTS];   // where the segment's world slices start in a data area
+  uint64_t area;                     // bytes of one data area
+  uint8_t *out;                      // local output: one data area
   uint32_t *counter;
   int rank, world, segments;
 };
@@ -60,16 +65,10 @@ __global__ void __launch_bounds__(1024, 1) push_gather_kernel(PushArgs a) {
   }
   __syncthreads();
   const uint32_t seq = s_seq;
-  uint32_t *const mine = reinterpret_cast<uint32_t *>(a.peer[a.rank]);
-  if ((int)threadIdx.x < a.world) {
-    st_release_sys(reinterpret_cast<uint32_t *>(a.peer[threadIdx.x]) + a.rank, seq);  // enter[rank] on peer
-    if (!wait_reached(mine + threadIdx.x, seq)) s_ok = 0;
-  }
-  __syncthreads();
-  if (!s_ok) return;
+  const uint64_t area_at = XCH_DATA_OFFSET + (uint64_t)(seq & 1u) * a.area;
   // the slices into every peer's data area (own buffer included), 16 bytes per store
   for (int g = 0; g < a.segments; g++) {
-    const uint64_t n16 = a.bytes[g] / 16, at = XCH_DATA_OFFSET + a.base[g] + (uint64_t)a.rank * a.bytes[g];
+    const uint64_t n16 = a.bytes[g] / 16, at = area_at + a.base[g] + (uint64_t)a.rank * a.bytes[g];
     const uint4 *src = reinterpret_cast<const uint4 *>(a.local[g]);
     for (uint64_t i = threadIdx.x; i < n16; i += blockDim.x) {
       const uint4 v = src[i];
@@ -81,11 +80,18 @@ __global__ void __launch_bounds__(1024, 1) push_gather_kernel(PushArgs a) {
   }
   __threadfence_system();
   __syncthreads();
+  uint32_t *const mine = reinterpret_cast<uint32_t *>(a.peer[a.rank]);
   if ((int)threadIdx.x < a.world) {
-    st_release_sys(reinterpret_cast<uint32_t *>(a.peer[threadIdx.x]) + 8 + a.rank, seq);  // done[rank] on peer
-    wait_reached(mine + 8 + threadIdx.x, seq);
+    st_release_sys(reinterpret_cast<uint32_t *>(a.peer[threadIdx.x]) + a.rank, seq);  // done[rank] on peer
+    if (!wait_reached(mine + threadIdx.x, seq)) s_ok = 0;
   }
   __syncthreads();
+  if (!s_ok) return;
+  // the gathered slices to the local output (readers never touch the symmetric buffer)
+  const uint4 *from = reinterpret_cast<const uint4 *>(a.peer[a.rank] + area_at);
+  uint4 *to = reinterpret_cast<uint4 *>(a.out);
+  const uint64_t total16 = (a.base[a.segments - 1] + (uint64_t)a.world * a.bytes[a.segments - 1]) / 16;
+  for (uint64_t i = threadIdx.x; i < total16; i += blockDim.x) to[i] = __ldcv(from + i);  // peers wrote it: no stale cache line
 }
 
 int exchange_status(int *status) {
@@ -95,8 +101,8 @@ int exchange_status(int *status) {
 
 }  // namespace bn
 
-extern "C" int bn_push_gather(const void *const *locals, const uint64_t *bytes, int segments, const uint64_t *peers, int rank, int world, uint32_t *counter, void *stream) {
-  if (!locals || !bytes || !peers || !counter || world < 1 || world > bn::XCH_MAX_RANKS || rank < 0 || rank >= world || segments < 1 || segments > bn::XCH_MAX_SEGMENTS)
+extern "C" int bn_push_gather(const void *const *locals, const uint64_t *bytes, int segments, const uint64_t *peers, uint64_t area_bytes, void *out, int rank, int world, uint32_t *counter, void *stream) {
+  if (!locals || !bytes || !peers || !out || !counter || world < 1 || world > bn::XCH_MAX_RANKS || rank < 0 || rank >= world || segments < 1 || segments > bn::XCH_MAX_SEGMENTS)
     return bn::fail(BN_ERR_ARG, "bn_push_gather: bad rank, world (1..8), segment count (1..4) or null pointer");
   bn::PushArgs a{};
   uint64_t base = 0;
@@ -105,11 +111,12 @@ extern "C" int bn_push_gather(const void *const *locals, const uint64_t *bytes, 
     a.local[g] = static_cast<const uint8_t *>(locals[g]), a.bytes[g] = bytes[g], a.base[g] = base;
     base += (uint64_t)world * bytes[g];
   }
+  if (base > area_bytes || area_bytes % 16 || (uintptr_t)out % 16) return bn::fail(BN_ERR_ARG, "bn_push_gather: the slices exceed a data area, or the area / output is not 16-byte aligned");
   for (int r = 0; r < world; r++) {
     if (!peers[r]) return bn::fail(BN_ERR_ARG, "bn_push_gather: null peer buffer");
     a.peer[r] = reinterpret_cast<uint8_t *>(peers[r]);
   }
-  a.counter = counter, a.rank = rank, a.world = world, a.segments = segments;
+  a.area = area_bytes, a.out = static_cast<uint8_t *>(out), a.counter = counter, a.rank = rank, a.world = world, a.segments = segments;
   bn::push_gather_kernel<<<1, 1024, 0, (cudaStream_t)stream>>>(a);
   return bn::launched("push_gather_kernel");
 }

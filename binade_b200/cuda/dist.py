@@ -91,9 +91,9 @@ class PushGather:
         ex = PushGather(group, max_bytes)   # collective: every rank of the group
         out = ex(flat)                      # flat [M, W] on this rank -> [world, M, W]
 
-    Results are views of this rank's buffer: they are overwritten by the next call on the same
-    object, which every rank enters only after its own readers of the previous result (stream
-    order), so a result must be consumed (or copied) before the object is used again. Safe to capture in a
+    Results are views of this object's output buffer: the next call on the same object overwrites
+    them (after this rank's readers, in stream order), so a result must be consumed or copied
+    before the object is used again. Safe to capture in a
     CUDA graph (the call number lives in device memory)."""
 
     HEADER = 256
@@ -109,8 +109,10 @@ class PushGather:
         if self.world > 8:
             raise ValueError("PushGather serves at most 8 ranks")
         self.cap = (max_bytes + 15) // 16 * 16
+        self.area = self.world * self.cap  # one data area: every rank's slices
         dev = torch.device("cuda", torch.cuda.current_device())
-        self.buf = symm_mem.empty(self.HEADER + self.world * self.cap, dtype=torch.uint8, device=dev)
+        self.out = torch.empty(self.area, dtype=torch.uint8, device=dev)  # where the kernel leaves the gathered slices
+        self.buf = symm_mem.empty(self.HEADER + 2 * self.area, dtype=torch.uint8, device=dev)
         self.buf.zero_()
         self.handle = symm_mem.rendezvous(self.buf, group)
         self.peers = (ctypes.c_uint64 * self.world)(*[int(p) for p in self.handle.buffer_ptrs])
@@ -126,15 +128,15 @@ class PushGather:
         from .kernels import _call, _p
 
         sizes = [t.numel() * t.element_size() for t in pieces]
-        if self.world * sum(sizes) > self.world * self.cap:
+        if sum(sizes) > self.cap:
             raise ValueError(f"slices of {sum(sizes)} bytes exceed the exchange's {self.cap}")
         n = len(pieces)
         ptrs = (ctypes.c_void_p * n)(*[t.data_ptr() for t in pieces])
         lens = (ctypes.c_uint64 * n)(*sizes)
-        _call("bn_push_gather", ctypes.cast(ptrs, ctypes.c_void_p), ctypes.cast(lens, ctypes.c_void_p), n, ctypes.cast(self.peers, ctypes.c_void_p), self.rank, self.world, _p(self.counter))
-        out, at = [], self.HEADER
+        _call("bn_push_gather", ctypes.cast(ptrs, ctypes.c_void_p), ctypes.cast(lens, ctypes.c_void_p), n, ctypes.cast(self.peers, ctypes.c_void_p), self.area, _p(self.out), self.rank, self.world, _p(self.counter))
+        out, at = [], 0
         for sz in sizes:
-            out.append(self.buf[at : at + self.world * sz].view(self.world, sz))
+            out.append(self.out[at : at + self.world * sz].view(self.world, sz))
             at += self.world * sz
         return out
 

@@ -207,15 +207,17 @@ int bn_r4_gather_grouped(const uint16_t *x, const bn_r4 *w, const uint32_t *xi, 
  * hook; the reference is single-device, so there is no counterpart). Every rank calls it with
  * 1..4 segments (one per projection): `locals[g]` is this rank's slice of segment g, `bytes[g]`
  * long (a multiple of 16, 16-byte aligned; host arrays of `segments` entries). `peers[r]` is
- * the address, on this GPU, of rank r's symmetric buffer (at least 256 + world * sum(bytes)
- * bytes, zeroed before the first call, mapped on every rank, e.g. by CUDA IPC or a symmetric-
- * memory allocator); `counter` is a zeroed uint32 in this rank's device memory that belongs to
- * this set of buffers. After the call, in stream order, segment g of this rank's own buffer
- * starts at byte 256 + world * (bytes[0] + .. + bytes[g-1]) and holds the world slices of that
- * segment in rank order. Ranks must make the same sequence of calls; world <= 8. Plain peer
- * stores and flags only (no TMA, no multicast); every wait is bounded. */
+ * the address, on this GPU, of rank r's symmetric buffer (256 + 2 * area_bytes bytes, zeroed
+ * before the first call, mapped on every rank, e.g. by CUDA IPC or a symmetric-memory
+ * allocator; area_bytes >= world * sum(bytes), a multiple of 16); `out` is area_bytes of this
+ * rank's own device memory; `counter` is a zeroed uint32 in this rank's device memory that
+ * belongs to this set of buffers. After the call, in stream order, segment g starts at byte
+ * world * (bytes[0] + .. + bytes[g-1]) of `out` and holds the world slices of that segment in
+ * rank order. Ranks must make the same sequence of calls; world <= 8. Plain peer stores and
+ * flags only (no TMA, no multicast); every wait is bounded. */
 int bn_push_gather(const void *const *locals, const uint64_t *bytes, int segments,
-                   const uint64_t *peers, int rank, int world, uint32_t *counter, void *stream);
+                   const uint64_t *peers, uint64_t area_bytes, void *out, int rank, int world,
+                   uint32_t *counter, void *stream);
 
 /* Device-side status of the calling thread's current device: 0, or non-zero once a kernel of
  * this library gave up a bounded wait (its output is then incomplete): bits 0..7 the streaming
