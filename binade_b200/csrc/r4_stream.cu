@@ -292,8 +292,16 @@ __global__ void __launch_bounds__(WARPS * 32, 1) r4_stream_kernel(StreamArgs a) 
   const uint32_t s_bar = bar_at + warp * (uint32_t)S * 8u;
 
   // this warp's rows: nfull groups of RW rows, then the remaining rows one per group
-  const int64_t workers = (int64_t)gridDim.x * WARPS, me = (int64_t)blockIdx.x * WARPS + warp;
-  const int64_t o_begin = a.N * me / workers, o_end = a.N * (me + 1) / workers;  // output rows of this warp
+  // output rows of this warp: an even split of N over all warps of the grid (32-bit arithmetic
+  // when it fits: a 64-bit division is a few hundred dependent instructions at kernel start)
+  const uint32_t workers = gridDim.x * WARPS, me = blockIdx.x * WARPS + warp;
+  int64_t o_begin, o_end;
+  if ((uint64_t)a.N * workers < (1ull << 32)) {
+    const uint32_t n32 = (uint32_t)a.N;
+    o_begin = n32 * me / workers, o_end = n32 * (me + 1u) / workers;
+  } else {
+    o_begin = a.N * (int64_t)me / workers, o_end = a.N * (int64_t)(me + 1u) / workers;
+  }
   const int64_t slot = blockIdx.y;
   // grouped gather: this block's expert, its first slot in `order` and how many slots it takes
   int64_t g_first = 0;
