@@ -36,6 +36,14 @@ int stream_gather(const bn_r4 *w, const uint16_t *x, const uint32_t *xi, const u
 
 int stream_gather_grouped(const bn_r4 *w, const uint16_t *x, const uint32_t *xi, const uint32_t *seg, const uint32_t *order, int64_t E, int64_t G, int64_t max_per_expert, int64_t n, int64_t K, int64_t RS, int64_t R0, int64_t split, uint16_t *y, uint16_t *y2, cudaStream_t s);
 
+// Batch-1 matvec with eight (or sixteen, or thirty-two) threads per row, up to four matrices that
+// share x in one launch, and the expert gather through the same kernel (r4_oct.cu); -1 when the
+// shape is outside its coverage.
+int oct_matvec(const bn_r4 *w, const uint16_t *x, int64_t N, int64_t K, uint16_t *y, cudaStream_t s);
+int oct_matvec_multi(const bn_r4 *const *w, const int64_t *N, uint16_t *const *y, int nmat, const uint16_t *x, int64_t K, cudaStream_t s);
+int oct_gather(const bn_r4 *w, const uint16_t *x, const uint32_t *xi, const uint32_t *ei, int64_t G, int64_t n, int64_t K, int64_t RS, int64_t R0, int64_t split, uint16_t *y, uint16_t *y2, cudaStream_t s);
+int oct_status(int *status);
+
 // Register-pipelined batch-1 matvec and expert gather (r4_direct.cu); -1 outside their coverage.
 int direct_matvec(const bn_r4 *w, const uint16_t *x, int64_t N, int64_t K, uint16_t *y, cudaStream_t s);
 int direct_gather(const bn_r4 *w, const uint16_t *x, const uint32_t *xi, const uint32_t *ei, int64_t G, int64_t n, int64_t K, int64_t RS, int64_t R0, int64_t split, uint16_t *y, uint16_t *y2, cudaStream_t s);

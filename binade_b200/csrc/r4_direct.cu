@@ -314,14 +314,14 @@ int direct_any(DirectArgs a, cudaStream_t s, int64_t slots) {
 // Returns -1 when the shape is outside what this kernel covers (K % 4 != 0, or x too long for
 // the shared window below the table: K > 31744).
 int direct_matvec(const bn_r4 *w, const uint16_t *x, int64_t N, int64_t K, uint16_t *y, cudaStream_t s) {
-  if (K % 4 || N < 1) return -1;
+  if (K % 4 || N < 1 || (reinterpret_cast<uintptr_t>(x) & 3) || (reinterpret_cast<uintptr_t>(w->raw) & 3)) return -1;  // 32-bit loads of x and of the raw bytes
   DirectArgs a{};
   a.w = *w, a.x = x, a.y = y, a.N = N, a.K = K, a.T = (int)tiles(K);
   return direct_any(a, s, 1);
 }
 
 int direct_gather(const bn_r4 *w, const uint16_t *x, const uint32_t *xi, const uint32_t *ei, int64_t G, int64_t n, int64_t K, int64_t RS, int64_t R0, int64_t split, uint16_t *y, uint16_t *y2, cudaStream_t s) {
-  if (K % 4 || n < 1 || G < 1 || G > 65535) return -1;
+  if (K % 4 || n < 1 || G < 1 || G > 65535 || (reinterpret_cast<uintptr_t>(x) & 3) || (reinterpret_cast<uintptr_t>(w->raw) & 3)) return -1;
   DirectArgs a{};
   a.w = *w, a.x = x, a.y = y, a.y2 = y2, a.N = n, a.K = K, a.T = (int)tiles(K);
   a.xi = xi, a.ei = ei, a.RS = RS, a.R0 = R0, a.split = split;

@@ -310,10 +310,10 @@ extern "C" int bn_r4_rows(const uint16_t *x, int64_t x_stride, const bn_r4 *w, i
   // the instantiation is the next power of two >= M: absent input rows are zeros in shared
   // memory and are never stored, so the weights stream once whatever M
   if (M == 1) {
-    // long rows: the register-pipelined kernel (its x and table leave no room for deep rings
-    // anyway); otherwise the streaming kernel, which needs K % 16 == 0; then whichever is left
-    static const bool stream_long = getenv("BINADE_B200_STREAM_LONG") != nullptr;  // experiments: long rows through the streaming kernel too
-    int e = (K >= 8192 && !stream_long) ? direct_matvec(w, x, N, K, y, s) : -1;
+    // the cp.async kernel (K % 16 == 0, 640 <= K <= 16384, aligned arrays); else, for long rows,
+    // the register-pipelined kernel; else the bulk-copy kernel (K % 16 == 0); then whichever is left
+    int e = oct_matvec(w, x, N, K, y, s);
+    if (e == -1 && K >= 8192) e = direct_matvec(w, x, N, K, y, s);
     if (e == -1) e = stream_matvec(w, x, N, K, y, s);
     if (e == -1) e = direct_matvec(w, x, N, K, y, s);
     if (e >= 0) return e;
@@ -329,6 +329,28 @@ extern "C" int bn_r4_rows(const uint16_t *x, int64_t x_stride, const bn_r4 *w, i
   return launch_rows<16, 2, false>(a, 1, s);
 }
 
+extern "C" int bn_r4_rows_multi(const uint16_t *x, const bn_r4 *const *w, const int64_t *N, int count, int64_t K, uint16_t *const *y, void *stream) {
+  if (!x || !w || !N || !y || count < 1 || count > 4 || K <= 0) return fail(BN_ERR_ARG, "bn_r4_rows_multi: 1..4 matrices, no null pointer");
+  if (K % 4) return fail(BN_ERR_ARG, "R4 needs K % 4 == 0");
+  for (int i = 0; i < count; i++) {
+    if (int e = check_r4(w[i])) return e;
+    if (!y[i] || N[i] < 0) return fail(BN_ERR_ARG, "bn_r4_rows_multi: bad size or null output");
+  }
+  // matrices with rows, in one launch when the shape allows it
+  const bn_r4 *ws[4];
+  int64_t Ns[4];
+  uint16_t *ys[4];
+  int n = 0;
+  for (int i = 0; i < count; i++)
+    if (N[i] > 0) ws[n] = w[i], Ns[n] = N[i], ys[n] = y[i], n++;
+  if (n == 0) return BN_OK;
+  const int e = oct_matvec_multi(ws, Ns, ys, n, x, K, (cudaStream_t)stream);
+  if (e >= 0) return e;
+  for (int i = 0; i < n; i++)
+    if (int e1 = bn_r4_rows(x, K, ws[i], 1, Ns[i], K, ys[i], Ns[i], stream)) return e1;
+  return BN_OK;
+}
+
 extern "C" int bn_r4_gather(const uint16_t *x, const bn_r4 *w, const uint32_t *xi, const uint32_t *ei, int64_t G, int64_t n, int64_t K, int64_t RS, int64_t R0, int64_t split, uint16_t *y, uint16_t *y2, void *stream) {
   if (int e = check_r4(w)) return e;
   if (!x || !xi || !ei || !y || G < 0 || n < 0 || K <= 0 || split < 0 || split >= (n > 0 ? n : 1)) return fail(BN_ERR_ARG, "bn_r4_gather: bad size or null pointer");
@@ -337,7 +359,8 @@ extern "C" int bn_r4_gather(const uint16_t *x, const bn_r4 *w, const uint32_t *x
   if (G == 0 || n == 0) return BN_OK;
   if (G > 65535) return fail(BN_ERR_ARG, "bn_r4_gather: more than 65535 slots");
   {
-    int e = stream_gather(w, x, xi, ei, G, n, K, RS, R0, split, y, y2, (cudaStream_t)stream);
+    int e = oct_gather(w, x, xi, ei, G, n, K, RS, R0, split, y, y2, (cudaStream_t)stream);
+    if (e == -1) e = stream_gather(w, x, xi, ei, G, n, K, RS, R0, split, y, y2, (cudaStream_t)stream);
     if (e == -1) e = direct_gather(w, x, xi, ei, G, n, K, RS, R0, split, y, y2, (cudaStream_t)stream);
     if (e >= 0) return e;
   }

@@ -1,0 +1,633 @@
+// Batch-1 fused R4 matvec, eight threads per weight row.
+//
+// The documented summation order has 32 virtual lanes per output row (lane l owns weights
+// 128t + 4l + j of every tile t). Here one thread plays four consecutive virtual lanes, so eight
+// threads cover a row and a warp walks four rows side by side:
+//
+//   thread p of a row's eight   virtual lanes 4p .. 4p+3: 16 consecutive weights of every tile,
+//                               i.e. 16 bytes of raw bytes and 8 bytes of code words per tile,
+//                               four fp32 accumulators
+//   loads                       every thread copies its own bytes into a private ring in shared
+//                               memory with cp.async, NQ quads (of four tiles) ahead of the quad
+//                               being decoded; groups complete in order, so "all but the newest
+//                               NQ - 1" is one wait instruction and costs no registers. The ring
+//                               runs on across the warp's rows, so it never drains between rows
+//   x                           BF16 in shared memory, multiplied with fma.rn.f32.bf16
+//   table                       256-entry pair table (code byte -> two exponents placed in a
+//                               BF16x2 word), one column per lane, on a 64 KB boundary of the
+//                               shared window so that a lookup address is one byte permute; x
+//                               lives in the unused halves of its entries
+//   escapes                     a warp takes the patch path for a tile when any of its four rows
+//                               flags it; escape bytes come from a 32-byte window of the row's
+//                               escapes held in registers (one word per thread)
+//   end of a row                virtual lanes combine with strides 16, 8, 4 by three shuffles
+//                               per accumulator, strides 2 and 1 inside the thread
+//
+// A thread reads back only what it copied itself: no barrier after start-up, no flag, no wait on
+// another thread. One launch takes up to four matrices that share x (q/k/v, gate/up), or the
+// slots of an expert gather. Needs K % 16 == 0, 640 <= K <= 16384 and 16-byte aligned raw /
+// codes / x.
+#include "common.cuh"
+
+namespace bn {
+namespace {
+
+constexpr uint32_t OC_BASE_MAX = 2048;    // the dynamic shared window starts below this address
+constexpr uint32_t OC_LUT = 65536;        // absolute shared address of the pair table
+constexpr uint32_t OC_TOP = 131072;       // the table (and x) end here; rings sit below the table and above this
+constexpr uint32_t OC_SMEM_MAX = 227 * 1024 - 256;  // dynamic shared memory a block may ask for (the kernel also has 64 static bytes)
+
+// Copies of this thread's bytes of one tile into its slot (R rows per warp: 4R raw bytes and 2R
+// code bytes per thread; with R = 1 the even lanes copy the code words of two lanes, cp.async
+// moving no less than four bytes). `after`: a value computed from the slot's previous contents,
+// so that the copy cannot be issued before those have been read.
+template <int R, int U>
+__device__ __forceinline__ void copy_tile(uint32_t at, uint32_t to_codes, const uint8_t *raw, const uint8_t *codes, bool code_lane, float after) {
+  constexpr int SLOT = 192 * R;
+  if constexpr (R == 4) {
+    asm volatile("cp.async.cg.shared.global [%0+%1], [%2+%3], 16;  // after %4" ::"r"(at), "n"(U * SLOT), "l"(raw), "n"(U * 128), "f"(after) : "memory");
+    asm volatile("cp.async.ca.shared.global [%0+%1], [%2+%3], 8;" ::"r"(at + to_codes), "n"(U * SLOT), "l"(codes), "n"(U * 64) : "memory");
+  } else if constexpr (R == 2) {
+    asm volatile("cp.async.ca.shared.global [%0+%1], [%2+%3], 8;  // after %4" ::"r"(at), "n"(U * SLOT), "l"(raw), "n"(U * 128), "f"(after) : "memory");
+    asm volatile("cp.async.ca.shared.global [%0+%1], [%2+%3], 4;" ::"r"(at + to_codes), "n"(U * SLOT), "l"(codes), "n"(U * 64) : "memory");
+  } else {
+    asm volatile("cp.async.ca.shared.global [%0+%1], [%2+%3], 4;  // after %4" ::"r"(at), "n"(U * SLOT), "l"(raw), "n"(U * 128), "f"(after) : "memory");
+    if (code_lane) asm volatile("cp.async.ca.shared.global [%0+%1], [%2+%3], 4;" ::"r"(at + to_codes), "n"(U * SLOT), "l"(codes), "n"(U * 64) : "memory");
+  }
+}
+__device__ __forceinline__ void cp_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+// Waits until all but the newest N cp.async groups of this thread have landed. The value returned
+// is an input of every read of the ring that follows, so none of them can move above the wait.
+template <int N>
+__device__ __forceinline__ uint32_t cp_wait() {
+  uint32_t token;
+  asm volatile("cp.async.wait_group %1;\n\tmov.u32 %0, 0;" : "=r"(token) : "n"(N) : "memory");
+  return token;
+}
+// This thread's raw bytes (rr: one word per lane word) and code words (cc: two lane words per
+// register) of the tile in slot U of the quad at `at`.
+template <int R, int U>
+__device__ __forceinline__ void ring_read(uint32_t at, uint32_t to_codes, uint32_t token, uint32_t (&rr)[R], uint32_t (&cc)[(R + 1) / 2]) {
+  constexpr int SLOT = 192 * R;
+  if constexpr (R == 4) {
+    asm("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4+%5];" : "=r"(rr[0]), "=r"(rr[1]), "=r"(rr[2]), "=r"(rr[3]) : "r"(at), "n"(U * SLOT), "r"(token));
+    asm("ld.shared.v2.u32 {%0, %1}, [%2+%3];" : "=r"(cc[0]), "=r"(cc[1]) : "r"(at + to_codes), "n"(U * SLOT), "r"(token));
+  } else if constexpr (R == 2) {
+    asm("ld.shared.v2.u32 {%0, %1}, [%2+%3];" : "=r"(rr[0]), "=r"(rr[1]) : "r"(at), "n"(U * SLOT), "r"(token));
+    asm("ld.shared.u32 %0, [%1+%2];" : "=r"(cc[0]) : "r"(at + to_codes), "n"(U * SLOT), "r"(token));
+  } else {
+    uint16_t c;
+    asm("ld.shared.u32 %0, [%1+%2];" : "=r"(rr[0]) : "r"(at), "n"(U * SLOT), "r"(token));
+    asm("ld.shared.u16 %0, [%1+%2];" : "=h"(c) : "r"(at + to_codes), "n"(U * SLOT), "r"(token));
+    cc[0] = c;
+  }
+}
+// x and the table never change after the block-wide barrier that publishes them; `ready` is a
+// value produced after that barrier, so no read can move above it.
+__device__ __forceinline__ uint32_t lut_read(uint32_t addr, uint32_t ready) {
+  uint32_t v;
+  asm("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr), "r"(ready));
+  return v;
+}
+// This thread's 4R values of x for tile U past xs: two BF16x2 words per lane word.
+template <int R, int U>
+__device__ __forceinline__ void x_read(uint32_t xs, uint32_t ready, uint32_t (&xx)[2 * R]) {
+  if constexpr (R == 4) {
+    asm("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4+%5];" : "=r"(xx[0]), "=r"(xx[1]), "=r"(xx[2]), "=r"(xx[3]) : "r"(xs), "n"(U * 512), "r"(ready));
+    asm("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4+%5];" : "=r"(xx[4]), "=r"(xx[5]), "=r"(xx[6]), "=r"(xx[7]) : "r"(xs), "n"(U * 512 + 256), "r"(ready));
+  } else if constexpr (R == 2) {
+    asm("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4+%5];" : "=r"(xx[0]), "=r"(xx[1]), "=r"(xx[2]), "=r"(xx[3]) : "r"(xs), "n"(U * 512), "r"(ready));
+  } else {
+    asm("ld.shared.v2.u32 {%0, %1}, [%2+%3];" : "=r"(xx[0]), "=r"(xx[1]) : "r"(xs), "n"(U * 512), "r"(ready));
+  }
+}
+// acc += w.lo * x.lo; acc += w.hi * x.hi with BF16 factors widened exactly (two fused ops).
+__device__ __forceinline__ float fma2_bf16(uint32_t w, uint32_t x, float acc) {
+  asm("{\n\t.reg .b16 wl, wh, xl, xh;\n\t"
+      "mov.b32 {wl, wh}, %1;\n\t"
+      "mov.b32 {xl, xh}, %2;\n\t"
+      "fma.rn.f32.bf16 %0, wl, xl, %0;\n\t"
+      "fma.rn.f32.bf16 %0, wh, xh, %0;\n\t}"
+      : "+f"(acc)
+      : "r"(w), "r"(x));
+  return acc;
+}
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+constexpr int OC_MAT = 4;  // matrices that can share one launch (and one x)
+
+struct OctArgs {
+  bn_r4 w[OC_MAT];
+  uint16_t *y[OC_MAT];
+  int64_t N[OC_MAT];        // rows of each matrix (of one expert, for a gather)
+  uint32_t gend[OC_MAT];    // row groups (4 rows) up to and including matrix i
+  int nmat;
+  const uint16_t *x;
+  int64_t K;
+  int T;
+  // expert gather (blockIdx.y = slot, one matrix): rows ei[slot] * RS + R0 .. + N[0], input row
+  // xi[slot]; outputs y [G, N], or with 0 < split < N: y [G, split] and y2 [G, N - split]
+  const uint32_t *xi, *ei;
+  int64_t RS, R0, split;
+  uint16_t *y2;
+  uint32_t smem;  // dynamic shared memory of the launch, bytes
+};
+
+__device__ int g_oct_error;  // set when the shared window does not match the launch; read by bn_device_status()
+
+// bit 4j of the result: nibble j of c is 15
+__device__ __forceinline__ uint32_t hits15(uint32_t c) {
+  const uint32_t t = c & (c >> 1);
+  return t & (t >> 2) & 0x11111111u;
+}
+
+// Escape bytes of a row's window: word p of the row's threads holds bytes base + 4p .. + 3.
+struct EscWindow {
+  uint32_t word, base;
+};
+
+__device__ __forceinline__ uint32_t window_load(const uint8_t *__restrict__ esc, uint64_t cap, uint32_t off) {
+  if ((uint64_t)off + 4 <= cap) return __ldg(reinterpret_cast<const uint32_t *>(esc + off));
+  uint32_t v = 0;  // the array's last, partial word: byte by byte
+#pragma unroll
+  for (int i = 0; i < 4; i++)
+    if ((uint64_t)off + i < cap) v |= (uint32_t)__ldg(esc + off + i) << (8 * i);
+  return v;
+}
+
+// val into pair word k of the four from w[B]
+template <int B, int N>
+__device__ __forceinline__ void or_into(uint32_t k, uint32_t val, uint32_t (&w)[N]) {
+#pragma unroll
+  for (int i = 0; i < 4 && B + i < N; i++) w[B + i] |= k == (uint32_t)i ? val : 0u;
+}
+
+// Geometry of a warp that walks R rows side by side (R = 4, 2 or 1): 32 / R threads per row, a
+// thread plays R consecutive virtual lanes.
+template <int R>
+struct OctGeom {
+  static constexpr int TPR = 32 / R;                  // threads per row
+  static constexpr int NC = (R + 1) / 2;              // code registers per thread and tile (two lane words each)
+  static constexpr uint32_t SLOT = 192 * R;           // a warp's bytes of one tile: 32 x 4R raw, 32 x 2R codes
+  static constexpr uint32_t QUAD = 4 * SLOT;
+  static constexpr uint32_t WINDOW = 4 * TPR;         // escape bytes a row's window holds
+};
+
+// General case of a flagged tile: some thread holds several escapes. Inclusive scan of the counts
+// over the row's threads, then every thread walks its own hits. Whole warp calls it.
+template <int R>
+__device__ __forceinline__ uint32_t escape_general(const uint32_t (&hits)[(R + 1) / 2], uint32_t cnt, uint32_t epos, EscWindow win, const uint8_t *__restrict__ esc, uint32_t lane, uint32_t (&w)[2 * R]) {
+  using Geo = OctGeom<R>;
+  const uint32_t p = lane & (Geo::TPR - 1);
+  uint32_t s = cnt;
+#pragma unroll
+  for (int d = 1; d < Geo::TPR; d <<= 1) {
+    const uint32_t n = __shfl_up_sync(BN_FULL, s, d, Geo::TPR);
+    if (p >= (uint32_t)d) s += n;
+  }
+  const uint32_t tot = __shfl_sync(BN_FULL, s, Geo::TPR - 1, Geo::TPR);
+  uint32_t q = epos + s - cnt;
+#pragma unroll
+  for (int half = 0; half < Geo::NC; half++) {
+    uint32_t h = hits[half];
+    while (__any_sync(BN_FULL, h != 0)) {
+      const uint32_t bit = (uint32_t)__ffs((int)h) - 1u;  // 4j
+      const uint32_t idx = q - win.base;
+      const uint32_t v = __shfl_sync(BN_FULL, win.word, (lane & ~(Geo::TPR - 1)) | ((idx >> 2) & (Geo::TPR - 1)));
+      uint32_t e = __byte_perm(v, 0u, 0x4440u | (idx & 3u));
+      if (h != 0 && idx >= Geo::WINDOW) e = esc[q];  // outside the window (a row dense with escapes)
+      const uint32_t val = e << (7u + ((bit & 4u) << 2));
+      if (h != 0) {
+        if (half) or_into<4>(bit >> 3, val, w);
+        else or_into<0>(bit >> 3, val, w);
+        q++;
+        h &= h - 1u;
+      }
+    }
+  }
+  return tot;
+}
+
+// Where a block's rings sit in the shared window (absolute shared addresses; base = start of the
+// dynamic allocation): warps 0 .. in_a-1 below the table, the others above it.
+struct OctLayout {
+  uint32_t ring_a, in_a, end;
+};
+__host__ __device__ inline OctLayout oct_layout(uint32_t base, uint32_t warps, uint32_t ring) {
+  OctLayout L;
+  L.ring_a = (base + 127u) & ~127u;
+  L.in_a = (OC_LUT - L.ring_a) / ring;
+  if (L.in_a > warps) L.in_a = warps;
+  L.end = OC_TOP + (warps - L.in_a) * ring;
+  return L;
+}
+
+// Per-thread state of the decode side.
+template <int R>
+struct OctRow {
+  float acc[R];
+  uint32_t epos;  // the row's escape cursor
+  EscWindow win;
+};
+
+// What a thread needs to know about itself and its row's matrix while it decodes.
+struct OctSelf {
+  uint32_t lane, to_codes, lut, ready, gmask, ltg;
+  const uint8_t *esc;
+  uint64_t esc_cap;
+};
+
+// One tile of this thread's row: slot U of the quad at `at`, x at xs + U * 512.
+//   flagged  some row of the warp holds a code 15 in this tile (warp-uniform)
+//   live     this thread holds weights in the tile (false only in a row's short last tile)
+template <int R, int U>
+__device__ __forceinline__ void oct_step(OctRow<R> &s, const OctSelf &me, uint32_t at, uint32_t xs, uint32_t token, bool flagged, bool live) {
+  using Geo = OctGeom<R>;
+  uint32_t rr[R], cc[Geo::NC], xx[2 * R], w[2 * R];
+  ring_read<R, U>(at, me.to_codes, token, rr, cc);
+  x_read<R, U>(xs, me.ready, xx);
+#pragma unroll
+  for (int i = 0; i < R; i++) {
+    const uint32_t c = cc[i >> 1];
+    w[2 * i] = (__byte_perm(rr[i], 0u, 0x1100) & 0x807F807Fu) | lut_read(__byte_perm(c, me.lut, (i & 1) ? 0x7624 : 0x7604), me.ready);
+    w[2 * i + 1] = (__byte_perm(rr[i], 0u, 0x3322) & 0x807F807Fu) | lut_read(__byte_perm(c, me.lut, (i & 1) ? 0x7634 : 0x7614), me.ready);
+  }
+#ifdef OC_PROBE_NO_ESC
+  if (false) {
+#else
+  if (flagged) {
+#endif
+    uint32_t hits[Geo::NC], cnt = 0;
+#pragma unroll
+    for (int i = 0; i < Geo::NC; i++) hits[i] = hits15(cc[i]), cnt += __popc(hits[i]);
+    const uint32_t one = __ballot_sync(BN_FULL, cnt == 1u), many = __ballot_sync(BN_FULL, cnt > 1u);
+    if (many == 0) {
+      // at most one escape per thread (nearly always one in the whole warp): its byte is as many
+      // places after the row's cursor as threads of the row before this one hold an escape
+      const uint32_t idx = s.epos + __popc(one & me.ltg) - s.win.base;
+      const uint32_t v = __shfl_sync(BN_FULL, s.win.word, (me.lane & ~(Geo::TPR - 1)) | ((idx >> 2) & (Geo::TPR - 1)));
+      if (cnt) {
+        const uint32_t e = idx < Geo::WINDOW ? __byte_perm(v, 0u, 0x4440u | (idx & 3u)) : (uint32_t)me.esc[s.win.base + idx];
+        const uint32_t upper = Geo::NC > 1 ? hits[Geo::NC - 1] : 0u;
+        const uint32_t bit = (uint32_t)__ffs((int)(hits[0] | upper)) - 1u;  // 4j: weight j of the register's eight
+        const uint32_t val = e << (7u + ((bit & 4u) << 2));
+        if (upper) or_into<4>(bit >> 3, val, w);
+        else or_into<0>(bit >> 3, val, w);
+      }
+      s.epos += __popc(one & me.gmask);
+    } else {
+      s.epos += escape_general<R>(hits, cnt, s.epos, s.win, me.esc, me.lane, w);
+    }
+    if (s.epos - s.win.base >= Geo::WINDOW / 2) {  // slide the window on (the load returns while tiles decode)
+      s.win.base = s.epos & ~3u;
+      s.win.word = window_load(me.esc, me.esc_cap, s.win.base + (me.lane & (Geo::TPR - 1)) * 4u);
+    }
+  }
+  if (live) {  // columns >= K are skipped, not added as zeros
+#pragma unroll
+    for (int i = 0; i < R; i++) s.acc[i] = fma2_bf16(w[2 * i + 1], xx[2 * i + 1], fma2_bf16(w[2 * i], xx[2 * i], s.acc[i]));
+  }
+}
+
+// R: rows a warp walks side by side; NQ: quads of four tiles in flight per thread; MAXW: most
+// warps a block may have (bounds the registers). Both sides of the ring move in quads: a quad
+// holds up to four consecutive tiles of one row (fewer at the row's end), so slot addresses
+// inside a quad are immediates.
+template <int R, int NQ, int MAXW>
+__global__ void __launch_bounds__(MAXW * 32, 1) r4_oct_kernel(const __grid_constant__ OctArgs a) {
+  using Geo = OctGeom<R>;
+  constexpr uint32_t SLOT = Geo::SLOT, QUAD = Geo::QUAD;
+  extern __shared__ __align__(128) uint8_t smem_raw[];
+  __shared__ uint32_t s_tab[16];
+  const uint32_t lane = lane_id(), warp = threadIdx.x >> 5, grp = lane / Geo::TPR, p = lane & (Geo::TPR - 1);
+  const uint32_t W = blockDim.x >> 5;
+  const uint32_t nwarps = gridDim.x * W, gw = blockIdx.x * W + warp;
+  const uint32_t base = smem_addr(smem_raw);
+  const int64_t K = a.K;
+  const int T = a.T;
+  const uint32_t G = a.gend[a.nmat - 1];
+  const int64_t slot = blockIdx.y;
+  const int64_t row0 = a.ei ? (int64_t)a.ei[slot] * a.RS + a.R0 : 0;  // storage row of output row 0
+  const bool partial = (K & 127) != 0;                    // the last tile of a row is short
+  const uint32_t pmax = (uint32_t)(K & 127) / (4u * R);   // threads that hold weights in it
+  const uint32_t row_codes = (uint32_t)T * 64u;
+  const OctLayout L = oct_layout(base, W, NQ * QUAD);
+  if (base > OC_BASE_MAX || L.end > base + a.smem) {  // the host sized the window for another layout
+    if (threadIdx.x == 0) atomicExch(&g_oct_error, 1);
+    return;
+  }
+  // this warp's ring: NQ quads of four slots; in a slot, a thread's raw bytes at lane * 4R, its
+  // code words at 128R + lane * 2R
+  const uint32_t ring = (warp < L.in_a ? L.ring_a + warp * (NQ * QUAD) : OC_TOP + (warp - L.in_a) * (NQ * QUAD)) + lane * (4u * R);
+  const uint32_t to_codes = 128u * R - lane * (2u * R);  // from this thread's raw address in a slot to its codes
+  const bool code_lane = R > 1 || (lane & 1u) == 0;      // R = 1: even lanes copy the code words of two lanes
+
+  // where group g of this launch lives: matrix, storage row of this thread's row (rows past the
+  // matrix's end are clamped to its last row and not stored)
+  auto locate = [&](uint32_t g, int &mi, int64_t &r) {
+    mi = 0;
+    uint32_t g0 = 0;
+#pragma unroll
+    for (int i = 1; i < OC_MAT; i++)
+      if (i < a.nmat && g >= a.gend[i - 1]) mi = i, g0 = a.gend[i - 1];
+    r = (int64_t)(g - g0) * R + grp;
+  };
+
+  // ---- load side: runs NQ quads ahead of the decode, straight on into the warp's next group
+  uint32_t pg = gw;
+  int pt = 0;
+  bool plive = pg < G;
+  const uint8_t *praw = nullptr, *pcode = nullptr;
+  uint32_t m_flag = 0, m_epos = 0;  // next group's first flag byte of this thread, escape cursor
+  auto aim = [&]() {  // point the load side at group pg and fetch its small per-row data
+    int mi;
+    int64_t r;
+    locate(pg, mi, r);
+    const int64_t srow = row0 + min(r, a.N[mi] - 1);
+    praw = a.w[mi].raw + srow * K + p * (4u * R);
+    pcode = reinterpret_cast<const uint8_t *>(a.w[mi].codes) + srow * row_codes + p * (2u * R);
+    m_epos = __ldg(a.w[mi].row_esc + srow);
+    m_flag = p < 8u && (int)p < T ? (uint32_t)__ldg(a.w[mi].flags + srow * T + p) : 0u;
+  };
+  // tiles of the load side's next quad
+  auto load_count = [&]() { return plive ? min(4, T - pt) : 0; };
+  // the quad's copies are issued: close the cp.async group, move on (into the next group at a row's end)
+  auto load_advance = [&](int n) {
+    cp_commit();
+    praw += n * 128, pcode += n * 64, pt += n;
+    if (plive && pt == T) {
+      pt = 0, pg += nwarps, plive = pg < G;
+      if (plive) aim();
+    }
+  };
+  // any quad, tile by tile (a row's last quad, short tiles)
+  auto load_quad_slow = [&](uint32_t at, int n, float after) {
+    for (int u = 0; u < n; u++) {
+      const bool short_tile = partial && pt + u == T - 1;
+      copy_tile<R, 0>(at + u * SLOT, to_codes, (short_tile && p >= pmax ? praw - p * (4u * R) : praw) + u * 128, pcode + u * 64, code_lane, after);  // threads past the row's end copy thread 0's bytes and ignore them
+    }
+  };
+
+  if (plive) aim();
+  uint32_t c_epos = m_epos, c_flag = m_flag;  // the first group's, before the load side moves on
+#pragma unroll
+  for (int q = 0; q < NQ; q++) {
+    const int n = load_count();
+    load_quad_slow(ring + q * QUAD, n, 0.0f);
+    load_advance(n);
+  }
+  pdl_launch_dependents();
+
+  // ---- x and the pair table into shared memory (whole block)
+  {
+    if (threadIdx.x < 16) s_tab[threadIdx.x] = threadIdx.x < 15 ? (uint32_t)__ldg(a.w[0].table + threadIdx.x) : 0u;
+    pdl_wait();  // x may be the previous kernel's output; the weights above are not
+    // x: a tile's 256 bytes sit in the unused halves of table entries 2t and 2t+1, placed so that
+    // the threads of a row cover all banks with each of their reads: with R = 4, thread p reads
+    // values 16p .. 16p+7 from the first half and 16p+8 .. 16p+15 from the second, both at byte
+    // 16p of the half; with R = 2 or 1 the tile is simply cut in two
+    const uint4 *x8 = reinterpret_cast<const uint4 *>(a.x + (a.ei ? (int64_t)a.xi[slot] * K : 0));
+    for (int i = threadIdx.x; i < T * 16; i += blockDim.x) {
+      const uint32_t t = (uint32_t)i >> 4, q = (uint32_t)i & 15u;  // tile, 16-byte piece of the tile
+      const uint4 v = (int64_t)i * 8 < K ? __ldg(x8 + i) : make_uint4(0, 0, 0, 0);
+      const uint32_t half = R == 4 ? q & 1u : q >> 3, piece = R == 4 ? q >> 1 : q & 7u;
+      *reinterpret_cast<uint4 *>(smem_raw + (OC_LUT - base) + (2u * t + half) * 256u + 128u + piece * 16u) = v;
+    }
+    __syncthreads();
+    // entry `code` holds table[code & 15] << 7 | table[code >> 4] << 23 in each of its 32 lanes'
+    // words: one 16-byte store writes four lanes
+    for (uint32_t i = threadIdx.x; i < 256 * 8; i += blockDim.x) {
+      const uint32_t code = i >> 3, v = (s_tab[code & 15] << 7) | (s_tab[code >> 4] << 23);
+      *reinterpret_cast<uint4 *>(smem_raw + (OC_LUT - base) + code * 256u + (i & 7u) * 16u) = make_uint4(v, v, v, v);
+    }
+    __syncthreads();
+  }
+  if (gw >= G) {
+    cp_wait<0>();
+    return;
+  }
+  OctSelf me;
+  asm volatile("mov.u32 %0, 0;" : "=r"(me.ready)::"memory");  // after the barrier: orders x / table reads
+  me.lane = lane, me.to_codes = to_codes, me.lut = OC_LUT + lane * 4u;
+  me.gmask = (R == 1 ? 0xFFFFFFFFu : ((1u << Geo::TPR) - 1u) << (grp * Geo::TPR)), me.ltg = me.gmask & lanemask_lt();
+  const uint32_t xs0 = OC_LUT + 128u + (R == 4 ? p * 16u : R == 2 ? (p >> 3) * 256u + (p & 7u) * 16u : (p >> 4) * 256u + (p & 15u) * 8u);
+
+  // ---- decode side
+  uint32_t cg = gw;  // group being decoded
+  int ct = 0;        // tile of it
+  int c_mi;
+  int64_t c_r;
+  locate(cg, c_mi, c_r);
+  const uint8_t *c_flags = nullptr;  // flag bytes of this thread's row
+  uint32_t fm = 0;      // bit u: some row of the warp flags tile (ct & ~7) + u
+  uint32_t nflag = 0;   // this thread's flag byte of the next block of eight tiles (threads p < 8)
+  uint32_t xs = xs0;
+  OctRow<R> s;
+  auto begin_group = [&]() {  // c_epos / c_flag hold the group's cursor and first flag bytes
+    const int64_t srow = row0 + min(c_r, a.N[c_mi] - 1);
+    c_flags = a.w[c_mi].flags + srow * T;
+    me.esc = a.w[c_mi].esc, me.esc_cap = a.w[c_mi].n_esc + 1;
+    s.epos = c_epos;
+    nflag = c_flag;
+    s.win.base = s.epos & ~3u;
+    s.win.word = window_load(me.esc, me.esc_cap, s.win.base + p * 4u);
+    xs = xs0;
+#pragma unroll
+    for (int i = 0; i < R; i++) s.acc[i] = 0.0f;
+  };
+  begin_group();
+
+  // end of a group: combine the 32 virtual lanes (virtual lane = R * p + i: the strides of R and
+  // more run across threads, the smaller ones inside the thread), store, move on to the warp's
+  // next group. Returns false when there is none.
+  auto end_group = [&]() -> bool {
+#pragma unroll
+    for (int o = Geo::TPR / 2; o >= 1; o >>= 1) {
+#pragma unroll
+      for (int i = 0; i < R; i++) s.acc[i] = s.acc[i] + __shfl_xor_sync(BN_FULL, s.acc[i], o);
+    }
+#pragma unroll
+    for (int st = R / 2; st >= 1; st >>= 1) {
+#pragma unroll
+      for (int i = 0; i < st; i++) s.acc[i] = s.acc[i] + s.acc[i + st];
+    }
+    if (p == 0 && c_r < a.N[c_mi]) {
+      const uint16_t v = f32_to_bf16_bits(s.acc[0]);
+      if (a.ei) {
+        if (a.split > 0 && c_r >= a.split) a.y2[slot * (a.N[0] - a.split) + (c_r - a.split)] = v;
+        else a.y[0][slot * (a.split > 0 ? a.split : a.N[0]) + c_r] = v;
+      } else {
+        a.y[c_mi][c_r] = v;
+      }
+    }
+    cg += nwarps;
+    if (cg >= G) return false;
+    ct = 0;
+    locate(cg, c_mi, c_r);
+    c_epos = m_epos, c_flag = m_flag;  // fetched when the load side crossed into this group
+    begin_group();
+    return true;
+  };
+
+  uint32_t at = ring;  // quad being decoded (this thread's raw address in its first slot)
+  const uint32_t ring_end = ring + NQ * QUAD;
+  for (;;) {
+    if ((ct & 7) == 0) {  // a new block of eight tiles: fold the flag bytes, fetch the next block's
+      const uint32_t v = __ballot_sync(BN_FULL, nflag != 0);
+      fm = (R == 4 ? v | (v >> 8) | (v >> 16) | (v >> 24) : R == 2 ? v | (v >> 16) : v) & 0xFFu;
+      const int nt = ct + 8 + (int)p;
+      nflag = p < 8u && nt < T ? (uint32_t)__ldg(c_flags + nt) : 0u;
+    }
+    const uint32_t fq = fm >> (ct & 4);  // bit u: tile ct + u is flagged
+    const int cn = min(4, T - ct), pn = load_count();
+    const uint32_t token = cp_wait<NQ - 1>();  // all but the newest NQ - 1 groups have landed: this quad's has
+    if (R == 1) __syncwarp();                  // a lane reads code words its neighbour copied
+    if (cn == 4 && !partial) {
+      // four whole tiles; each slot is refilled, with a tile of the quad NQ ahead, once it is read
+      oct_step<R, 0>(s, me, at, xs, token, fq & 1u, true);
+      oct_step<R, 1>(s, me, at, xs, token, fq & 2u, true);
+      oct_step<R, 2>(s, me, at, xs, token, fq & 4u, true);
+      oct_step<R, 3>(s, me, at, xs, token, fq & 8u, true);
+      if (R == 1) __syncwarp();  // the neighbour's reads too
+      if (pn > 0) copy_tile<R, 0>(at, to_codes, praw, pcode, code_lane, s.acc[0]);
+      if (pn > 1) copy_tile<R, 1>(at, to_codes, praw, pcode, code_lane, s.acc[0]);
+      if (pn > 2) copy_tile<R, 2>(at, to_codes, praw, pcode, code_lane, s.acc[0]);
+      if (pn > 3) copy_tile<R, 3>(at, to_codes, praw, pcode, code_lane, s.acc[0]);
+    } else {
+      for (int u = 0; u < cn; u++) {
+        const bool live = !(partial && ct + u == T - 1) || p < pmax;
+        oct_step<R, 0>(s, me, at + u * SLOT, xs + u * 512u, token, (fq >> u) & 1u, live);
+      }
+      if (R == 1) __syncwarp();
+      load_quad_slow(at, pn, s.acc[0]);
+    }
+    load_advance(pn);
+    xs += cn * 512u;
+    at = at + QUAD == ring_end ? ring : at + QUAD;
+    ct += cn;
+    if (ct == T) {
+      if (!end_group()) break;
+    }
+  }
+  cp_wait<0>();
+}
+
+int oct_sms() {
+  static int n = 0;
+  if (!n) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    if (n <= 0) n = 148;
+  }
+  return n;
+}
+
+// Dynamic shared memory a block of `warps` warps with rings of `ring` bytes needs, whatever the
+// window's start (the kernel re-derives the layout from the real start); 0 if it does not fit.
+uint32_t oct_smem(uint32_t warps, uint32_t ring) {
+  const uint32_t a = oct_layout(0, warps, ring).end, b = oct_layout(OC_BASE_MAX, warps, ring).end;
+  const uint32_t need = a > b ? a : b;  // the window ends at base + smem >= smem
+  return need <= OC_SMEM_MAX ? need : 0;
+}
+
+template <int R, int NQ, int MAXW>
+int launch_oct_as(OctArgs a, unsigned blocks, unsigned slots, unsigned warps, cudaStream_t s) {
+  auto kern = r4_oct_kernel<R, NQ, MAXW>;
+  a.smem = oct_smem(warps, NQ * OctGeom<R>::QUAD);
+  if (!a.smem || warps > MAXW || NQ * 4 >= a.T) return -1;  // the ring must be shorter than a row (see the kernel's load side)
+  BN_CUDA(allow_smem(kern, OC_SMEM_MAX));
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(blocks, slots), cfg.blockDim = dim3(warps * 32), cfg.dynamicSmemBytes = a.smem, cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;  // start-up and the first weight loads overlap the previous kernel's tail
+  cfg.attrs = attr, cfg.numAttrs = 1;
+  BN_CUDA(cudaLaunchKernelEx(&cfg, kern, a));
+  return launched("r4_oct_kernel");
+}
+
+// Rows a warp walks side by side for `rows` output rows spread over `blocks` blocks: four when
+// that still gives every SM a dozen warps or more, else two, else one (measured on 3840-wide
+// rows: 15360 and 8192 rows are fastest with four, 4096 and 2048 with two).
+int oct_rows_per_warp(int64_t rows, int64_t blocks) {
+  return rows >= blocks * 52 ? 4 : rows >= blocks * 13 ? 2 : 1;
+}
+
+}  // namespace
+
+int oct_status(int *status) {
+  BN_CUDA(cudaMemcpyFromSymbol(status, g_oct_error, sizeof(int)));
+  return BN_OK;
+}
+
+// Launch shape: one block per SM (per slot share of the SMs for a gather), as many warps as
+// spread the row groups evenly; deeper rings when the warps are few, since then they are all the
+// memory parallelism there is.
+template <int R>
+static int oct_launch_r(OctArgs &a, int64_t blocks, int64_t slots, cudaStream_t s) {
+  const int64_t groups = a.gend[a.nmat - 1];
+  if (blocks > groups) blocks = groups;
+  const int64_t rounds = (groups + blocks * 32 - 1) / (blocks * 32);
+  const int64_t warps = (groups + blocks * rounds - 1) / (blocks * rounds);
+  int e = -1;
+  if (R == 4) {
+    if (warps <= 16 && e == -1) e = launch_oct_as<4, 2, 16>(a, (unsigned)blocks, (unsigned)slots, (unsigned)warps, s);
+    if (warps <= 26 && e == -1) e = launch_oct_as<4, 1, 26>(a, (unsigned)blocks, (unsigned)slots, (unsigned)warps, s);
+    if (e == -1) e = launch_oct_as<4, 1, 32>(a, (unsigned)blocks, (unsigned)slots, (unsigned)warps, s);
+  } else if (R == 2) {
+    if (warps <= 16 && e == -1) e = launch_oct_as<2, 4, 16>(a, (unsigned)blocks, (unsigned)slots, (unsigned)warps, s);
+    if (e == -1) e = launch_oct_as<2, 2, 32>(a, (unsigned)blocks, (unsigned)slots, (unsigned)warps, s);
+    if (e == -1) e = launch_oct_as<2, 1, 32>(a, (unsigned)blocks, (unsigned)slots, (unsigned)warps, s);
+  } else {
+    e = launch_oct_as<1, 2, 32>(a, (unsigned)blocks, (unsigned)slots, (unsigned)warps, s);
+    if (e == -1) e = launch_oct_as<1, 1, 32>(a, (unsigned)blocks, (unsigned)slots, (unsigned)warps, s);
+  }
+  return e;
+}
+
+// Fills gend for R rows per group and launches.
+static int oct_launch(OctArgs &a, int64_t slots, cudaStream_t s) {
+  const int64_t blocks = (oct_sms() + slots - 1) / slots;
+  int64_t rows = 0;
+  for (int i = 0; i < a.nmat; i++) rows += a.N[i];
+  const int R = oct_rows_per_warp(rows, blocks);
+  uint32_t g = 0;
+  for (int i = 0; i < OC_MAT; i++) {
+    if (i < a.nmat) g += (uint32_t)((a.N[i] + R - 1) / R);
+    a.gend[i] = g;
+  }
+  return R == 4 ? oct_launch_r<4>(a, blocks, slots, s) : R == 2 ? oct_launch_r<2>(a, blocks, slots, s) : oct_launch_r<1>(a, blocks, slots, s);
+}
+
+static bool oct_aligned(const bn_r4 *w, const uint16_t *x) {
+  return ((reinterpret_cast<uintptr_t>(w->raw) | reinterpret_cast<uintptr_t>(w->codes) | reinterpret_cast<uintptr_t>(x)) & 15) == 0 && (reinterpret_cast<uintptr_t>(w->esc) & 3) == 0;
+}
+
+// Up to four matrices of the same K against one x; -1 when the shape is outside the kernel's coverage.
+int oct_matvec_multi(const bn_r4 *const *w, const int64_t *N, uint16_t *const *y, int nmat, const uint16_t *x, int64_t K, cudaStream_t s) {
+  if (nmat < 1 || nmat > OC_MAT || K % 16 || K < 640 || K > 16384) return -1;
+  OctArgs a{};
+  for (int i = 0; i < nmat; i++) {
+    if (N[i] < 1 || N[i] > (1ll << 30) || !oct_aligned(w[i], x)) return -1;
+    a.w[i] = *w[i], a.y[i] = y[i], a.N[i] = N[i];
+  }
+  a.nmat = nmat, a.x = x, a.K = K, a.T = (int)tiles(K);
+  return oct_launch(a, 1, s);
+}
+
+int oct_matvec(const bn_r4 *w, const uint16_t *x, int64_t N, int64_t K, uint16_t *y, cudaStream_t s) {
+  return oct_matvec_multi(&w, &N, &y, 1, x, K, s);
+}
+
+int oct_gather(const bn_r4 *w, const uint16_t *x, const uint32_t *xi, const uint32_t *ei, int64_t G, int64_t n, int64_t K, int64_t RS, int64_t R0, int64_t split, uint16_t *y, uint16_t *y2, cudaStream_t s) {
+  if (K % 16 || K < 640 || K > 16384 || n < 1 || n > (1ll << 30) || G < 1 || G > 65535 || !oct_aligned(w, x)) return -1;
+  OctArgs a{};
+  a.w[0] = *w, a.y[0] = y, a.N[0] = n, a.nmat = 1;
+  a.x = x, a.K = K, a.T = (int)tiles(K);
+  a.xi = xi, a.ei = ei, a.RS = RS, a.R0 = R0, a.split = split, a.y2 = y2;
+  return oct_launch(a, G, s);
+}
+
+}  // namespace bn

@@ -545,9 +545,14 @@ static int launch_stream(StreamArgs a, cudaStream_t s, int64_t slots = 1, int64_
 // Returns -1 when the shape is outside what the streaming kernel covers. More resident warps
 // hide more of the decode's dependent-issue latency, so the widest block whose rings still fit
 // the shared window next to x is taken (24 warps for K = 3840, 20 for K = 15360).
+// The bulk copies and the 16-byte reads of x need 16-byte aligned arrays.
+static bool stream_aligned(const bn_r4 *w, const uint16_t *x) {
+  return ((reinterpret_cast<uintptr_t>(w->raw) | reinterpret_cast<uintptr_t>(w->codes) | reinterpret_cast<uintptr_t>(x)) & 15) == 0;
+}
+
 int stream_matvec(const bn_r4 *w, const uint16_t *x, int64_t N, int64_t K, uint16_t *y, cudaStream_t s) {
   const int64_t T = tiles(K);
-  if (K % 16 || N < 1 || T > 128) return -1;  // x lives in the table's 256 half entries, two per tile
+  if (K % 16 || N < 1 || T > 128 || !stream_aligned(w, x)) return -1;  // x lives in the table's 256 half entries, two per tile
   StreamArgs a{};
   a.w = *w, a.x = x, a.y = y, a.N = N, a.K = K, a.T = (int)T;
   // 26 warps when that evens the rows out (15360 rows over 148 SMs: 104 per SM = 26 x 4, against
@@ -565,7 +570,7 @@ int stream_matvec(const bn_r4 *w, const uint16_t *x, int64_t N, int64_t K, uint1
 // Expert gather through the streaming kernel; -1 when the shape is outside its coverage.
 int stream_gather(const bn_r4 *w, const uint16_t *x, const uint32_t *xi, const uint32_t *ei, int64_t G, int64_t n, int64_t K, int64_t RS, int64_t R0, int64_t split, uint16_t *y, uint16_t *y2, cudaStream_t s) {
   const int64_t T = tiles(K);
-  if (K % 16 || n < 1 || T > 128 || G < 1 || G > 65535) return -1;
+  if (K % 16 || n < 1 || T > 128 || G < 1 || G > 65535 || !stream_aligned(w, x)) return -1;
   StreamArgs a{};
   a.w = *w, a.x = x, a.y = y, a.y2 = y2, a.N = n, a.K = K, a.T = (int)T;
   a.xi = xi, a.ei = ei, a.RS = RS, a.R0 = R0, a.split = split;
@@ -587,7 +592,7 @@ static int stream_grouped_m(StreamArgs a, cudaStream_t s, int64_t groups, int64_
 
 int stream_gather_grouped(const bn_r4 *w, const uint16_t *x, const uint32_t *xi, const uint32_t *seg, const uint32_t *order, int64_t E, int64_t G, int64_t max_per_expert, int64_t n, int64_t K, int64_t RS, int64_t R0, int64_t split, uint16_t *y, uint16_t *y2, cudaStream_t s) {
   const int64_t T = tiles(K);
-  if (K % 16 || n < 1 || T > 200 || E < 1 || max_per_expert < 1) return -1;
+  if (K % 16 || n < 1 || T > 200 || E < 1 || max_per_expert < 1 || !stream_aligned(w, x)) return -1;
   const int m = max_per_expert <= 4 ? 4 : 8;
   const int64_t chunks = (max_per_expert + m - 1) / m;
   if (E * chunks > 65535) return -1;
@@ -610,7 +615,7 @@ static int stream_rows_m(StreamArgs a, cudaStream_t s) {
 
 int stream_rows(const bn_r4 *w, const uint16_t *x, int64_t x_stride, int64_t M, int64_t N, int64_t K, uint16_t *y, int64_t y_stride, cudaStream_t s) {
   const int64_t T = tiles(K);
-  if (K % 16 || x_stride % 8 || N < 1 || T > 200 || M < 2 || M > 8) return -1;
+  if (K % 16 || x_stride % 8 || N < 1 || T > 200 || M < 2 || M > 8 || !stream_aligned(w, x)) return -1;
   StreamArgs a{};
   a.w = *w, a.x = x, a.y = y, a.N = N, a.K = K, a.T = (int)T;
   a.m = (int)M, a.x_stride = x_stride, a.y_stride = y_stride;
@@ -623,8 +628,10 @@ int stream_rows(const bn_r4 *w, const uint16_t *x, int64_t x_stride, int64_t M, 
 
 extern "C" int bn_device_status(int *status) {
   if (!status) return bn::fail(BN_ERR_ARG, "bn_device_status: null pointer");
-  int stream = 0, mma = 0, xch = 0;
+  int stream = 0, mma = 0, xch = 0, oct = 0;
   BN_CUDA(cudaMemcpyFromSymbol(&stream, bn::g_stream_error, sizeof(int)));
+  if (int e = bn::oct_status(&oct)) return e;
+  if (oct) stream |= 4;
   if (int e = bn::mma_status(&mma)) return e;
   if (int e = bn::exchange_status(&xch)) return e;
   *status = stream | (mma << 8) | (xch << 16);

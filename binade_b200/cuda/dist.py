@@ -258,12 +258,16 @@ class RowShardedGroup(nn.Module):
         self.locals = nn.ModuleList(locals_) if all(isinstance(m, nn.Module) for m in locals_) else locals_
         self.Ns = list(Ns)
         self.group = group
+        from . import r4
+
+        # R4 projections of one input run as one launch
+        self._fused = r4.R4LinearGroup(locals_) if 1 <= len(locals_) <= 4 and all(isinstance(m, r4.R4Linear) for m in locals_) else None
 
     def forward(self, x: torch.Tensor):
         import torch.distributed as dist
 
         world = dist.get_world_size(self.group)
-        ys = [m(x) for m in self.locals]
+        ys = self._fused(x) if self._fused is not None else [m(x) for m in self.locals]
         if world == 1:
             return ys
         widths = [N // world for N in self.Ns]

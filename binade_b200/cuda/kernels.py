@@ -276,6 +276,26 @@ def r4_matvec(a: dict, x: torch.Tensor, N: int, K: int, struct=None) -> torch.Te
     return y
 
 
+class R4Group:
+    """Up to four R4 matrices of the same K whose batch-1 products share their input: one launch
+    for all of them (bn_r4_rows_multi). Keeps the bn_r4 structs and the pointer arrays alive."""
+
+    def __init__(self, structs, Ns, K: int):
+        if not 1 <= len(structs) <= 4:
+            raise ValueError("a group holds one to four matrices")
+        self.structs, self.Ns, self.K = list(structs), [int(n) for n in Ns], int(K)
+        n = len(self.structs)
+        self._w = (ctypes.c_void_p * n)(*[ctypes.addressof(s) for s in self.structs])
+        self._n = (ctypes.c_int64 * n)(*self.Ns)
+
+    def __call__(self, x: torch.Tensor):
+        """x [..., K] holding one row -> list of [..., N_i]."""
+        ys = [torch.empty((*x.shape[:-1], n), dtype=torch.bfloat16, device=x.device) for n in self.Ns]
+        yp = (ctypes.c_void_p * len(ys))(*[y.data_ptr() for y in ys])
+        _call("bn_r4_rows_multi", _p(x), ctypes.cast(self._w, ctypes.c_void_p), ctypes.cast(self._n, ctypes.c_void_p), len(ys), self.K, ctypes.cast(yp, ctypes.c_void_p))
+        return ys
+
+
 def r4_gather(a: dict, x: torch.Tensor, xi: torch.Tensor, ei: torch.Tensor, n: int, rs: int, r0: int, K: int, split: int | None = None, shape: tuple | None = None):
     """[G, n] (or `shape`), or with split the pair [G, split], [G, n - split]
     (reference: r4_gather, cuda_kernels.py:133-146). xi, ei: int32 tensors of G entries."""

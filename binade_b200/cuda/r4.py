@@ -4,6 +4,7 @@ Same roles and names as the reference's binade/mlx/r4.py, on torch:
   transcode(module)   Rice arrays {raw, table, meta, bits, roff} -> R4 dict, on the GPU in one
                       fused pass (reference: transcode + _rank_chunks, r4.py:119-175)
   R4Linear(a)         the linear-layer hook: y = x @ W.T with W decoded inside the kernel
+  R4LinearGroup(ms)   projections sharing an input: one launch for all of them at batch 1
   R4Embedding(a)      token rows decoded from an R4 table (r4.py:303-325); as_linear for tied heads
   RiceEmbedding(w)    gather-only table kept as a Rice stream, about 10.7 bits per weight resident
                       (r4.py:328-367)
@@ -195,6 +196,25 @@ class R4Linear(nn.Module, _R4):
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         return self._rows(x)
+
+
+class R4LinearGroup(nn.Module):
+    """Projections that share their input (q, k and v of an attention block; gate and up of an
+    MLP): forward(x) returns the list of their outputs. One input row goes through a single
+    launch for up to four matrices (bn_r4_rows_multi), every output bit-identical to what its own
+    R4Linear gives; more rows go module by module. The reference launches one kernel per
+    projection (binade/mlx/r4.py:186-192)."""
+
+    def __init__(self, linears):
+        super().__init__()
+        self.linears = nn.ModuleList(list(linears))
+        ks = {m.K for m in self.linears}
+        self._group = ck.R4Group([m._struct for m in self.linears], [m.N for m in self.linears], ks.pop()) if len(ks) == 1 and 1 <= len(self.linears) <= 4 else None
+
+    def forward(self, x: torch.Tensor):
+        if self._group is not None and x.numel() == self._group.K:
+            return self._group(x.contiguous())
+        return [m(x) for m in self.linears]
 
 
 class R4Embedding(nn.Module, _R4):

@@ -178,9 +178,19 @@ int bn_rice_lookup(const uint8_t *meta, const uint32_t *bits, uint64_t nwords, c
  * their products (fused multiply-add) for t then j ascending; columns >= K are skipped; lanes
  * combine with strides 16, 8, 4, 2, 1; one round-to-nearest-even to BF16. M = 1 replaces
  * r4_matvec, binade/mlx/cuda_kernels.py:118-130 (same order for K % 128 == 0). The weights are
- * read once whatever M. x_stride / y_stride: elements between rows of X / Y. */
+ * read once whatever M. x_stride / y_stride: elements between rows of X / Y. Any alignment of x
+ * is served; the fastest kernels need x and the raw / codes arrays on 16-byte boundaries and
+ * K % 16 == 0 (other calls run a plain-load kernel with the same results). */
 int bn_r4_rows(const uint16_t *x, int64_t x_stride, const bn_r4 *w, int64_t M, int64_t N, int64_t K,
                uint16_t *y, int64_t y_stride, void *stream);
+
+/* Up to four batch-1 products that share one input, in one launch: y[i] [N[i]] = W[i] . x for
+ * `count` matrices of the same K (q, k and v of an attention block; gate and up of an MLP), every
+ * output in the documented order of bn_r4_rows and bit-identical to `count` calls of it. The
+ * reference launches one r4_matvec per matrix (binade/mlx/cuda_kernels.py:118-130); small
+ * matrices are bound by the launch, not by their bytes. w, N, y: host arrays of `count` entries. */
+int bn_r4_rows_multi(const uint16_t *x, const bn_r4 *const *w, const int64_t *N, int count, int64_t K,
+                     uint16_t *const *y, void *stream);
 
 /* G independent matvecs (the decode step of a mixture of experts). Slot g multiplies input row
  * xi[g] of x [., K] by storage rows ei[g] * RS + R0 + r, r < n. With split == 0 results go to
@@ -220,8 +230,8 @@ int bn_push_gather(const void *const *locals, const uint64_t *bytes, int segment
                    uint32_t *counter, void *stream);
 
 /* Device-side status of the calling thread's current device: 0, or non-zero once a kernel of
- * this library gave up a bounded wait (its output is then incomplete): bits 0..7 the streaming
- * matvec, bits 8..15 the tensor-core GEMM, bits 16..23 the peer exchange. Every wait inside the
+ * this library gave up a bounded wait or refused a launch whose shared-memory window did not
+ * match (its output is then incomplete): bits 0..7 the batch-1 matvec kernels, bits 8..15 the tensor-core GEMM, bits 16..23 the peer exchange. Every wait inside the
  * kernels is bounded, so a lost copy or an absent peer ends in this status instead of a hang.
  * Synchronises with the device. No counterpart in the reference. */
 int bn_device_status(int *status);

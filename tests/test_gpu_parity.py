@@ -374,6 +374,85 @@ def test_matvec_bit_exact(N, K):
     assert np.array_equal(words(got), words(ref))
 
 
+@pytest.mark.parametrize("N,K", [(7800, 640), (7701, 1296), (2100, 3840), (1925, 704), (600, 16384), (1500, 2816), (15360, 768)])
+def test_matvec_rows_per_warp_shapes(N, K):
+    """The batch-1 kernel walks four, two or one row per warp depending on the row count, with
+    rings of different depths, full and short last tiles, one or several rounds per warp."""
+    from binade_b200.cuda import r4
+
+    rng = np.random.default_rng(N * 7 + K)
+    u = weights(rng, (N, K))
+    xw = bf16_words(rng.standard_normal((1, K)))
+    m = r4.R4Linear(r4.transcode(packed_arrays(u)))
+    got = m(dev(xw).view(torch.bfloat16))
+    assert np.array_equal(words(got)[0], o.c_r4_matvec(o.pack_r4(u), xw[0], N, K))
+
+
+@pytest.mark.parametrize("dense_escapes", [0.02, 0.5])
+def test_matvec_rows_dense_with_escapes(dense_escapes):
+    """Tiles with many escapes per thread and rows with more escapes than the register window
+    holds: the general patch path and the window's refills."""
+    from binade_b200.cuda import r4
+
+    N, K = 2200, 1280
+    rng = np.random.default_rng(17)
+    u = weights(rng, (N, K))
+    rare = bf16_words((2.0 ** np.arange(-60, 60, 1.5)).astype(np.float32))  # 80 exponents: most land past rank 14
+    hit = rng.random((N, K)) < dense_escapes
+    u[hit] = rare[rng.integers(0, len(rare), int(hit.sum()))]
+    xw = bf16_words(rng.standard_normal((1, K)) * 1e-3)
+    m = r4.R4Linear(r4.transcode(packed_arrays(u)))
+    want = o.pack_r4(u)
+    assert want["esc"].size - 1 > 0.5 * dense_escapes * N * K  # most of the rare exponents really escape
+    got = m(dev(xw).view(torch.bfloat16))
+    assert np.array_equal(words(got)[0], o.c_r4_matvec(want, xw[0], N, K))
+
+
+def test_linear_group_one_launch():
+    """q, k, v (and gate, up) through bn_r4_rows_multi: the same bits as one call per matrix,
+    for group sizes 1..4, unequal row counts, and a row count that is not a multiple of four."""
+    from binade_b200.cuda import r4
+
+    K = 1664
+    rng = np.random.default_rng(3)
+    Ns = [4096, 1022, 1024, 517]
+    us = [weights(rng, (n, K)) for n in Ns]
+    ms = [r4.R4Linear(r4.transcode(packed_arrays(u))) for u in us]
+    xw = bf16_words(rng.standard_normal((1, K)))
+    x = dev(xw).view(torch.bfloat16)
+    for count in (1, 2, 3, 4):
+        ys = r4.R4LinearGroup(ms[:count])(x)
+        assert len(ys) == count
+        for y, u, n in zip(ys, us, Ns):
+            assert y.shape == (1, n)
+            assert np.array_equal(words(y)[0], o.c_r4_matvec(o.pack_r4(u), xw[0], n, K))
+    two_rows = torch.cat([x, x])
+    for y, m in zip(r4.R4LinearGroup(ms[:2])(two_rows), ms):  # several rows: module by module
+        assert np.array_equal(words(y), words(m(two_rows)))
+
+
+def test_matvec_unaligned_input_falls_back():
+    """An input vector that does not start on a 16-byte boundary (a view at an odd offset) is
+    served by the plain-load kernel instead of the bulk-copy ones: same bits."""
+    from binade_b200.cuda import kernels as ck
+    from binade_b200.cuda import r4
+
+    N, K = 700, 2048
+    rng = np.random.default_rng(5)
+    u = weights(rng, (N, K))
+    xw = bf16_words(rng.standard_normal((1, K)))
+    m = r4.R4Linear(r4.transcode(packed_arrays(u)))
+    want = o.c_r4_matvec(o.pack_r4(u), xw[0], N, K)
+    for shift in (1, 3, 4):
+        buf = torch.zeros(K + 8, dtype=torch.bfloat16, device="cuda")
+        buf[shift : shift + K] = dev(xw).view(torch.bfloat16)[0]
+        x = buf[shift : shift + K]
+        assert x.data_ptr() % 16 != 0
+        assert np.array_equal(words(ck.r4_matvec(m._a, x, N, K)), want)
+        xs = buf[shift : shift + K].reshape(1, K)
+        assert np.array_equal(words(ck.r4_rows(m._a, xs, N, K))[0], want)
+
+
 def adversarial(R: int, K: int, seed: int = 0) -> np.ndarray:
     """Rows whose sum with an all-ones input depends on the order: +2^25 first, then ones that
     vanish against it (fp32 ulp at 2^25 is 4), then -2^25: 0 in the documented order. Row types
