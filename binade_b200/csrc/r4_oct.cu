@@ -121,7 +121,8 @@ struct OctArgs {
   bn_r4 w[OC_MAT];
   uint16_t *y[OC_MAT];
   int64_t N[OC_MAT];        // rows of each matrix (of one expert, for a gather)
-  uint32_t gend[OC_MAT];    // row groups (4 rows) up to and including matrix i
+  uint32_t groups[OC_MAT];  // row groups (R rows each) of matrix i
+  uint32_t bend[OC_MAT];    // blocks (of grid.x) up to and including matrix i: a block serves one matrix, whose table it builds
   int nmat;
   const uint16_t *x;
   int64_t K;
@@ -302,12 +303,21 @@ __global__ void __launch_bounds__(MAXW * 32, 1) r4_oct_kernel(const __grid_const
   __shared__ uint32_t s_tab[16];
   const uint32_t lane = lane_id(), warp = threadIdx.x >> 5, grp = lane / Geo::TPR, p = lane & (Geo::TPR - 1);
   const uint32_t W = blockDim.x >> 5;
-  const uint32_t nwarps = gridDim.x * W, gw = blockIdx.x * W + warp;
   const uint32_t base = smem_addr(smem_raw);
   const int64_t K = a.K;
   const int T = a.T;
-  const uint32_t G = a.gend[a.nmat - 1];
+  // this block's matrix: blocks are dealt out to the matrices of the launch in proportion to
+  // their rows, since a block holds one pair table
+  int mi = 0;
+  uint32_t b0 = 0;
+#pragma unroll
+  for (int i = 1; i < OC_MAT; i++)
+    if (i < a.nmat && blockIdx.x >= a.bend[i - 1]) mi = i, b0 = a.bend[i - 1];
+  const bn_r4 mat = a.w[mi];
+  const int64_t N = a.N[mi];
+  const uint32_t G = a.groups[mi];
   const int64_t slot = blockIdx.y;
+  const uint32_t nwarps = (a.bend[mi] - b0) * W, gw = (blockIdx.x - b0) * W + warp;
   const int64_t row0 = a.ei ? (int64_t)a.ei[slot] * a.RS + a.R0 : 0;  // storage row of output row 0
   const bool partial = (K & 127) != 0;                    // the last tile of a row is short
   const uint32_t pmax = (uint32_t)(K & 127) / (4u * R);   // threads that hold weights in it
@@ -323,16 +333,9 @@ __global__ void __launch_bounds__(MAXW * 32, 1) r4_oct_kernel(const __grid_const
   const uint32_t to_codes = 128u * R - lane * (2u * R);  // from this thread's raw address in a slot to its codes
   const bool code_lane = R > 1 || (lane & 1u) == 0;      // R = 1: even lanes copy the code words of two lanes
 
-  // where group g of this launch lives: matrix, storage row of this thread's row (rows past the
-  // matrix's end are clamped to its last row and not stored)
-  auto locate = [&](uint32_t g, int &mi, int64_t &r) {
-    mi = 0;
-    uint32_t g0 = 0;
-#pragma unroll
-    for (int i = 1; i < OC_MAT; i++)
-      if (i < a.nmat && g >= a.gend[i - 1]) mi = i, g0 = a.gend[i - 1];
-    r = (int64_t)(g - g0) * R + grp;
-  };
+  // this thread's output row in group g of the matrix (rows past the matrix's end are clamped to
+  // its last row when they are read and are not stored)
+  auto row_of = [&](uint32_t g) { return (int64_t)g * R + grp; };
 
   // ---- load side: runs NQ quads ahead of the decode, straight on into the warp's next group
   uint32_t pg = gw;
@@ -341,14 +344,11 @@ __global__ void __launch_bounds__(MAXW * 32, 1) r4_oct_kernel(const __grid_const
   const uint8_t *praw = nullptr, *pcode = nullptr;
   uint32_t m_flag = 0, m_epos = 0;  // next group's first flag byte of this thread, escape cursor
   auto aim = [&]() {  // point the load side at group pg and fetch its small per-row data
-    int mi;
-    int64_t r;
-    locate(pg, mi, r);
-    const int64_t srow = row0 + min(r, a.N[mi] - 1);
-    praw = a.w[mi].raw + srow * K + p * (4u * R);
-    pcode = reinterpret_cast<const uint8_t *>(a.w[mi].codes) + srow * row_codes + p * (2u * R);
-    m_epos = __ldg(a.w[mi].row_esc + srow);
-    m_flag = p < 8u && (int)p < T ? (uint32_t)__ldg(a.w[mi].flags + srow * T + p) : 0u;
+    const int64_t srow = row0 + min(row_of(pg), N - 1);
+    praw = mat.raw + srow * K + p * (4u * R);
+    pcode = reinterpret_cast<const uint8_t *>(mat.codes) + srow * row_codes + p * (2u * R);
+    m_epos = __ldg(mat.row_esc + srow);
+    m_flag = p < 8u && (int)p < T ? (uint32_t)__ldg(mat.flags + srow * T + p) : 0u;
   };
   // tiles of the load side's next quad
   auto load_count = [&]() { return plive ? min(4, T - pt) : 0; };
@@ -381,7 +381,7 @@ __global__ void __launch_bounds__(MAXW * 32, 1) r4_oct_kernel(const __grid_const
 
   // ---- x and the pair table into shared memory (whole block)
   {
-    if (threadIdx.x < 16) s_tab[threadIdx.x] = threadIdx.x < 15 ? (uint32_t)__ldg(a.w[0].table + threadIdx.x) : 0u;
+    if (threadIdx.x < 16) s_tab[threadIdx.x] = threadIdx.x < 15 ? (uint32_t)__ldg(mat.table + threadIdx.x) : 0u;
     pdl_wait();  // x may be the previous kernel's output; the weights above are not
     // x: a tile's 256 bytes sit in the unused halves of table entries 2t and 2t+1, placed so that
     // the threads of a row cover all banks with each of their reads: with R = 4, thread p reads
@@ -416,18 +416,16 @@ __global__ void __launch_bounds__(MAXW * 32, 1) r4_oct_kernel(const __grid_const
   // ---- decode side
   uint32_t cg = gw;  // group being decoded
   int ct = 0;        // tile of it
-  int c_mi;
-  int64_t c_r;
-  locate(cg, c_mi, c_r);
+  int64_t c_r = row_of(cg);
   const uint8_t *c_flags = nullptr;  // flag bytes of this thread's row
+  me.esc = mat.esc, me.esc_cap = mat.n_esc + 1;
   uint32_t fm = 0;      // bit u: some row of the warp flags tile (ct & ~7) + u
   uint32_t nflag = 0;   // this thread's flag byte of the next block of eight tiles (threads p < 8)
   uint32_t xs = xs0;
   OctRow<R> s;
   auto begin_group = [&]() {  // c_epos / c_flag hold the group's cursor and first flag bytes
-    const int64_t srow = row0 + min(c_r, a.N[c_mi] - 1);
-    c_flags = a.w[c_mi].flags + srow * T;
-    me.esc = a.w[c_mi].esc, me.esc_cap = a.w[c_mi].n_esc + 1;
+    const int64_t srow = row0 + min(c_r, N - 1);
+    c_flags = mat.flags + srow * T;
     s.epos = c_epos;
     nflag = c_flag;
     s.win.base = s.epos & ~3u;
@@ -452,19 +450,19 @@ __global__ void __launch_bounds__(MAXW * 32, 1) r4_oct_kernel(const __grid_const
 #pragma unroll
       for (int i = 0; i < st; i++) s.acc[i] = s.acc[i] + s.acc[i + st];
     }
-    if (p == 0 && c_r < a.N[c_mi]) {
+    if (p == 0 && c_r < N) {
       const uint16_t v = f32_to_bf16_bits(s.acc[0]);
       if (a.ei) {
-        if (a.split > 0 && c_r >= a.split) a.y2[slot * (a.N[0] - a.split) + (c_r - a.split)] = v;
-        else a.y[0][slot * (a.split > 0 ? a.split : a.N[0]) + c_r] = v;
+        if (a.split > 0 && c_r >= a.split) a.y2[slot * (N - a.split) + (c_r - a.split)] = v;
+        else a.y[0][slot * (a.split > 0 ? a.split : N) + c_r] = v;
       } else {
-        a.y[c_mi][c_r] = v;
+        a.y[mi][c_r] = v;
       }
     }
     cg += nwarps;
     if (cg >= G) return false;
     ct = 0;
-    locate(cg, c_mi, c_r);
+    c_r = row_of(cg);
     c_epos = m_epos, c_flag = m_flag;  // fetched when the load side crossed into this group
     begin_group();
     return true;
@@ -562,15 +560,41 @@ int oct_status(int *status) {
   return BN_OK;
 }
 
-// Launch shape: one block per SM (per slot share of the SMs for a gather), as many warps as
-// spread the row groups evenly; deeper rings when the warps are few, since then they are all the
-// memory parallelism there is.
+// Launch shape: one block per SM (per slot share of the SMs for a gather), dealt out to the
+// matrices in proportion to their rows; as many warps as spread a matrix's row groups evenly over
+// its blocks; deeper rings when the warps are few, since then they are all the memory
+// parallelism there is.
+// Fills the launch's shape for R rows per warp: row groups, blocks per matrix (proportional to
+// its groups, at least one, summing to `blocks`, which shrinks to the group count when that is
+// smaller). Returns the warps a block needs, or -1 when there are fewer blocks than matrices.
+static int64_t oct_shape(OctArgs &a, int R, int64_t &blocks) {
+  int64_t groups = 0;
+  for (int i = 0; i < a.nmat; i++) a.groups[i] = (uint32_t)((a.N[i] + R - 1) / R), groups += a.groups[i];
+  if (blocks > groups) blocks = groups;
+  if (blocks < a.nmat) return -1;
+  int64_t share[OC_MAT], given = 0;
+  for (int i = 0; i < a.nmat; i++) share[i] = max((int64_t)1, blocks * a.groups[i] / groups), given += share[i];
+  for (int i = 0; given != blocks; i = (i + 1) % a.nmat) {
+    if (given < blocks) share[i]++, given++;
+    else if (share[i] > 1) share[i]--, given--;
+  }
+  int64_t warps = 1;
+  uint32_t b = 0;
+  for (int i = 0; i < OC_MAT; i++) {
+    if (i < a.nmat) {
+      b += (uint32_t)share[i];
+      const int64_t rounds = (a.groups[i] + share[i] * 32 - 1) / (share[i] * 32);
+      warps = max(warps, (int64_t)((a.groups[i] + share[i] * rounds - 1) / (share[i] * rounds)));
+    }
+    a.bend[i] = b;
+  }
+  return warps;
+}
+
 template <int R>
 static int oct_launch_r(OctArgs &a, int64_t blocks, int64_t slots, cudaStream_t s) {
-  const int64_t groups = a.gend[a.nmat - 1];
-  if (blocks > groups) blocks = groups;
-  const int64_t rounds = (groups + blocks * 32 - 1) / (blocks * 32);
-  const int64_t warps = (groups + blocks * rounds - 1) / (blocks * rounds);
+  const int64_t warps = oct_shape(a, R, blocks);
+  if (warps < 0) return -1;
   int e = -1;
   if (R == 4) {
     if (warps <= 16 && e == -1) e = launch_oct_as<4, 2, 16>(a, (unsigned)blocks, (unsigned)slots, (unsigned)warps, s);
@@ -587,17 +611,11 @@ static int oct_launch_r(OctArgs &a, int64_t blocks, int64_t slots, cudaStream_t 
   return e;
 }
 
-// Fills gend for R rows per group and launches.
 static int oct_launch(OctArgs &a, int64_t slots, cudaStream_t s) {
   const int64_t blocks = (oct_sms() + slots - 1) / slots;
   int64_t rows = 0;
   for (int i = 0; i < a.nmat; i++) rows += a.N[i];
   const int R = oct_rows_per_warp(rows, blocks);
-  uint32_t g = 0;
-  for (int i = 0; i < OC_MAT; i++) {
-    if (i < a.nmat) g += (uint32_t)((a.N[i] + R - 1) / R);
-    a.gend[i] = g;
-  }
   return R == 4 ? oct_launch_r<4>(a, blocks, slots, s) : R == 2 ? oct_launch_r<2>(a, blocks, slots, s) : oct_launch_r<1>(a, blocks, slots, s);
 }
 

@@ -63,7 +63,7 @@ class Decoder(nn.Module):
         s = self.shape = shape
         if s.heads % world or s.kv_heads % world or s.ffn % world or s.hidden % world or s.vocab % world:
             raise ValueError(f"world {world} does not divide heads, kv_heads, ffn, hidden and vocab")
-        self.rank, self.world, self.group = rank, world, group
+        self.rank, self.world, self.group, self.seed = rank, world, group, seed
         dev = torch.device(device)
         self.hq, self.hkv = s.heads // world, s.kv_heads // world
         d = s.head_dim
@@ -112,6 +112,51 @@ class Decoder(nn.Module):
         ang = torch.arange(s.max_seq, device=dev, dtype=torch.float32)[:, None] * inv[None, :]
         self.cos, self.sin = torch.cos(ang), torch.sin(ang)  # [max_seq, d/2]
         self.positions = torch.arange(s.max_seq, device=dev)
+
+    def _sources(self):
+        """(module, source weight) for every linear of this rank, weights regenerated one at a
+        time from the construction seeds."""
+        s, d, dev = self.shape, self.shape.head_dim, self.k_cache.device
+        rows_of = lambda w, count: w[slice(*row_range(count, self.rank, self.world))]
+        local = lambda m: m.local if isinstance(m, RowShardedLinear) else m
+        for l in range(s.layers):
+            base = self.seed + 100 * (l + 1)
+            wq, wk, wv = (synthetic_weight(n, s.hidden, base + j, dev) for j, n in ((1, s.heads * d), (2, s.kv_heads * d), (3, s.kv_heads * d)))
+            yield self.qkv[l], torch.cat([rows_of(wq, s.heads * d), rows_of(wk, s.kv_heads * d), rows_of(wv, s.kv_heads * d)])
+            yield local(self.o[l]), rows_of(synthetic_weight(s.hidden, s.heads * d, base + 4, dev), s.hidden)
+            yield self.gate_up[l], torch.cat([rows_of(synthetic_weight(s.ffn, s.hidden, base + 5, dev), s.ffn), rows_of(synthetic_weight(s.ffn, s.hidden, base + 6, dev), s.ffn)])
+            yield local(self.down[l]), rows_of(synthetic_weight(s.hidden, s.ffn, base + 7, dev), s.hidden)
+        yield local(self.lm_head), rows_of(synthetic_weight(s.vocab, s.hidden, self.seed + 2, dev), s.vocab)
+
+    @torch.no_grad()
+    def self_check(self) -> dict:
+        """For a model on R4 weights: every linear's dense decode must equal its source weight
+        bit for bit (raises otherwise), and one decode step (token 0 at position 0) is run with
+        every linear's output compared with an fp32 product of the same weights: returns the
+        number of linears checked and the largest deviation in BF16 units in the last place
+        (the sums differ from fp32 only by their order, so a few ulps at most)."""
+        checked, worst = 0, 0
+        hooks = []
+
+        def compare(module, inputs, output):
+            nonlocal worst
+            ref = (inputs[0].reshape(-1, module.K).float() @ module.dense().reshape(module.N, module.K).float().T).to(torch.bfloat16)
+            worst = max(worst, int(r4.ulp_distance(output.reshape(ref.shape), ref).max().item()))
+
+        for m, w in self._sources():
+            if not isinstance(m, r4.R4Linear):
+                return {"linears": 0, "note": "not an R4 model"}
+            if not torch.equal(m.dense().reshape(w.shape).view(torch.int16), w.view(torch.int16)):
+                raise RuntimeError("an R4 linear does not decode to its source weight")
+            checked += 1
+            hooks.append(m.register_forward_hook(compare))
+            del w
+        dev = self.k_cache.device
+        self.step(torch.zeros(1, dtype=torch.int64, device=dev), torch.zeros(1, dtype=torch.int64, device=dev))
+        for h in hooks:
+            h.remove()
+        self.k_cache.zero_(), self.v_cache.zero_()
+        return {"linears_decoding_to_their_source": checked, "max_ulp_vs_fp32_product_step0": worst}
 
     def linear_bytes(self) -> int:
         """Weight bytes one decode step streams on this rank (R4 arrays or BF16 words)."""

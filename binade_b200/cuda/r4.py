@@ -124,6 +124,16 @@ def from_dense(w: torch.Tensor) -> dict:
     return {"raw": raw, "table": table_t, "codes": codes, "flags": flags, "esc": esc, "row_esc": row_esc, "shape": shape}
 
 
+def ulp_distance(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+    """Distance between two bfloat16 tensors in units in the last place: the difference of their
+    positions on the number line of BF16 values (+0 and -0 coincide), as int32."""
+    def key(t):
+        v = t.contiguous().view(torch.int16).to(torch.int32) & 0xFFFF
+        return torch.where(v >= 0x8000, -(v & 0x7FFF), v)
+
+    return (key(a) - key(b)).abs()
+
+
 def r4_bytes(a: dict) -> int:
     """Bytes a matvec streams: every R4 array (reference: scripts/matvec_bench.py:34-35)."""
     return sum(a[k].numel() * a[k].element_size() for k in ck.R4_KEYS)
