@@ -176,38 +176,44 @@ struct OctGeom {
 };
 
 // General case of a flagged tile: some thread holds several escapes. Inclusive scan of the counts
-// over the row's threads, then every thread walks its own hits. Whole warp calls it.
+// over the row's threads, then every thread walks its own hits. Whole warp calls it. Kept out of
+// line, pair words in and out by value: it is rare, and inlined its loops and merges cost the
+// common path registers and moves.
 template <int R>
-__device__ __forceinline__ uint32_t escape_general(const uint32_t (&hits)[(R + 1) / 2], uint32_t cnt, uint32_t epos, EscWindow win, const uint8_t *__restrict__ esc, uint32_t lane, uint32_t (&w)[2 * R]) {
+struct OctWords {
+  uint32_t w[2 * R], tot;
+};
+template <int R>
+__device__ __noinline__ OctWords<R> escape_general(OctWords<R> io, uint32_t h0, uint32_t h1, uint32_t cnt, uint32_t epos, uint32_t win_word, uint32_t win_base, const uint8_t *__restrict__ esc) {
   using Geo = OctGeom<R>;
-  const uint32_t p = lane & (Geo::TPR - 1);
+  const uint32_t lane = lane_id(), p = lane & (Geo::TPR - 1);
   uint32_t s = cnt;
 #pragma unroll
   for (int d = 1; d < Geo::TPR; d <<= 1) {
     const uint32_t n = __shfl_up_sync(BN_FULL, s, d, Geo::TPR);
     if (p >= (uint32_t)d) s += n;
   }
-  const uint32_t tot = __shfl_sync(BN_FULL, s, Geo::TPR - 1, Geo::TPR);
+  io.tot = __shfl_sync(BN_FULL, s, Geo::TPR - 1, Geo::TPR);
   uint32_t q = epos + s - cnt;
 #pragma unroll
   for (int half = 0; half < Geo::NC; half++) {
-    uint32_t h = hits[half];
+    uint32_t h = half ? h1 : h0;
     while (__any_sync(BN_FULL, h != 0)) {
       const uint32_t bit = (uint32_t)__ffs((int)h) - 1u;  // 4j
-      const uint32_t idx = q - win.base;
-      const uint32_t v = __shfl_sync(BN_FULL, win.word, (lane & ~(Geo::TPR - 1)) | ((idx >> 2) & (Geo::TPR - 1)));
+      const uint32_t idx = q - win_base;
+      const uint32_t v = __shfl_sync(BN_FULL, win_word, (lane & ~(Geo::TPR - 1)) | ((idx >> 2) & (Geo::TPR - 1)));
       uint32_t e = __byte_perm(v, 0u, 0x4440u | (idx & 3u));
       if (h != 0 && idx >= Geo::WINDOW) e = esc[q];  // outside the window (a row dense with escapes)
       const uint32_t val = e << (7u + ((bit & 4u) << 2));
       if (h != 0) {
-        if (half) or_into<4>(bit >> 3, val, w);
-        else or_into<0>(bit >> 3, val, w);
+        if (half) or_into<4>(bit >> 3, val, io.w);
+        else or_into<0>(bit >> 3, val, io.w);
         q++;
         h &= h - 1u;
       }
     }
   }
-  return tot;
+  return io;
 }
 
 // Where a block's rings sit in the shared window (absolute shared addresses; base = start of the
@@ -234,26 +240,38 @@ struct OctRow {
 
 // What a thread needs to know about itself and its row's matrix while it decodes.
 struct OctSelf {
-  uint32_t lane, to_codes, lut, ready, gmask, ltg;
+  uint32_t lane, lane_hi, to_codes, lut, ready, gmask, ltg;  // lane_hi: first lane of this thread's row
   const uint8_t *esc;
   uint64_t esc_cap;
 };
 
-// One tile of this thread's row: slot U of the quad at `at`, x at xs + U * 512.
-//   flagged  some row of the warp holds a code 15 in this tile (warp-uniform)
-//   live     this thread holds weights in the tile (false only in a row's short last tile)
+// One tile of this thread's row, decoded: pair words (escapes not yet applied), the matching
+// values of x, and the code registers (the patch path looks for code 15 in them).
+template <int R>
+struct OctTile {
+  uint32_t w[2 * R], xx[2 * R], cc[(R + 1) / 2];
+};
+
+// Reads slot U of the quad at `at` and x at xs + U * 512, looks the exponents up.
 template <int R, int U>
-__device__ __forceinline__ void oct_step(OctRow<R> &s, const OctSelf &me, uint32_t at, uint32_t xs, uint32_t token, bool flagged, bool live) {
-  using Geo = OctGeom<R>;
-  uint32_t rr[R], cc[Geo::NC], xx[2 * R], w[2 * R];
-  ring_read<R, U>(at, me.to_codes, token, rr, cc);
-  x_read<R, U>(xs, me.ready, xx);
+__device__ __forceinline__ void oct_decode(OctTile<R> &t, const OctSelf &me, uint32_t at, uint32_t xs, uint32_t token) {
+  uint32_t rr[R];
+  ring_read<R, U>(at, me.to_codes, token, rr, t.cc);
+  x_read<R, U>(xs, me.ready, t.xx);
 #pragma unroll
   for (int i = 0; i < R; i++) {
-    const uint32_t c = cc[i >> 1];
-    w[2 * i] = (__byte_perm(rr[i], 0u, 0x1100) & 0x807F807Fu) | lut_read(__byte_perm(c, me.lut, (i & 1) ? 0x7624 : 0x7604), me.ready);
-    w[2 * i + 1] = (__byte_perm(rr[i], 0u, 0x3322) & 0x807F807Fu) | lut_read(__byte_perm(c, me.lut, (i & 1) ? 0x7634 : 0x7614), me.ready);
+    const uint32_t c = t.cc[i >> 1];
+    t.w[2 * i] = (__byte_perm(rr[i], 0u, 0x1100) & 0x807F807Fu) | lut_read(__byte_perm(c, me.lut, (i & 1) ? 0x7624 : 0x7604), me.ready);
+    t.w[2 * i + 1] = (__byte_perm(rr[i], 0u, 0x3322) & 0x807F807Fu) | lut_read(__byte_perm(c, me.lut, (i & 1) ? 0x7634 : 0x7614), me.ready);
   }
+}
+
+// Applies the tile's escapes, if any row of the warp has some, and adds its products.
+//   flagged  some row of the warp holds a code 15 in this tile (warp-uniform)
+//   live     this thread holds weights in the tile (false only in a row's short last tile)
+template <int R>
+__device__ __forceinline__ void oct_finish(OctRow<R> &s, OctTile<R> &t, const OctSelf &me, bool flagged, bool live) {
+  using Geo = OctGeom<R>;
 #ifdef OC_PROBE_NO_ESC
   if (false) {
 #else
@@ -261,35 +279,52 @@ __device__ __forceinline__ void oct_step(OctRow<R> &s, const OctSelf &me, uint32
 #endif
     uint32_t hits[Geo::NC], cnt = 0;
 #pragma unroll
-    for (int i = 0; i < Geo::NC; i++) hits[i] = hits15(cc[i]), cnt += __popc(hits[i]);
+    for (int i = 0; i < Geo::NC; i++) hits[i] = hits15(t.cc[i]), cnt += __popc(hits[i]);
     const uint32_t one = __ballot_sync(BN_FULL, cnt == 1u), many = __ballot_sync(BN_FULL, cnt > 1u);
-    if (many == 0) {
-      // at most one escape per thread (nearly always one in the whole warp): its byte is as many
-      // places after the row's cursor as threads of the row before this one hold an escape
-      const uint32_t idx = s.epos + __popc(one & me.ltg) - s.win.base;
-      const uint32_t v = __shfl_sync(BN_FULL, s.win.word, (me.lane & ~(Geo::TPR - 1)) | ((idx >> 2) & (Geo::TPR - 1)));
-      if (cnt) {
-        const uint32_t e = idx < Geo::WINDOW ? __byte_perm(v, 0u, 0x4440u | (idx & 3u)) : (uint32_t)me.esc[s.win.base + idx];
-        const uint32_t upper = Geo::NC > 1 ? hits[Geo::NC - 1] : 0u;
-        const uint32_t bit = (uint32_t)__ffs((int)(hits[0] | upper)) - 1u;  // 4j: weight j of the register's eight
-        const uint32_t val = e << (7u + ((bit & 4u) << 2));
-        if (upper) or_into<4>(bit >> 3, val, w);
-        else or_into<0>(bit >> 3, val, w);
-      }
+    // at most one escape per thread (nearly always one in the whole warp), all inside the rows'
+    // windows: straight-line code. Its byte is as many places after the row's cursor as threads
+    // of the row before this one hold an escape.
+    const uint32_t idx = s.epos + __popc(one & me.ltg) - s.win.base;
+    const uint32_t far = __ballot_sync(BN_FULL, cnt != 0 && idx >= Geo::WINDOW);
+    if (__builtin_expect((many | far) == 0, 1)) {
+      const uint32_t v = __shfl_sync(BN_FULL, s.win.word, me.lane_hi | ((idx >> 2) & (Geo::TPR - 1)));
+      const uint32_t e = cnt ? __byte_perm(v, 0u, 0x4440u | (idx & 3u)) : 0u;  // threads without an escape OR nothing in
+      const uint32_t upper = Geo::NC > 1 ? hits[Geo::NC - 1] : 0u;
+      const uint32_t bit = (uint32_t)__ffs((int)(hits[0] | upper)) - 1u;  // 4j: weight j of the register's eight
+      const uint32_t val = e << (7u + ((bit & 4u) << 2));
+      const uint32_t k = (bit >> 3) & 3u;
+      const uint32_t lo = upper ? 0u : val, hi = upper ? val : 0u;
+#pragma unroll
+      for (int i = 0; i < 4 && i < 2 * R; i++) t.w[i] |= k == (uint32_t)i ? lo : 0u;
+#pragma unroll
+      for (int i = 4; i < 2 * R; i++) t.w[i] |= k == (uint32_t)(i - 4) ? hi : 0u;
       s.epos += __popc(one & me.gmask);
     } else {
-      s.epos += escape_general<R>(hits, cnt, s.epos, s.win, me.esc, me.lane, w);
+      OctWords<R> io;
+#pragma unroll
+      for (int i = 0; i < 2 * R; i++) io.w[i] = t.w[i];
+      io = escape_general<R>(io, hits[0], Geo::NC > 1 ? hits[Geo::NC - 1] : 0u, cnt, s.epos, s.win.word, s.win.base, me.esc);
+#pragma unroll
+      for (int i = 0; i < 2 * R; i++) t.w[i] = io.w[i];
+      s.epos += io.tot;
     }
-    if (s.epos - s.win.base >= Geo::WINDOW / 2) {  // slide the window on (the load returns while tiles decode)
+    if (__builtin_expect(s.epos - s.win.base >= Geo::WINDOW / 2, 0)) {  // slide the window on (the load returns while tiles decode)
       s.win.base = s.epos & ~3u;
       s.win.word = window_load(me.esc, me.esc_cap, s.win.base + (me.lane & (Geo::TPR - 1)) * 4u);
     }
   }
   if (live) {  // columns >= K are skipped, not added as zeros
 #pragma unroll
-    for (int i = 0; i < R; i++) s.acc[i] = fma2_bf16(w[2 * i + 1], xx[2 * i + 1], fma2_bf16(w[2 * i], xx[2 * i], s.acc[i]));
+    for (int i = 0; i < R; i++) s.acc[i] = fma2_bf16(t.w[2 * i + 1], t.xx[2 * i + 1], fma2_bf16(t.w[2 * i], t.xx[2 * i], s.acc[i]));
   }
 }
+
+#ifndef OC_BATCH4
+#define OC_BATCH4 1  // tiles decoded before the first of them is finished, four rows per warp
+#endif
+#ifndef OC_BATCH2
+#define OC_BATCH2 1  // the same with two rows or one row per warp
+#endif
 
 // R: rows a warp walks side by side; NQ: quads of four tiles in flight per thread; MAXW: most
 // warps a block may have (bounds the registers). Both sides of the ring move in quads: a quad
@@ -409,7 +444,7 @@ __global__ void __launch_bounds__(MAXW * 32, 1) r4_oct_kernel(const __grid_const
   }
   OctSelf me;
   asm volatile("mov.u32 %0, 0;" : "=r"(me.ready)::"memory");  // after the barrier: orders x / table reads
-  me.lane = lane, me.to_codes = to_codes, me.lut = OC_LUT + lane * 4u;
+  me.lane = lane, me.lane_hi = lane & ~(Geo::TPR - 1), me.to_codes = to_codes, me.lut = OC_LUT + lane * 4u;
   me.gmask = (R == 1 ? 0xFFFFFFFFu : ((1u << Geo::TPR) - 1u) << (grp * Geo::TPR)), me.ltg = me.gmask & lanemask_lt();
   const uint32_t xs0 = OC_LUT + 128u + (R == 4 ? p * 16u : R == 2 ? (p >> 3) * 256u + (p & 7u) * 16u : (p >> 4) * 256u + (p & 15u) * 8u);
 
@@ -482,11 +517,25 @@ __global__ void __launch_bounds__(MAXW * 32, 1) r4_oct_kernel(const __grid_const
     const uint32_t token = cp_wait<NQ - 1>();  // all but the newest NQ - 1 groups have landed: this quad's has
     if (R == 1) __syncwarp();                  // a lane reads code words its neighbour copied
     if (cn == 4 && !partial) {
-      // four whole tiles; each slot is refilled, with a tile of the quad NQ ahead, once it is read
-      oct_step<R, 0>(s, me, at, xs, token, fq & 1u, true);
-      oct_step<R, 1>(s, me, at, xs, token, fq & 2u, true);
-      oct_step<R, 2>(s, me, at, xs, token, fq & 4u, true);
-      oct_step<R, 3>(s, me, at, xs, token, fq & 8u, true);
+      // four whole tiles, decoded a few at a time before their escapes and products, so that the
+      // table lookups of several tiles are in flight together; each slot is refilled, with a
+      // tile of the quad NQ ahead, once the quad is read
+      constexpr int B = R == 4 ? OC_BATCH4 : OC_BATCH2;
+      OctTile<R> t[B];
+      if constexpr (B == 4) {
+        oct_decode<R, 0>(t[0], me, at, xs, token), oct_decode<R, 1>(t[1], me, at, xs, token), oct_decode<R, 2>(t[2], me, at, xs, token), oct_decode<R, 3>(t[3], me, at, xs, token);
+        oct_finish<R>(s, t[0], me, fq & 1u, true), oct_finish<R>(s, t[1], me, fq & 2u, true), oct_finish<R>(s, t[2], me, fq & 4u, true), oct_finish<R>(s, t[3], me, fq & 8u, true);
+      } else if constexpr (B == 2) {
+        oct_decode<R, 0>(t[0], me, at, xs, token), oct_decode<R, 1>(t[1], me, at, xs, token);
+        oct_finish<R>(s, t[0], me, fq & 1u, true), oct_finish<R>(s, t[1], me, fq & 2u, true);
+        oct_decode<R, 2>(t[0], me, at, xs, token), oct_decode<R, 3>(t[1], me, at, xs, token);
+        oct_finish<R>(s, t[0], me, fq & 4u, true), oct_finish<R>(s, t[1], me, fq & 8u, true);
+      } else {
+        oct_decode<R, 0>(t[0], me, at, xs, token), oct_finish<R>(s, t[0], me, fq & 1u, true);
+        oct_decode<R, 1>(t[0], me, at, xs, token), oct_finish<R>(s, t[0], me, fq & 2u, true);
+        oct_decode<R, 2>(t[0], me, at, xs, token), oct_finish<R>(s, t[0], me, fq & 4u, true);
+        oct_decode<R, 3>(t[0], me, at, xs, token), oct_finish<R>(s, t[0], me, fq & 8u, true);
+      }
       if (R == 1) __syncwarp();  // the neighbour's reads too
       if (pn > 0) copy_tile<R, 0>(at, to_codes, praw, pcode, code_lane, s.acc[0]);
       if (pn > 1) copy_tile<R, 1>(at, to_codes, praw, pcode, code_lane, s.acc[0]);
@@ -495,7 +544,9 @@ __global__ void __launch_bounds__(MAXW * 32, 1) r4_oct_kernel(const __grid_const
     } else {
       for (int u = 0; u < cn; u++) {
         const bool live = !(partial && ct + u == T - 1) || p < pmax;
-        oct_step<R, 0>(s, me, at + u * SLOT, xs + u * 512u, token, (fq >> u) & 1u, live);
+        OctTile<R> t;
+        oct_decode<R, 0>(t, me, at + u * SLOT, xs + u * 512u, token);
+        oct_finish<R>(s, t, me, (fq >> u) & 1u, live);
       }
       if (R == 1) __syncwarp();
       load_quad_slow(at, pn, s.acc[0]);
