@@ -279,20 +279,29 @@ def run_ours(args) -> dict | None:
     group_k = [by_name[g[0]][1] for g in groups]
     out_names = [nm for g in groups for nm in g]
     pushed = False
+    exchanges = []
     if world > 1:
         # every rank's matrices are its row shard of a world-times taller layer: the public
-        # sharded hook multiplies locally (one launch per group) and all-gathers the slices in
-        # rank order, one collective per group, as the sharded decoder does
-        from binade_b200.cuda.dist import RowShardedGroup, make_exchange  # the library's peer-store all-gather, or NCCL
+        # sharded hook multiplies locally (one launch per group); the step's seven output slices
+        # are then gathered in rank order with ONE collective (the step evaluates the four groups
+        # on given inputs, so nothing needs a gathered vector before the step's end)
+        from binade_b200.cuda.dist import RowShardedGroup, gather_all, make_exchange  # the library's peer-store all-gather, or NCCL
 
-        stepper = [[RowShardedGroup([by_name[nm][2][c] for nm in g], [world * by_name[nm][0] for nm in g], exchange=make_exchange(max_bytes=2 * sum(by_name[nm][0] for nm in g))) for g in groups] for c in range(copies)]
-        pushed = stepper[0][0].exchange is not None
+        stepper = [[RowShardedGroup([by_name[nm][2][c] for nm in g], [world * by_name[nm][0] for nm in g]) for g in groups] for c in range(copies)]
+        exchanges = [make_exchange(max_bytes=2 * sum(by_name[nm][0] for nm in out_names) + 256) for c in range(copies)]
+        pushed = exchanges[0] is not None
+
+        def step(i: int, inputs=None):
+            inputs = inputs or xs
+            slices = [y for grp, k in zip(stepper[i % copies], group_k) for y in grp(inputs[k], gather=False)]
+            return gather_all(slices, exchange=exchanges[i % copies])
+
     else:
         stepper = [[r4.R4LinearGroup([by_name[nm][2][c] for nm in g]) for g in groups] for c in range(copies)]
 
-    def step(i: int, inputs=None):
-        inputs = inputs or xs
-        return [y for grp, k in zip(stepper[i % copies], group_k) for y in grp(inputs[k])]
+        def step(i: int, inputs=None):
+            inputs = inputs or xs
+            return [y for grp, k in zip(stepper[i % copies], group_k) for y in grp(inputs[k])]
 
     # ---- the step's own outputs: every group launch (and, with several GPUs, every gathered
     # vector on every rank) against the single-matrix products checked above
@@ -359,6 +368,9 @@ def run_ours(args) -> dict | None:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms = float(t.item())
     ms_per_step = ms / args.steps
+    for ex in exchanges:
+        if ex is not None:
+            ex.check()  # a wait that ran out on any rank voids the run
     note(f"timed region done: {ms_per_step * 1e3:.1f} us per step")
     value = world * step_bytes / (ms_per_step * 1e-3) / 1e9
 
@@ -474,7 +486,7 @@ def run_ours(args) -> dict | None:
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
         "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16 weights (R4 coded), fp32 accumulate", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "copies_rotated": copies, "bytes_per_step": step_bytes, "launches_per_step": [" + ".join(g) for g in groups], "l2": f"each step streams {step_bytes / 1e6:.0f} MB of distinct weights (> 126 MB L2), {copies} copies rotated", "timing": "CUDA-graph replays (one step per weight copy per graph), CUDA events, max over ranks", "collective": ("peer-store all-gather kernel over NVLink (bn_push_gather)" if pushed else "NCCL all-gather") + " of the projection outputs, one per group sharing an input (q k v | o | gate up | down)" if world > 1 else "none"},
+        "config": {"workload": WORKLOAD, "copies_rotated": copies, "bytes_per_step": step_bytes, "launches_per_step": [" + ".join(g) for g in groups], "l2": f"each step streams {step_bytes / 1e6:.0f} MB of distinct weights (> 126 MB L2), {copies} copies rotated", "timing": "CUDA-graph replays (one step per weight copy per graph), CUDA events, max over ranks", "collective": ("peer-store all-gather kernel over NVLink (bn_push_gather)" if pushed else "NCCL all-gather") + " of the seven projection outputs, one per step" if world > 1 else "none"},
         "pct_of_nominal_8tbs": round(100 * value / world / NOMINAL_HBM_GBS, 2),
         "bits_per_weight": {"file_format2": round(bits_file / numel, 3), "r4_in_memory": round(bits_r4 / numel, 3)},
         "parity": parity,

@@ -25,6 +25,8 @@ _SIGNATURES = {
     "cuda": {
         "bn_abi_version": [],
         "bn_device_status": [C.POINTER(_int)],
+        "bn_device_status_reset": [],
+        "bn_set_wait_limit_ns": [_u64],
         "bn_rice_ranks": [_vp, _vp, _u64, _vp, _i64, _i64, _vp, _vp, _vp],
         "bn_rice_unpack": [_vp, _vp, _u64, _vp, _vp, _vp, _i64, _i64, _vp, _vp, _vp],
         "bn_rice_to_r4": [_vp, _vp, _u64, _vp, _vp, _i64, _i64, _vp, _vp, _vp, _vp, _u64, _vp, _vp, _vp],

@@ -52,6 +52,10 @@ int direct_gather(const bn_r4 *w, const uint16_t *x, const uint32_t *xi, const u
 int mma_rows(const bn_r4 *w, const uint16_t *x, int64_t x_stride, int64_t M, int64_t N, int64_t K, uint16_t *y, int64_t y_stride, cudaStream_t s);
 int mma_status(int *status);
 int exchange_status(int *status);  // exchange.cu
+int exchange_status_reset();
+int mma_status_reset();
+int stream_status_reset();
+int oct_status_reset();
 
 inline int64_t tiles(int64_t K) { return (K + BN_TILE - 1) / BN_TILE; }
 

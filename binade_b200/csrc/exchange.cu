@@ -15,20 +15,23 @@
 // Two areas make the stores safe without a handshake: a rank that writes area q & 1 for exchange
 // q + 2 has seen every peer's done q + 1, which a peer raises only after its own exchange q (copy
 // to the output included) has finished in its stream. Readers use the local output buffer, which
-// only this rank's next exchange overwrites, after them in stream order. Every wait is bounded:
-// on giving up the kernel sets a status flag and returns (the output is then invalid, the context
-// stays usable).
+// only this rank's next exchange overwrites, after them in stream order. Every wait is bounded
+// by the GPU's nanosecond timer (two seconds unless bn_set_wait_limit_ns says otherwise): on
+// giving up the kernel sets a status flag and returns (the output is then invalid, the context
+// stays usable). The kernel may be launched before its predecessor in the stream has finished
+// (programmatic dependent launch): it reads nothing before griddepcontrol.wait.
 #include "common.cuh"
 
 namespace bn {
 
 constexpr int XCH_MAX_RANKS = 8;
 constexpr uint32_t XCH_DATA_OFFSET = 256;
-constexpr uint32_t XCH_SPIN_LIMIT = 1u << 24;
+constexpr uint64_t XCH_WAIT_NS = 2000000000ull;  // default bound of a wait on a peer's flag
 
 __device__ int g_exchange_error;
+static uint64_t g_wait_ns = XCH_WAIT_NS;  // host side: the bound handed to the next launches
 
-constexpr int XCH_MAX_SEGMENTS = 4;
+constexpr int XCH_MAX_SEGMENTS = 8;
 
 struct PushArgs {
   uint8_t *peer[XCH_MAX_RANKS];  // every rank's symmetric buffer, as mapped on this GPU
@@ -38,8 +41,15 @@ struct PushArgs {
   uint64_t area;                     // bytes of one data area
   uint8_t *out;                      // local output: one data area
   uint32_t *counter;
+  uint64_t wait_ns;  // bound of the wait on the peers' flags
   int rank, world, segments;
 };
+
+__device__ __forceinline__ uint64_t global_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
 
 __device__ __forceinline__ void st_release_sys(uint32_t *p, uint32_t v) { asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory"); }
 __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t *p) {
@@ -47,10 +57,16 @@ __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t *p) {
   asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
   return v;
 }
-// Waits until *p has reached `want` (counters only grow; the difference is taken modulo 2^32).
-__device__ __forceinline__ bool wait_reached(const uint32_t *p, uint32_t want) {
-  for (uint32_t i = 0; i < XCH_SPIN_LIMIT; i++)
-    if ((int32_t)(ld_acquire_sys(p) - want) >= 0) return true;
+// Waits until *p has reached `want` (counters only grow; the difference is taken modulo 2^32),
+// for `limit_ns` nanoseconds at most.
+__device__ __forceinline__ bool wait_reached(const uint32_t *p, uint32_t want, uint64_t limit_ns) {
+  const uint64_t t0 = global_ns();
+  for (;;) {
+#pragma unroll 1
+    for (int i = 0; i < 64; i++)
+      if ((int32_t)(ld_acquire_sys(p) - want) >= 0) return true;
+    if (global_ns() - t0 > limit_ns) break;
+  }
   atomicExch(&g_exchange_error, 1);
   return false;
 }
@@ -58,6 +74,7 @@ __device__ __forceinline__ bool wait_reached(const uint32_t *p, uint32_t want) {
 __global__ void __launch_bounds__(1024, 1) push_gather_kernel(PushArgs a) {
   __shared__ uint32_t s_seq;
   __shared__ int s_ok;
+  asm volatile("griddepcontrol.wait;" ::: "memory");  // the slices are the previous kernel's output
   if (threadIdx.x == 0) {
     s_seq = *a.counter + 1;  // launches of one exchange object are ordered by their stream
     *a.counter = s_seq;
@@ -83,7 +100,7 @@ __global__ void __launch_bounds__(1024, 1) push_gather_kernel(PushArgs a) {
   uint32_t *const mine = reinterpret_cast<uint32_t *>(a.peer[a.rank]);
   if ((int)threadIdx.x < a.world) {
     st_release_sys(reinterpret_cast<uint32_t *>(a.peer[threadIdx.x]) + a.rank, seq);  // done[rank] on peer
-    if (!wait_reached(mine + threadIdx.x, seq)) s_ok = 0;
+    if (!wait_reached(mine + threadIdx.x, seq, a.wait_ns)) s_ok = 0;
   }
   __syncthreads();
   if (!s_ok) return;
@@ -99,11 +116,17 @@ int exchange_status(int *status) {
   return BN_OK;
 }
 
+int exchange_status_reset() {
+  const int zero = 0;
+  BN_CUDA(cudaMemcpyToSymbol(g_exchange_error, &zero, sizeof(int)));
+  return BN_OK;
+}
+
 }  // namespace bn
 
 extern "C" int bn_push_gather(const void *const *locals, const uint64_t *bytes, int segments, const uint64_t *peers, uint64_t area_bytes, void *out, int rank, int world, uint32_t *counter, void *stream) {
   if (!locals || !bytes || !peers || !out || !counter || world < 1 || world > bn::XCH_MAX_RANKS || rank < 0 || rank >= world || segments < 1 || segments > bn::XCH_MAX_SEGMENTS)
-    return bn::fail(BN_ERR_ARG, "bn_push_gather: bad rank, world (1..8), segment count (1..4) or null pointer");
+    return bn::fail(BN_ERR_ARG, "bn_push_gather: bad rank, world (1..8), segment count (1..8) or null pointer");
   bn::PushArgs a{};
   uint64_t base = 0;
   for (int g = 0; g < segments; g++) {
@@ -117,6 +140,18 @@ extern "C" int bn_push_gather(const void *const *locals, const uint64_t *bytes, 
     a.peer[r] = reinterpret_cast<uint8_t *>(peers[r]);
   }
   a.area = area_bytes, a.out = static_cast<uint8_t *>(out), a.counter = counter, a.rank = rank, a.world = world, a.segments = segments;
-  bn::push_gather_kernel<<<1, 1024, 0, (cudaStream_t)stream>>>(a);
+  a.wait_ns = bn::g_wait_ns;
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(1), cfg.blockDim = dim3(1024), cfg.stream = (cudaStream_t)stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;  // its launch overlaps the tail of the kernel that produces the slices
+  cfg.attrs = attr, cfg.numAttrs = 1;
+  BN_CUDA(cudaLaunchKernelEx(&cfg, bn::push_gather_kernel, a));
   return bn::launched("push_gather_kernel");
+}
+
+extern "C" int bn_set_wait_limit_ns(uint64_t ns) {
+  bn::g_wait_ns = ns ? ns : bn::XCH_WAIT_NS;
+  return BN_OK;
 }

@@ -345,6 +345,12 @@ int mma_rows(const bn_r4 *w, const uint16_t *x, int64_t x_stride, int64_t M, int
   return -1;
 }
 
+int mma_status_reset() {
+  const int zero = 0;
+  BN_CUDA(cudaMemcpyToSymbol(g_mma_error, &zero, sizeof(int)));
+  return BN_OK;
+}
+
 int mma_status(int *status) {
   BN_CUDA(cudaMemcpyFromSymbol(status, g_mma_error, sizeof(int)));
   return BN_OK;

@@ -611,6 +611,12 @@ int oct_status(int *status) {
   return BN_OK;
 }
 
+int oct_status_reset() {
+  const int zero = 0;
+  BN_CUDA(cudaMemcpyToSymbol(g_oct_error, &zero, sizeof(int)));
+  return BN_OK;
+}
+
 // Launch shape: one block per SM (per slot share of the SMs for a gather), dealt out to the
 // matrices in proportion to their rows; as many warps as spread a matrix's row groups evenly over
 // its blocks; deeper rings when the warps are few, since then they are all the memory

@@ -624,7 +624,20 @@ int stream_rows(const bn_r4 *w, const uint16_t *x, int64_t x_stride, int64_t M, 
   return stream_rows_m<8>(a, s);
 }
 
+int stream_status_reset() {
+  const int zero = 0;
+  BN_CUDA(cudaMemcpyToSymbol(g_stream_error, &zero, sizeof(int)));
+  return BN_OK;
+}
+
 }  // namespace bn
+
+extern "C" int bn_device_status_reset(void) {
+  if (int e = bn::stream_status_reset()) return e;
+  if (int e = bn::oct_status_reset()) return e;
+  if (int e = bn::mma_status_reset()) return e;
+  return bn::exchange_status_reset();
+}
 
 extern "C" int bn_device_status(int *status) {
   if (!status) return bn::fail(BN_ERR_ARG, "bn_device_status: null pointer");

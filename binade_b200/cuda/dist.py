@@ -10,6 +10,7 @@ reference is single-device; this module is the multi-GPU form of its linear-laye
   RowShardedLinear(local, N, ...)  y = all_gather(local(x)) over the process group
   RowShardedGroup(locals, Ns, ...) several projections of the same input (q, k, v; gate, up)
                                    with one all-gather for all of them
+  gather_all(slices, ...)          one collective for the slices of several groups
 
   make_exchange(group, max_bytes)  a PushGather, or None when the ranks should stay on NCCL
   PushGather(group, max_bytes)     the all-gather as one kernel of this library over NVLink peer
@@ -94,7 +95,14 @@ class PushGather:
     Results are views of this object's output buffer: the next call on the same object overwrites
     them (after this rank's readers, in stream order), so a result must be consumed or copied
     before the object is used again. Safe to capture in a
-    CUDA graph (the call number lives in device memory)."""
+    CUDA graph (the call number lives in device memory).
+
+    A peer that never arrives does not hang the GPU: the kernel's wait is bounded (two seconds
+    by default), after which it sets the device status and returns with the output incomplete.
+    The kernel cannot tell the host by itself, so call `check()` wherever the host synchronises
+    anyway (the end of a generation, after a batch of graph replays): it raises, on every rank,
+    if any rank gave up, and retires the object (`gather_rows` then returns None and callers fall
+    back to the library collective)."""
 
     HEADER = 256
 
@@ -117,11 +125,31 @@ class PushGather:
         self.handle = symm_mem.rendezvous(self.buf, group)
         self.peers = (ctypes.c_uint64 * self.world)(*[int(p) for p in self.handle.buffer_ptrs])
         self.counter = torch.zeros(1, dtype=torch.int32, device=dev)
+        self.group, self.dead = group, False
         torch.cuda.synchronize()
         dist.barrier(group)  # every buffer is zeroed before anyone's first flag arrives
 
+    def check(self) -> None:
+        """Raises RuntimeError on every rank if a kernel of this library gave up a wait on any
+        rank since the last check (synchronises the device and the group). The object is then
+        retired: after a lost exchange the ranks' call numbers may differ."""
+        import ctypes
+
+        import torch.distributed as dist
+
+        from .. import _native
+
+        st = ctypes.c_int(0)
+        _native.call("cuda", "bn_device_status", ctypes.byref(st))
+        flag = torch.tensor([st.value], device=self.out.device, dtype=torch.int32)
+        dist.all_reduce(flag, op=dist.ReduceOp.MAX, group=self.group)
+        if int(flag.item()):
+            self.dead = True
+            _native.call("cuda", "bn_device_status_reset")
+            raise RuntimeError(f"a bounded wait of the peer-store exchange ran out (device status {int(flag.item()):#x} on some rank): the gathered data is incomplete; this exchange is retired")
+
     def _push(self, pieces):
-        """One exchange of 1..4 contiguous device tensors (16-byte aligned, sizes a multiple of
+        """One exchange of 1..8 contiguous device tensors (16-byte aligned, sizes a multiple of
         16 bytes): returns, per piece, the uint8 view [world, bytes] of the gathered slices."""
         import ctypes
 
@@ -145,15 +173,18 @@ class PushGather:
         return t.is_contiguous() and t.data_ptr() % 16 == 0 and (t.numel() * t.element_size()) % 16 == 0 and t.numel() > 0
 
     def gather_rows(self, ys):
-        """Single-row slices ys[j] [.., w_j] (one row each) of 1..4 projections -> their full
+        """Single-row slices ys[j] [.., w_j] (one row each) of 1..8 projections -> their full
         rows [.., world * w_j], written by the kernel in their final layout: the results are
         views of this rank's buffer, no copy before or after. None if a slice cannot be pushed
-        as it is (several rows, unaligned or odd size): the caller then takes __call__."""
-        if not 1 <= len(ys) <= 4 or any(y.numel() != y.shape[-1] or not self._pushable(y) for y in ys):
+        as it is (several rows, unaligned or odd size) or the object is retired: the caller then
+        takes another route."""
+        if self.dead or not 1 <= len(ys) <= 8 or any(y.numel() != y.shape[-1] or not self._pushable(y) for y in ys):
             return None
         return [g.view(y.dtype).reshape(*y.shape[:-1], self.world * y.shape[-1]) for g, y in zip(self._push(list(ys)), ys)]
 
     def __call__(self, flat: torch.Tensor) -> torch.Tensor:
+        if self.dead:
+            raise RuntimeError("this exchange was retired after a lost wait")
         flat = flat.contiguous()
         nbytes = flat.numel() * flat.element_size()
         padded = (nbytes + 15) // 16 * 16
@@ -190,6 +221,30 @@ def make_exchange(group=None, max_bytes: int = 1 << 20):
     flag = torch.tensor([ok], device="cuda", dtype=torch.int32)
     dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=group)
     return ex if int(flag.item()) == 1 else None
+
+
+def gather_all(slices, group=None, exchange=None):
+    """One collective for up to eight single-row slices [.., w_j] of evenly sharded projections:
+    returns their full rows [.., world * w_j] in rank order = row order. Through the peer-store
+    kernel when an exchange is given and the slices can be pushed as they are, else one library
+    all-gather of the slices laid side by side."""
+    import torch.distributed as dist
+
+    world = dist.get_world_size(group)
+    if world == 1:
+        return list(slices)
+    if exchange is not None:
+        fast = exchange.gather_rows(list(slices))
+        if fast is not None:
+            return fast
+    widths = [y.shape[-1] for y in slices]
+    flat = torch.cat([y.reshape(1, -1) for y in slices], dim=-1)
+    out = _all_gather(flat, world, group, None)  # [world, 1, sum of widths]
+    res, c = [], 0
+    for y, w in zip(slices, widths):
+        res.append(out[:, :, c : c + w].movedim(0, 1).reshape(*y.shape[:-1], world * w))
+        c += w
+    return res
 
 
 def _all_gather(flat: torch.Tensor, world: int, group, exchange) -> torch.Tensor:
@@ -249,7 +304,10 @@ class RowShardedGroup(nn.Module):
     hook (q, k and v share their input, so do gate and up): the small-message latency of the
     collective is paid once per group instead of once per projection. Every N must divide evenly
     over the ranks. forward(x) returns the list of full outputs, bit-identical to what
-    RowShardedLinear gives for each projection alone."""
+    RowShardedLinear gives for each projection alone. forward(x, gather=False) returns the local
+    slices only: a caller with several groups whose outputs are not needed in between (a layer
+    that evaluates q k v, o, gate up, down on given inputs) gathers them all with one collective
+    (`gather_all`), paying the small-message latency once."""
 
     def __init__(self, locals_, Ns, group=None, exchange=None):
         super().__init__()
@@ -263,12 +321,12 @@ class RowShardedGroup(nn.Module):
         # R4 projections of one input run as one launch
         self._fused = r4.R4LinearGroup(locals_) if 1 <= len(locals_) <= 4 and all(isinstance(m, r4.R4Linear) for m in locals_) else None
 
-    def forward(self, x: torch.Tensor):
+    def forward(self, x: torch.Tensor, gather: bool = True):
         import torch.distributed as dist
 
         world = dist.get_world_size(self.group)
         ys = self._fused(x) if self._fused is not None else [m(x) for m in self.locals]
-        if world == 1:
+        if world == 1 or not gather:
             return ys
         widths = [N // world for N in self.Ns]
         for y, w, N in zip(ys, widths, self.Ns):

@@ -170,7 +170,7 @@ class Decoder(nn.Module):
         """All-gather a local slice [.., n_total / world] into the full vector (row order)."""
         if self.world == 1:
             return y
-        if self.exchange is not None:
+        if self.exchange is not None and not self.exchange.dead:
             fast = self.exchange.gather_rows([y.reshape(1, -1)])
             return fast[0] if fast is not None else self.exchange(y.reshape(1, -1)).reshape(1, n_total)
         import torch.distributed as dist
@@ -253,4 +253,6 @@ class Decoder(nn.Module):
             run()
         e1.record()
         torch.cuda.synchronize()
+        if self.exchange is not None:
+            self.exchange.check()  # a peer that never arrived: raise instead of returning tokens from stale vectors
         return out, e0.elapsed_time(e1) / 1e3

@@ -223,8 +223,10 @@ int bn_r4_gather_grouped(const uint16_t *x, const bn_r4 *w, const uint32_t *xi, 
  * rank's own device memory; `counter` is a zeroed uint32 in this rank's device memory that
  * belongs to this set of buffers. After the call, in stream order, segment g starts at byte
  * world * (bytes[0] + .. + bytes[g-1]) of `out` and holds the world slices of that segment in
- * rank order. Ranks must make the same sequence of calls; world <= 8. Plain peer stores and
- * flags only (no TMA, no multicast); every wait is bounded. */
+ * rank order. Ranks must make the same sequence of calls; world <= 8; 1..8 segments. Plain peer
+ * stores and flags only (no TMA, no multicast). The wait for the peers' flags is bounded by the
+ * GPU's nanosecond timer (two seconds, or what bn_set_wait_limit_ns set): a rank whose peer never
+ * arrives sets the device status (bits 16..23) and returns with `out` incomplete. */
 int bn_push_gather(const void *const *locals, const uint64_t *bytes, int segments,
                    const uint64_t *peers, uint64_t area_bytes, void *out, int rank, int world,
                    uint32_t *counter, void *stream);
@@ -235,6 +237,13 @@ int bn_push_gather(const void *const *locals, const uint64_t *bytes, int segment
  * kernels is bounded, so a lost copy or an absent peer ends in this status instead of a hang.
  * Synchronises with the device. No counterpart in the reference. */
 int bn_device_status(int *status);
+
+/* Clears the device status of the current device (after a caller has handled a failure). */
+int bn_device_status_reset(void);
+
+/* Bound, in nanoseconds, of every later wait on a peer's flag (bn_push_gather); 0 restores the
+ * default of two seconds. Process-wide. No counterpart in the reference. */
+int bn_set_wait_limit_ns(uint64_t ns);
 
 /* ------------------------------------------------------------------ 3. host codec --------- */
 

@@ -131,6 +131,12 @@ def _group_main(rank: int, world: int, port: int, out_dir: str):
     ys = g(torch.from_numpy(x.view(np.int16)).view(torch.bfloat16))
     for i, y in enumerate(ys):
         np.save(os.path.join(out_dir, f"g{rank}_{i}.npy"), y.view(torch.int16).numpy().view(np.uint16))
+    # the deferred form: local slices of a one-row input, gathered by one collective
+    x1 = torch.from_numpy(x[:1].view(np.int16)).view(torch.bfloat16)
+    late = bd.gather_all(g(x1, gather=False))
+    same = all(torch.equal(a.view(torch.int16), b.view(torch.int16)) for a, b in zip(late, g(x1)))
+    with open(os.path.join(out_dir, f"late{rank}"), "w") as f:
+        f.write("1" if same and len(late) == len(Ns) else "0")
     dist.destroy_process_group()
 
 
@@ -144,6 +150,7 @@ def test_row_sharded_group_two_gloo_ranks(tmp_path):
         want = o.c_dense_rows(x, _weights((N, 128), seed=20 + i))
         for rank in range(world):
             assert np.array_equal(np.load(tmp_path / f"g{rank}_{i}.npy"), want), (rank, i)
+    assert [(tmp_path / f"late{r}").read_text() for r in range(world)] == ["1", "1"]  # gather_all of the local slices
 
 
 def _ep_main(rank: int, world: int, port: int, out_dir: str):

@@ -36,6 +36,18 @@ def _rank_main(rank: int, world: int, port: int, N: int, K: int, out_dir: str):
     y2 = bd.RowShardedLinear(cut, N)(x)
     full = r4.R4Linear(r4.transcode(p))(x)
     ok = torch.equal(y.view(torch.int16), full.view(torch.int16)) and torch.equal(y2.view(torch.int16), full.view(torch.int16))
+    # two projections of one input as a group (one launch, one exchange), and the deferred form:
+    # local slices of two groups gathered by one collective, through the peer-store kernel and NCCL
+    if N % world == 0:
+        ex = bd.make_exchange(max_bytes=8 * N)
+        for exchange in (ex, None):
+            grp = bd.RowShardedGroup([local, cut], [N, N], exchange=exchange)
+            a, b = grp(x)
+            ok = ok and torch.equal(a.view(torch.int16), full.view(torch.int16)) and torch.equal(b.view(torch.int16), full.view(torch.int16))
+            both = bd.gather_all(grp(x, gather=False) + grp(x, gather=False), exchange=exchange)
+            ok = ok and len(both) == 4 and all(torch.equal(t.view(torch.int16), full.view(torch.int16)) for t in both)
+        if ex is not None:
+            ex.check()
     with open(os.path.join(out_dir, f"ok{rank}"), "w") as f:
         f.write("1" if ok else "0")
     dist.barrier()
