@@ -475,6 +475,9 @@ def run_ours(args) -> dict | None:
         note("prefill and MoE legs done")
         config1 = config1_leg(torch)
         note("configuration 1 done")
+    elif world > 1 and not args.quick and 128 % world == 0:
+        moe_leg = moe_parallel_leg(torch, dist, dev, rank, world)
+        note("expert-parallel MoE leg done")
     if rank != 0:
         return None
 
@@ -616,6 +619,56 @@ def moe_path_leg(torch, dev, graph_us) -> dict:
         active = int(torch.unique(idx).numel())
         grouped = B * 8 >= layer.GROUP_MIN_SLOTS * E  # slots grouped by expert: every active expert is read once
         out[str(B)] = {"us": round(us, 1), "slots": B * 8, "active_experts": active, "path": "grouped by expert" if grouped else "slot by slot", "gbs_of_slot_bytes": round(B * 8 * per_expert / us / 1e3, 1), "gbs_of_distinct_expert_bytes": round(active * per_expert / us / 1e3, 1), "checked": "gathers and layer output bit-identical to the oracle"}
+    return out
+
+
+def moe_parallel_leg(torch, dist, dev, rank: int, world: int) -> dict:
+    """The same expert layer with its 128 experts and the token batch split over the ranks:
+    ExpertParallelGLU (all-to-all dispatch of the slots' input rows to the ranks owning their
+    experts, the local expert path, all-to-all combine). Every rank checks its tokens' outputs
+    bit for bit against the whole layer on its own GPU, then the forward is timed eagerly with
+    CUDA events (max over ranks). Batches of 1 / 8 / 64 tokens in all; a rank without a real
+    token brings a padding token."""
+    from binade_b200.cuda import moe, r4
+
+    E, n, D, k = 128, 704, 2816, 8
+    per = E // world
+    g = torch.Generator(device=dev).manual_seed(5)
+    gu = (torch.randn((E, 2 * n, D), device=dev, generator=g) * 0.02).to(torch.bfloat16)
+    dn = (torch.randn((E, D, n), device=dev, generator=g) * 0.02).to(torch.bfloat16)
+    whole = moe.R4SwitchGLU(r4.R4Linear(r4.from_dense(gu)), r4.R4Linear(r4.from_dense(dn)))
+    local = moe.R4SwitchGLU(r4.R4Linear(r4.from_dense(gu[rank * per : (rank + 1) * per].contiguous())), r4.R4Linear(r4.from_dense(dn[rank * per : (rank + 1) * per].contiguous())))
+    del gu, dn
+    ep = moe.ExpertParallelGLU(local.slots, E, D, rank, world)
+    out = {}
+    for B in (1, 8, 64):
+        each = -(-B // world)
+        x = torch.randn((each * world, D), device=dev, generator=g).to(torch.bfloat16)
+        idx = torch.topk(torch.softmax(torch.rand((each * world, E), device=dev, generator=g), dim=-1), k, dim=-1).indices
+        idx[B:] = -1  # padding tokens
+        mine = slice(rank * each, (rank + 1) * each)
+        y = ep(x[mine], idx[mine])
+        want = whole(x[mine], idx[mine].clamp(min=0))
+        want[idx[mine] < 0] = 0
+        if not torch.equal(y.view(torch.int16), want.view(torch.int16)):
+            raise SystemExit(f"bench: expert-parallel output differs from the single-GPU layer at {B} tokens (rank {rank})")
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        for _ in range(3):
+            ep(x[mine], idx[mine])
+        dist.barrier()
+        e0.record()
+        for _ in range(20):
+            ep(x[mine], idx[mine])
+        e1.record()
+        torch.cuda.synchronize()
+        t = torch.tensor([e0.elapsed_time(e1) * 1e3 / 20], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e0.record()
+        for _ in range(20):
+            whole(x[:B], idx[:B])
+        e1.record()
+        torch.cuda.synchronize()
+        out[str(B)] = {"us": round(float(t.item()), 1), "single_gpu_layer_us_eager": round(e0.elapsed_time(e1) * 1e3 / 20, 1), "tokens_per_rank": each, "experts_per_rank": per, "checked": "bit-identical to the single-GPU layer on every rank", "timing": "eager launches (torch glue + 2 all-to-all + 2 gather kernels), CUDA events, max over ranks"}
     return out
 
 

@@ -222,6 +222,7 @@ __global__ void __launch_bounds__(WARPS * 32, 1) r4_direct_kernel(DirectArgs a) 
   const uint32_t x_at = (base + 15u) & ~15u;
   if (base > DR_BASE_MAX || x_at + (uint32_t)T * 256u > 65536u || a.smem < 131072u - base) return;  // the host checked the same layout
   const int64_t slot = blockIdx.y;
+  if (a.ei && a.ei[slot] == BN_NO_EXPERT) return;  // a padding slot
   const int64_t row0 = a.ei ? (int64_t)a.ei[slot] * a.RS + a.R0 : 0;  // storage row of output row 0
   {
     const uint4 *x8 = reinterpret_cast<const uint4 *>(a.x + (a.ei ? (int64_t)a.xi[slot] * K : 0));

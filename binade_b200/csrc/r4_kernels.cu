@@ -94,6 +94,7 @@ __global__ void __launch_bounds__(MV_THREADS) r4_rows_kernel(RowsArgs a) {
   int64_t g = 0;
   if (GATHER) {
     g = blockIdx.y;
+    if (a.ei[g] == BN_NO_EXPERT) return;  // a padding slot
     row0 = (int64_t)a.ei[g] * a.RS + a.R0;
     x = a.x + (int64_t)a.xi[g] * a.x_stride;
   }

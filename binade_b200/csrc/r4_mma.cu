@@ -309,8 +309,7 @@ int mma_rows(const bn_r4 *w, const uint16_t *x, int64_t x_stride, int64_t M, int
   a.tmem_cols = 32;
   while ((int)a.tmem_cols < a.BN) a.tmem_cols *= 2;
   // an equal share of the rows for every SM, in whole warps' worth of rows
-  int dw = MMA_DECODE_WARPS, rpw = MMA_RPW;
-  if (const char *e = getenv("BINADE_B200_MMA_SHAPE")) sscanf(e, "%dx%d", &dw, &rpw);  // experiments only
+  constexpr int dw = MMA_DECODE_WARPS, rpw = MMA_RPW;
   int64_t rows = (N + mma_sms() - 1) / mma_sms();
   rows = (rows + rpw - 1) / rpw * rpw;
   if (rows > dw * rpw) rows = dw * rpw;
@@ -330,19 +329,9 @@ int mma_rows(const bn_r4 *w, const uint16_t *x, int64_t x_stride, int64_t M, int
     return fail(BN_ERR_CUDA, "cuTensorMapEncodeTiled failed for the input rows");
   const uint32_t smem = fixed + (uint32_t)stages * per_stage;
   const unsigned grid = (unsigned)((N + rows - 1) / rows);
-#define BN_MMA_LAUNCH(DW, RPW)                                                        \
-  if (dw == DW && rpw == RPW) {                                                       \
-    BN_CUDA(allow_smem(r4_mma_kernel<DW, RPW>, smem));                                \
-    r4_mma_kernel<DW, RPW><<<grid, (DW + 1) * 32, smem, s>>>(x_map, a);               \
-    return launched("r4_mma_kernel");                                                 \
-  }
-  BN_MMA_LAUNCH(28, 4)
-  BN_MMA_LAUNCH(24, 5)
-  BN_MMA_LAUNCH(20, 6)
-  BN_MMA_LAUNCH(16, 7)
-  BN_MMA_LAUNCH(14, 8)
-#undef BN_MMA_LAUNCH
-  return -1;
+  BN_CUDA(allow_smem(r4_mma_kernel<dw, rpw>, smem));
+  r4_mma_kernel<dw, rpw><<<grid, (dw + 1) * 32, smem, s>>>(x_map, a);
+  return launched("r4_mma_kernel");
 }
 
 int mma_status_reset() {

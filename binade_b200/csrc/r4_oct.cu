@@ -353,6 +353,7 @@ __global__ void __launch_bounds__(MAXW * 32, 1) r4_oct_kernel(const __grid_const
   const uint32_t G = a.groups[mi];
   const int64_t slot = blockIdx.y;
   const uint32_t nwarps = (a.bend[mi] - b0) * W, gw = (blockIdx.x - b0) * W + warp;
+  if (a.ei && a.ei[slot] == BN_NO_EXPERT) return;  // a padding slot: nothing to compute, nothing stored
   const int64_t row0 = a.ei ? (int64_t)a.ei[slot] * a.RS + a.R0 : 0;  // storage row of output row 0
   const bool partial = (K & 127) != 0;                    // the last tile of a row is short
   const uint32_t pmax = (uint32_t)(K & 127) / (4u * R);   // threads that hold weights in it

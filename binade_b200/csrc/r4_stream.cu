@@ -303,6 +303,7 @@ __global__ void __launch_bounds__(WARPS * 32, 1) r4_stream_kernel(StreamArgs a) 
     o_begin = a.N * (int64_t)me / workers, o_end = a.N * (int64_t)(me + 1u) / workers;
   }
   const int64_t slot = blockIdx.y;
+  if (!a.seg && a.ei && a.ei[slot] == BN_NO_EXPERT) return;  // a padding slot (whole block, before any barrier is armed)
   // grouped gather: this block's expert, its first slot in `order` and how many slots it takes
   int64_t g_first = 0;
   int g_count = a.m;

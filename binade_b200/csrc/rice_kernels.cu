@@ -7,6 +7,8 @@
 //   unary planes  j = 0 .. qmax-1: one bit per weight still alive (q >= j), set iff q > j
 // The bit offset of a lane inside a plane is the number of alive weights before it: a warp
 // prefix sum over per-lane alive counts, done with three ballots.
+#include <atomic>
+
 #include "common.cuh"
 
 namespace bn {
@@ -471,19 +473,23 @@ __global__ void __launch_bounds__(256) compact_esc_static_kernel(const uint32_t 
   }
 }
 
-// The scratch array's device address on the current device, looked up once per device.
+// The scratch array's device address on the current device, looked up once per device. The cache
+// is atomic: two host threads making their first call together both look the address up and
+// store the same value. It does not outlive cudaDeviceReset (the address belongs to the context).
 static int static_scratch(unsigned char **out) {
-  static unsigned char *ptr[64] = {nullptr};
+  static std::atomic<unsigned char *> ptr[64];
   int dev = 0;
   BN_CUDA(cudaGetDevice(&dev));
   if (dev < 0 || dev >= 64) return fail(BN_ERR_ARG, "bn_rice_to_r4_static: device index out of range");
-  if (!ptr[dev]) {
+  unsigned char *known = ptr[dev].load(std::memory_order_acquire);
+  if (!known) {
     // g_static_scratch names the array on the host side only; kernels need its device address
     void *p = nullptr;
     BN_CUDA(cudaGetSymbolAddress(&p, g_static_scratch));
-    ptr[dev] = static_cast<unsigned char *>(p);
+    known = static_cast<unsigned char *>(p);
+    ptr[dev].store(known, std::memory_order_release);
   }
-  *out = ptr[dev];
+  *out = known;
   return BN_OK;
 }
 
@@ -494,7 +500,7 @@ extern "C" int bn_rice_to_r4_static(const uint8_t *meta, const uint32_t *bits, u
   if (int e = check_stream(meta, bits, roff, R, K)) return e;
   if (!table || !codes || !flags || !row_esc || !esc || !info || esc_cap < 1) return fail(BN_ERR_ARG, "bn_rice_to_r4_static: null pointer or empty esc");
   if (K % 4) return fail(BN_ERR_ARG, "R4 needs K % 4 == 0");
-  if (R > STATIC_MAX_ROWS || R * K > STATIC_MAX_WEIGHTS) return fail(BN_ERR_CAPACITY, "bn_rice_to_r4_static: at most 65536 rows and 16 Mi weights per call (expand larger tensors in row chunks, or use bn_rice_to_r4 with caller scratch)");
+  if (R > STATIC_MAX_ROWS || K > STATIC_MAX_WEIGHTS / (R > 0 ? R : 1)) return fail(BN_ERR_CAPACITY, "bn_rice_to_r4_static: at most 65536 rows and 16 Mi weights per call (expand larger tensors in row chunks, or use bn_rice_to_r4 with caller scratch)");
   unsigned char *scratch = nullptr;
   if (int e = static_scratch(&scratch)) return e;
   cudaStream_t s = (cudaStream_t)stream;

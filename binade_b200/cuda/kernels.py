@@ -17,6 +17,7 @@ from .. import _native
 from ..format import TILE
 
 R4_KEYS = ("raw", "codes", "flags", "esc", "table", "row_esc")
+NO_EXPERT = -1  # BN_NO_EXPERT (0xFFFFFFFF) in an int32 tensor: the expert id of a padding slot
 
 
 def require_cuda() -> torch.device:
@@ -212,13 +213,15 @@ def r4_gather_grouped(a: dict, x: torch.Tensor, xi: torch.Tensor, ei: torch.Tens
     """r4_gather's outputs with every expert's rows read once for all its slots: the slots are
     sorted by expert on the device (no host sync) and each expert multiplies up to 8 input rows
     per pass. ei: int32 [G] expert of each slot (0 <= ei < E); max_per_expert bounds the slots of
-    one expert (the token count when a token names an expert at most once). K % 16 == 0."""
+    one expert (the token count when a token names an expert at most once). K % 16 == 0.
+    Slots whose expert id is NO_EXPERT (padding) sort behind every expert and are skipped."""
     G = ei.numel()
     dev = x.device
-    order = torch.argsort(ei, stable=True).to(torch.int32)
-    counts = torch.zeros(E, dtype=torch.int32, device=dev).scatter_add_(0, ei.to(torch.int64), torch.ones(G, dtype=torch.int32, device=dev))  # (bincount would synchronise)
+    bucket = torch.clamp(ei.to(torch.int64) & 0xFFFFFFFF, max=E)  # padding slots: one bucket past the experts
+    order = torch.argsort(bucket, stable=True).to(torch.int32)
+    counts = torch.zeros(E + 1, dtype=torch.int32, device=dev).scatter_add_(0, bucket, torch.ones(G, dtype=torch.int32, device=dev))  # (bincount would synchronise)
     seg = torch.zeros(E + 1, dtype=torch.int32, device=dev)
-    seg[1:] = torch.cumsum(counts, 0).to(torch.int32)
+    seg[1:] = torch.cumsum(counts[:E], 0).to(torch.int32)
     if split:
         y = torch.empty((G, split), dtype=torch.bfloat16, device=dev)
         y2 = torch.empty((G, n - split), dtype=torch.bfloat16, device=dev)

@@ -7,9 +7,11 @@ inside the kernel by `ei[g] * rows_per_expert`.
   R4SwitchGLU(gate_up, down, activation)   y[.., k, D] = down_e(act(up_e x, gate_e x)) for the k
                                            experts `indices[.., k]` of every token, one fused
                                            gather launch for gate+up and one for down
-  ExpertParallelGLU(local, E, rank, world)  experts spread over the ranks of a process group:
-                                           every rank runs the slots whose expert it owns and
-                                           the slot outputs travel back with one all-to-all
+  BinadeSwitchGLU(gate_up, down)           holder of the packed stacks until r4.convert
+  ExpertParallelGLU(local, E, rank, world)  experts and tokens spread over the ranks of a process
+                                           group: an all-to-all brings every slot's input row
+                                           to the rank that owns its expert, a second one
+                                           takes the outputs back
 
 Router softmax / top-k and the weighted sum over the k experts stay with the caller, as in the
 reference (mlx-lm's SwitchGLU contract).
@@ -68,15 +70,39 @@ class R4SwitchGLU(nn.Module):
         return self.slots(flat, xi, ei).reshape(*indices.shape, self.D)
 
 
+class BinadeSwitchGLU(nn.Module):
+    """Holder of one layer's packed expert stacks until `r4.convert` swaps it for an R4SwitchGLU
+    (reference: BinadeSwitchGLU, binade/mlx/moe.py:29-52). gate_up_proj / down_proj: dicts of
+    file arrays {raw, table, meta, bits, roff} (or format 1), raw shaped [E, 2n, D] and
+    [E, D, n]. It cannot run."""
+
+    def __init__(self, gate_up_proj: dict, down_proj: dict, activation=swiglu):
+        super().__init__()
+        self.gate_up_proj, self.down_proj, self._activation = gate_up_proj, down_proj, activation
+
+    def forward(self, x, indices):
+        raise RuntimeError("packed experts run on the R4 runtime: call binade_b200.cuda.r4.convert(model)")
+
+
 class ExpertParallelGLU(nn.Module):
-    """Experts partitioned over ranks: rank r owns experts [r * E/world, (r+1) * E/world). Every
-    rank sees the same tokens and indices (as in tensor-parallel decoding) and computes only the
-    slots whose expert it owns, with `local_slots(x, xi, ei_local) -> [G_local, D]` (the `.slots`
-    of an R4SwitchGLU over its own experts). Every rank needs every slot's output, so each rank
-    sends the slots it computed to all ranks in one all-to-all of fixed-capacity buffers (capacity
-    = the number of slots: no count exchange, no host sync) and scatters what it receives to the
-    slots' positions. A slot is computed by exactly one rank, so the result does not depend on the
-    number of ranks."""
+    """Experts partitioned over the ranks of a process group, tokens too: rank r owns experts
+    [r * E/world, (r + 1) * E/world) and brings its own share of the batch. One forward is a
+    dispatch, the local expert path, and a combine:
+
+      dispatch  every (token, expert) slot of this rank's tokens travels to the rank that owns
+                its expert: one all-to-all of fixed-size chunks. A chunk holds `cap` input rows
+                (cap = this rank's slot count, the most one peer can get from it) followed by
+                the slots' local expert ids, padding slots marked NO_EXPERT, so the input rows
+                and their ids share one collective and no count crosses the host.
+      compute   `local_slots(x_rows, xi, ei_local) -> [slots, D]` on what arrived (the `.slots`
+                of an R4SwitchGLU over this rank's experts); padding slots are skipped inside
+                the kernels, so a rank streams only the experts really routed to it.
+      combine   the slot outputs go back the way they came (one all-to-all) and are put in their
+                slots' places.
+
+    Every rank must bring the same number of tokens (pad with tokens routed to NO_EXPERT slots
+    if need be: indices < 0). A slot is computed by exactly one rank with the single-GPU kernels,
+    so outputs are bit-identical to R4SwitchGLU on one GPU."""
 
     def __init__(self, local_slots, E: int, D: int, rank: int, world: int, group=None):
         super().__init__()
@@ -86,34 +112,50 @@ class ExpertParallelGLU(nn.Module):
         self.per = E // world
 
     def forward(self, x: torch.Tensor, indices: torch.Tensor) -> torch.Tensor:
+        """x [tokens, D] and indices [tokens, k] of this rank's tokens -> [tokens, k, D]."""
         import torch.distributed as dist
 
-        k = indices.shape[-1]
-        flat = x.reshape(-1, x.shape[-1])
+        from .kernels import NO_EXPERT
+
+        k, D, W = indices.shape[-1], self.D, self.world
+        flat = x.reshape(-1, D)
         ei = indices.reshape(-1).to(torch.int64)
-        G = ei.numel()
-        xi = torch.arange(G, dtype=torch.int32, device=x.device) // k
-        owner = ei // self.per
-        mine = owner == self.rank
-        # this rank's slots first (stable order), padded with slot 0 of expert 0: fixed shapes
-        order = torch.argsort((~mine).to(torch.int8), stable=True)
-        n_mine = mine.sum()
-        sel_ei = torch.where(torch.arange(G, device=x.device) < n_mine, ei[order] - self.rank * self.per, torch.zeros_like(ei)).to(torch.int32)
-        out = self.local_slots(flat, xi[order], sel_ei)  # [G, D]; rows >= n_mine are padding
-        if self.world == 1:
-            y = torch.empty_like(out)
-            y[order] = out
-            return y.reshape(*indices.shape, self.D)
-        # all-to-all: every rank sends (its slot outputs, their slot numbers, its count) to everyone
-        send = out[None].expand(self.world, G, self.D).contiguous()
-        recv = torch.empty_like(send)
-        dist.all_to_all_single(recv.view(self.world * G, self.D), send.view(self.world * G, self.D), group=self.group)
-        meta_send = torch.cat([order.to(torch.int64), n_mine.reshape(1).to(torch.int64)])[None].expand(self.world, G + 1).contiguous()
-        meta_recv = torch.empty_like(meta_send)
-        dist.all_to_all_single(meta_recv.view(-1), meta_send.view(-1), group=self.group)
-        y = torch.zeros((G + 1, self.D), dtype=out.dtype, device=out.device)  # row G swallows padding
-        for r in range(self.world):
-            pos, cnt = meta_recv[r, :G], meta_recv[r, G]
-            dst = torch.where(torch.arange(G, device=x.device) < cnt, pos, torch.full_like(pos, G))
-            y.index_copy_(0, dst, recv[r])
-        return y[:G].reshape(*indices.shape, self.D)
+        S = ei.numel()  # this rank's slots; also the capacity of a chunk
+        dev = x.device
+        xi = torch.arange(S, device=dev) // k
+        real = ei >= 0
+        owner = torch.where(real, ei // self.per, torch.full_like(ei, W))  # padding tokens: no owner
+        # place of each slot in its owner's chunk: its rank among this rank's slots of that owner
+        order = torch.argsort(owner, stable=True)
+        counts = torch.zeros(W + 1, dtype=torch.int64, device=dev).scatter_add_(0, owner, torch.ones_like(owner))
+        start = torch.cumsum(counts, 0) - counts
+        within = torch.empty_like(order)
+        within[order] = torch.arange(S, device=dev) - start[owner[order]]
+        # a chunk: S input rows, then the ids in as many rows as S int32 values need. Padding
+        # slots go to a spare chunk that is not sent: every index below is fixed-shape, so the
+        # whole forward can be captured in a CUDA graph
+        id_rows = -(-4 * S // (2 * D))
+        rows = S + id_rows
+        stage = torch.zeros((W + 1, rows, D), dtype=torch.bfloat16, device=dev)
+        ids = torch.full((W + 1, id_rows * D // 2), NO_EXPERT, dtype=torch.int32, device=dev)
+        stage[owner, within] = flat[xi]
+        ids[owner, within] = torch.where(real, ei - owner * self.per, torch.full_like(ei, NO_EXPERT)).to(torch.int32)
+        stage[:, S:] = ids.view(torch.bfloat16).view(W + 1, id_rows, D)
+        send = stage[:W]
+        if W > 1:
+            recv = torch.empty_like(send)
+            dist.all_to_all_single(recv.view(W * rows, D), send.reshape(W * rows, D), group=self.group)
+        else:
+            recv = send
+        # what arrived: W chunks of S slots each; slot j of chunk p reads input row p * rows + j
+        got_ids = recv[:, S:].reshape(W, -1).view(torch.int32)[:, :S].reshape(-1)
+        got_xi = (torch.arange(W, device=dev)[:, None] * rows + torch.arange(S, device=dev)[None, :]).reshape(-1).to(torch.int32)
+        out = self.local_slots(recv.reshape(W * rows, D), got_xi, got_ids)  # [W * S, D]; rows of padding slots are garbage
+        if W > 1:
+            back = torch.empty_like(out)
+            dist.all_to_all_single(back, out.contiguous(), group=self.group)
+        else:
+            back = out
+        back = torch.cat([back.view(W, S, D), torch.zeros((1, S, D), dtype=back.dtype, device=dev)])  # chunk W: zeros for padding slots
+        y = back[owner, within]
+        return y.reshape(*indices.shape, D)

@@ -274,12 +274,22 @@ class RiceEmbedding(nn.Module):
 
 def convert(model: nn.Module, log=None) -> int:
     """Swap every file-array holder for its runtime counterpart in place: BinadeLinear ->
-    R4Linear, BinadeEmbedding -> R4Embedding, or RiceEmbedding for a gather-only table; returns
+    R4Linear, BinadeEmbedding -> R4Embedding, or RiceEmbedding for a gather-only table,
+    moe.BinadeSwitchGLU -> moe.R4SwitchGLU; returns
     how many were converted (reference: r4.py:375-410). Each holder's file arrays are dropped as
     soon as its runtime arrays exist."""
-    todo = [(parent, name) for parent in model.modules() for name, child in parent.named_children() if isinstance(child, (BinadeLinear, BinadeEmbedding))]
+    from . import moe
+
+    todo = [(parent, name) for parent in model.modules() for name, child in parent.named_children() if isinstance(child, (BinadeLinear, BinadeEmbedding, moe.BinadeSwitchGLU))]
     for i, (parent, name) in enumerate(todo, 1):
         holder = getattr(parent, name)
+        if isinstance(holder, moe.BinadeSwitchGLU):  # both expert stacks of a layer (reference r4.py:388-391)
+            new = moe.R4SwitchGLU(R4Linear(transcode(holder.gate_up_proj)), R4Linear(transcode(holder.down_proj)), holder._activation)
+            setattr(parent, name, new)
+            holder.gate_up_proj = holder.down_proj = None
+            if log and (i % 50 == 0 or i == len(todo)):
+                log(f"R4 transcode {i}/{len(todo)}")
+            continue
         if isinstance(holder, BinadeEmbedding):
             new = RiceEmbedding(holder.weight) if holder.gather_only and "bits" in holder.weight else R4Embedding(transcode(holder))
         else:

@@ -82,6 +82,8 @@ class PackedModel:
 
     def rows(self, name: str, chunk: int = CHUNK):
         """Yield (r0, r1, uint16 [r1 - r0, K]) over a packed tensor's 2-D view."""
+        import torch
+
         from .cuda import kernels as ck
 
         raw = self.infos[f"{name}.raw"]
@@ -93,7 +95,7 @@ class PackedModel:
             for r0 in range(0, R, step):
                 r1 = min(R, r0 + step)
                 part = ck.Format1.rows_of(f1, r0, r1)
-                yield r0, r1, part.unpack(st.read(raw, (r0, r1))).view(torch_int16()).cpu().numpy().view(np.uint16)
+                yield r0, r1, part.unpack(st.read(raw, (r0, r1))).view(torch.int16).cpu().numpy().view(np.uint16)
             return
         table, meta, words, roff = (st.read(self.infos[f"{name}.{s}"]) for s in ("table", "meta", "bits", "roff"))
         R, K = raw.rows, raw.shape[-1]
@@ -112,12 +114,6 @@ class PackedModel:
         if name not in self.packed:
             return st.read(self.infos[name])
         return np.concatenate([u for _, _, u in self.rows(name)]).reshape(self.info(name).shape)
-
-
-def torch_int16():
-    import torch
-
-    return torch.int16
 
 
 def main():

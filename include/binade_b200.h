@@ -111,7 +111,8 @@ int bn_r4_finish(const uint32_t *row_cnt, const uint8_t *esc_tmp, const uint32_t
  *            0), info: 4 x uint32 on the device = {number of escapes, R - first bad row (0 = every
  *            row ends where it must), 1 if esc_cap < escapes + 1 (esc is then cut short), 0}
  * The first call on a device looks up the array's device address (cudaGetSymbolAddress, with that
- * device current); make that first call before any stream capture begins. All calls share the
+ * device current) and keeps it for the life of that device's context (it does not survive
+ * cudaDeviceReset); make that first call before any stream capture begins. All calls share the
  * one array and it keeps the last call's contents (the call clears the counters it needs at
  * zero): two calls whose kernels overlap on the GPU, on different streams or from different
  * threads, race; run them one after the other. */
@@ -192,8 +193,13 @@ int bn_r4_rows(const uint16_t *x, int64_t x_stride, const bn_r4 *w, int64_t M, i
 int bn_r4_rows_multi(const uint16_t *x, const bn_r4 *const *w, const int64_t *N, int count, int64_t K,
                      uint16_t *const *y, void *stream);
 
+/* Expert id of a padding slot: bn_r4_gather computes and stores nothing for it (a caller with a
+ * fixed number of slots, e.g. under a CUDA graph, marks the unused ones). */
+#define BN_NO_EXPERT 0xFFFFFFFFu
+
 /* G independent matvecs (the decode step of a mixture of experts). Slot g multiplies input row
- * xi[g] of x [., K] by storage rows ei[g] * RS + R0 + r, r < n. With split == 0 results go to
+ * xi[g] of x [., K] by storage rows ei[g] * RS + R0 + r, r < n; a slot with ei[g] == BN_NO_EXPERT
+ * is skipped (its output row is left untouched). With split == 0 results go to
  * y [G, n]; with 0 < split < n, rows below split go to y [G, split] and the rest to
  * y2 [G, n - split]. Replaces r4_gather, binade/mlx/cuda_kernels.py:133-146. */
 int bn_r4_gather(const uint16_t *x, const bn_r4 *w, const uint32_t *xi, const uint32_t *ei, int64_t G,

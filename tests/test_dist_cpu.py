@@ -153,6 +153,16 @@ def test_row_sharded_group_two_gloo_ranks(tmp_path):
     assert [(tmp_path / f"late{r}").read_text() for r in range(world)] == ["1", "1"]  # gather_all of the local slices
 
 
+def _ep_case():
+    E, D, tokens, k = 8, 16, 6, 3
+    g = torch.Generator().manual_seed(9)
+    x = torch.randn((tokens, D), generator=g).to(torch.bfloat16)
+    idx = torch.stack([torch.randperm(E, generator=g)[:k] for _ in range(tokens)])
+    idx[5, 2] = -1  # a padding slot: routed nowhere, output zero
+    table = torch.randn((E, D), generator=torch.Generator().manual_seed(3)).to(torch.bfloat16)  # a toy "expert": y = x * table[e]
+    return E, D, x, idx, table
+
+
 def _ep_main(rank: int, world: int, port: int, out_dir: str):
     import torch.distributed as dist
 
@@ -160,28 +170,28 @@ def _ep_main(rank: int, world: int, port: int, out_dir: str):
 
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     dist.init_process_group("gloo", rank=rank, world_size=world)
-    E, D, tokens, k = 8, 16, 5, 3
-    g = torch.Generator().manual_seed(9)
-    x = torch.randn((tokens, D), generator=g).to(torch.bfloat16)
-    idx = torch.stack([torch.randperm(E, generator=g)[:k] for _ in range(tokens)])
-    table = torch.randn((E, D), generator=torch.Generator().manual_seed(3)).to(torch.bfloat16)  # a toy "expert": y = x * table[e]
+    E, D, x, idx, table = _ep_case()
+    mine = slice(rank * x.shape[0] // world, (rank + 1) * x.shape[0] // world)  # this rank's share of the batch
 
-    def local_slots(xf, xi, ei_local):  # stands for R4SwitchGLU.slots over this rank's experts
-        return xf[xi.long()] * table[ei_local.long() + rank * (E // world)]
+    def local_slots(xf, xi, ei_local):  # stands for R4SwitchGLU.slots over this rank's experts; padding slots untouched
+        out = torch.full((ei_local.numel(), D), 7.0, dtype=torch.bfloat16)
+        real = ei_local >= 0
+        out[real] = xf[xi[real].long()] * table[ei_local[real].long() + rank * (E // world)]
+        return out
 
-    y = moe.ExpertParallelGLU(local_slots, E, D, rank, world)(x, idx)
+    y = moe.ExpertParallelGLU(local_slots, E, D, rank, world)(x[mine], idx[mine])
     torch.save(y, os.path.join(out_dir, f"y{rank}.pt"))
     dist.destroy_process_group()
 
 
 def test_expert_parallel_two_gloo_ranks(tmp_path):
-    """Every slot is computed by the rank owning its expert and reaches every rank in place."""
-    mp.spawn(_ep_main, args=(2, _free_port(), str(tmp_path)), nprocs=2, join=True)
-    E, D, tokens, k = 8, 16, 5, 3
-    g = torch.Generator().manual_seed(9)
-    x = torch.randn((tokens, D), generator=g).to(torch.bfloat16)
-    idx = torch.stack([torch.randperm(E, generator=g)[:k] for _ in range(tokens)])
-    table = torch.randn((E, D), generator=torch.Generator().manual_seed(3)).to(torch.bfloat16)
-    want = x[:, None, :] * table[idx]
-    for r in range(2):
-        assert torch.equal(torch.load(tmp_path / f"y{r}.pt"), want), r
+    """Every slot's input row reaches the rank owning its expert (all-to-all), is computed there
+    once, and its output comes back to the slot's place on the rank that holds the token."""
+    world = 2
+    mp.spawn(_ep_main, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+    E, D, x, idx, table = _ep_case()
+    want = x[:, None, :] * table[idx.clamp(min=0)]
+    want[idx < 0] = 0
+    for r in range(world):
+        mine = slice(r * x.shape[0] // world, (r + 1) * x.shape[0] // world)
+        assert torch.equal(torch.load(tmp_path / f"y{r}.pt"), want[mine]), r

@@ -153,3 +153,47 @@ def test_push_gather_two_gpus(tmp_path):
         port = s.getsockname()[1]
     mp.spawn(_push_main, args=(2, port, str(tmp_path)), nprocs=2, join=True)
     assert [(tmp_path / f"ok{r}").read_text() for r in range(2)] == ["1", "1"]
+
+
+def _ep_main(rank: int, world: int, port: int, out_dir: str):
+    import torch.distributed as dist
+
+    from binade_b200.cuda import moe, r4
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    E, n, D, k = 8, 128, 768, 3
+    g = torch.Generator(device="cuda").manual_seed(11)
+    gu = (torch.randn((E, 2 * n, D), device="cuda", generator=g) * 0.02).to(torch.bfloat16)
+    dn = (torch.randn((E, D, n), device="cuda", generator=g) * 0.02).to(torch.bfloat16)
+    per = E // world
+    whole = moe.R4SwitchGLU(r4.R4Linear(r4.from_dense(gu)), r4.R4Linear(r4.from_dense(dn)))
+    local = moe.R4SwitchGLU(r4.R4Linear(r4.from_dense(gu[rank * per : (rank + 1) * per].contiguous())), r4.R4Linear(r4.from_dense(dn[rank * per : (rank + 1) * per].contiguous())))
+    ep = moe.ExpertParallelGLU(local.slots, E, D, rank, world)
+    ok = True
+    for tokens in (2, 8, 40):  # per rank: slot by slot, then grouped by expert
+        x = torch.randn((world * tokens, D), device="cuda", generator=g).to(torch.bfloat16)
+        idx = torch.stack([torch.randperm(E, device="cuda", generator=g)[:k] for _ in range(world * tokens)])
+        idx[1, 0] = -1  # a padding slot
+        mine = slice(rank * tokens, (rank + 1) * tokens)
+        y = ep(x[mine], idx[mine])
+        want = whole(x[mine], idx[mine].clamp(min=0))
+        want[idx[mine] < 0] = 0
+        ok = ok and torch.equal(y.view(torch.int16), want.view(torch.int16))
+    with open(os.path.join(out_dir, f"ep{rank}"), "w") as f:
+        f.write("1" if ok else "0")
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_expert_parallel_two_gpus(tmp_path):
+    """Experts and tokens split over two GPUs, all-to-all dispatch and combine: every output is
+    bit-identical to the single-GPU layer over all experts."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    mp.spawn(_ep_main, args=(2, port, str(tmp_path)), nprocs=2, join=True)
+    assert [(tmp_path / f"ep{r}").read_text() for r in range(2)] == ["1", "1"]

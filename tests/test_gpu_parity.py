@@ -605,6 +605,51 @@ def test_grouped_gather_equals_slot_by_slot(tokens, E, topk):
     assert np.array_equal(words(y), words(glu(x, idx)))
 
 
+def test_padding_slots_are_skipped():
+    """A slot whose expert id is NO_EXPERT computes nothing and leaves its output row alone, slot
+    by slot and grouped by expert; the other slots are unchanged by its presence."""
+    from binade_b200.cuda import kernels as ck
+    from binade_b200.cuda import r4
+
+    E, n, K, tokens, topk = 4, 96, 1280, 12, 2
+    rng = np.random.default_rng(8)
+    m = r4.R4Linear(r4.transcode(packed_arrays(weights(rng, (E, n, K)))))
+    x = dev(bf16_words(rng.standard_normal((tokens, K)))).view(torch.bfloat16)
+    ei = torch.tensor(rng.integers(0, E, tokens * topk), dtype=torch.int32, device="cuda")
+    xi = torch.arange(tokens * topk, dtype=torch.int32, device="cuda") // topk
+    plain = m._gather(x, xi, ei, n, n)
+    holes = ei.clone()
+    holes[[0, 5, 23]] = ck.NO_EXPERT
+    keep = torch.ones(tokens * topk, dtype=torch.bool, device="cuda")
+    keep[[0, 5, 23]] = False
+    for got in (m._gather(x, xi, holes, n, n), m._gather_grouped(x, xi, holes, E, tokens, n, n)):
+        assert torch.equal(got[keep].view(torch.int16), plain[keep].view(torch.int16))
+
+
+def test_convert_swaps_expert_holders():
+    from binade_b200.cuda import moe, r4
+
+    rng = np.random.default_rng(4)
+    E, n, D = 3, 32, 256
+    gu, dn = weights(rng, (E, 2 * n, D)), weights(rng, (E, D, n), escapes=False)
+
+    class Layer(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.experts = moe.BinadeSwitchGLU(packed_arrays(gu), packed_arrays(dn))
+
+    model = Layer()
+    with pytest.raises(RuntimeError):
+        model.experts(None, None)
+    assert r4.convert(model) == 1
+    assert isinstance(model.experts, moe.R4SwitchGLU) and (model.experts.E, model.experts.n, model.experts.D) == (E, n, D)
+    assert np.array_equal(words(model.experts._gu.dense()), gu) and np.array_equal(words(model.experts._down.dense()), dn)
+    x = dev(bf16_words(rng.standard_normal((2, D)))).view(torch.bfloat16)
+    idx = torch.tensor([[0, 2], [1, 0]], device="cuda")
+    direct = moe.R4SwitchGLU(r4.R4Linear(r4.transcode(packed_arrays(gu))), r4.R4Linear(r4.transcode(packed_arrays(dn))))
+    assert torch.equal(model.experts(x, idx).view(torch.int16), direct(x, idx).view(torch.int16))
+
+
 def test_convert_swaps_holders():
     from binade_b200.cuda import r4
 
@@ -630,17 +675,6 @@ def test_convert_swaps_holders():
     assert a["shape"] == (300, 256)
 
 
-def test_zz_device_status_is_clean():
-    """No kernel of this run gave up a bounded wait (collected last in this file)."""
-    import ctypes
-
-    from binade_b200 import _native
-
-    st = ctypes.c_int(-1)
-    _native.call("cuda", "bn_device_status", ctypes.byref(st))
-    assert st.value == 0
-
-
 def test_switch_glu_matches_oracle():
     """MoE decode step: fused gate/up gather, SwiGLU, down gather, against the oracle's products."""
     from binade_b200.cuda import moe, r4
@@ -664,3 +698,14 @@ def test_switch_glu_matches_oracle():
     h = words(moe.swiglu(up, gate))
     want = o.c_r4_gather(a_dn, h, np.arange(ei.size, dtype=np.uint32), ei, D, n, D)
     assert np.array_equal(words(y).reshape(-1, D), want)
+
+
+def test_zz_device_status_is_clean():
+    """No kernel of this run gave up a bounded wait (collected last in this file)."""
+    import ctypes
+
+    from binade_b200 import _native
+
+    st = ctypes.c_int(-1)
+    _native.call("cuda", "bn_device_status", ctypes.byref(st))
+    assert st.value == 0

@@ -44,6 +44,12 @@ def check(u: np.ndarray):
     assert info.tolist() == [n, 0, 0, 0]
     assert torch.equal(codes, want["codes"]) and torch.equal(flags, want["flags"]) and torch.equal(row_esc, want["row_esc"])
     assert torch.equal(esc[: n + 1], want["esc"])
+    # and directly against the CPU oracle's arrays (the reference's transcode, restated)
+    from oracle import oracle as o
+
+    ref = o.pack_r4(u.reshape(-1, u.shape[-1]))
+    assert np.array_equal(codes.cpu().numpy().view(np.uint16), ref["codes"]) and np.array_equal(flags.cpu().numpy(), ref["flags"])
+    assert np.array_equal(row_esc.cpu().numpy().view(np.uint32), ref["row_esc"]) and np.array_equal(esc[: n + 1].cpu().numpy(), ref["esc"])
 
 
 def test_static_expander_matches_two_calls_in_a_row():
