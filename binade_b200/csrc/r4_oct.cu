@@ -176,24 +176,20 @@ struct OctGeom {
 };
 
 // General case of a flagged tile: some thread holds several escapes. Inclusive scan of the counts
-// over the row's threads, then every thread walks its own hits. Whole warp calls it. Kept out of
-// line, pair words in and out by value: it is rare, and inlined its loops and merges cost the
-// common path registers and moves.
+// over the row's threads, then every thread walks its own hits. Whole warp calls it. Inlined:
+// as a separate function its call made the caller keep registers in local memory around it, and
+// those loads and stores (evicted from L1 by the streamed weights) cost more than the path itself.
 template <int R>
-struct OctWords {
-  uint32_t w[2 * R], tot;
-};
-template <int R>
-__device__ __noinline__ OctWords<R> escape_general(OctWords<R> io, uint32_t h0, uint32_t h1, uint32_t cnt, uint32_t epos, uint32_t win_word, uint32_t win_base, const uint8_t *__restrict__ esc) {
+__device__ __forceinline__ uint32_t escape_general(uint32_t (&w)[2 * R], uint32_t h0, uint32_t h1, uint32_t epos, uint32_t win_word, uint32_t win_base, const uint8_t *__restrict__ esc, uint32_t lane) {
   using Geo = OctGeom<R>;
-  const uint32_t lane = lane_id(), p = lane & (Geo::TPR - 1);
+  const uint32_t p = lane & (Geo::TPR - 1), cnt = __popc(h0) + __popc(h1);
   uint32_t s = cnt;
 #pragma unroll
   for (int d = 1; d < Geo::TPR; d <<= 1) {
     const uint32_t n = __shfl_up_sync(BN_FULL, s, d, Geo::TPR);
     if (p >= (uint32_t)d) s += n;
   }
-  io.tot = __shfl_sync(BN_FULL, s, Geo::TPR - 1, Geo::TPR);
+  const uint32_t tot = __shfl_sync(BN_FULL, s, Geo::TPR - 1, Geo::TPR);
   uint32_t q = epos + s - cnt;
 #pragma unroll
   for (int half = 0; half < Geo::NC; half++) {
@@ -206,14 +202,14 @@ __device__ __noinline__ OctWords<R> escape_general(OctWords<R> io, uint32_t h0, 
       if (h != 0 && idx >= Geo::WINDOW) e = esc[q];  // outside the window (a row dense with escapes)
       const uint32_t val = e << (7u + ((bit & 4u) << 2));
       if (h != 0) {
-        if (half) or_into<4>(bit >> 3, val, io.w);
-        else or_into<0>(bit >> 3, val, io.w);
+        if (half) or_into<4>(bit >> 3, val, w);
+        else or_into<0>(bit >> 3, val, w);
         q++;
         h &= h - 1u;
       }
     }
   }
-  return io;
+  return tot;
 }
 
 // Where a block's rings sit in the shared window (absolute shared addresses; base = start of the
@@ -272,25 +268,22 @@ __device__ __forceinline__ void oct_decode(OctTile<R> &t, const OctSelf &me, uin
 template <int R>
 __device__ __forceinline__ void oct_finish(OctRow<R> &s, OctTile<R> &t, const OctSelf &me, bool flagged, bool live) {
   using Geo = OctGeom<R>;
-#ifdef OC_PROBE_NO_ESC
-  if (false) {
-#else
   if (flagged) {
-#endif
-    uint32_t hits[Geo::NC], cnt = 0;
+    uint32_t hits[Geo::NC];
 #pragma unroll
-    for (int i = 0; i < Geo::NC; i++) hits[i] = hits15(t.cc[i]), cnt += __popc(hits[i]);
-    const uint32_t one = __ballot_sync(BN_FULL, cnt == 1u), many = __ballot_sync(BN_FULL, cnt > 1u);
-    // at most one escape per thread (nearly always one in the whole warp), all inside the rows'
-    // windows: straight-line code. Its byte is as many places after the row's cursor as threads
-    // of the row before this one hold an escape.
-    const uint32_t idx = s.epos + __popc(one & me.ltg) - s.win.base;
-    const uint32_t far = __ballot_sync(BN_FULL, cnt != 0 && idx >= Geo::WINDOW);
-    if (__builtin_expect((many | far) == 0, 1)) {
-      const uint32_t v = __shfl_sync(BN_FULL, s.win.word, me.lane_hi | ((idx >> 2) & (Geo::TPR - 1)));
-      const uint32_t e = cnt ? __byte_perm(v, 0u, 0x4440u | (idx & 3u)) : 0u;  // threads without an escape OR nothing in
-      const uint32_t upper = Geo::NC > 1 ? hits[Geo::NC - 1] : 0u;
-      const uint32_t bit = (uint32_t)__ffs((int)(hits[0] | upper)) - 1u;  // 4j: weight j of the register's eight
+    for (int i = 0; i < Geo::NC; i++) hits[i] = hits15(t.cc[i]);
+    const uint32_t upper = Geo::NC > 1 ? hits[Geo::NC - 1] : 0u, h = hits[0] | upper;
+    const bool several = ((hits[0] & (hits[0] - 1u)) | (upper & (upper - 1u))) != 0 || (hits[0] != 0 && upper != 0);
+    const uint32_t one = __ballot_sync(BN_FULL, h != 0), many = __ballot_sync(BN_FULL, several);
+    if (__builtin_expect(many == 0, 1)) {
+      // at most one escape per thread (nearly always one in the whole warp): straight-line code.
+      // Its byte is as many places after the row's cursor as threads of the row before this one
+      // hold an escape; the window reaches that far, since it is slid on as soon as the cursor
+      // is half-way through it and a tile adds at most one escape per thread here.
+      const uint32_t idx = s.epos + __popc(one & me.ltg) - s.win.base;
+      const uint32_t v = __shfl_sync(BN_FULL, s.win.word, me.lane_hi | (idx >> 2));
+      const uint32_t e = h ? __byte_perm(v, 0u, 0x4440u | (idx & 3u)) : 0u;  // threads without an escape OR nothing in
+      const uint32_t bit = 31u - (uint32_t)__clz((int)h);  // 4j: weight j of the register's eight (h holds one bit)
       const uint32_t val = e << (7u + ((bit & 4u) << 2));
       const uint32_t k = (bit >> 3) & 3u;
       const uint32_t lo = upper ? 0u : val, hi = upper ? val : 0u;
@@ -300,13 +293,7 @@ __device__ __forceinline__ void oct_finish(OctRow<R> &s, OctTile<R> &t, const Oc
       for (int i = 4; i < 2 * R; i++) t.w[i] |= k == (uint32_t)(i - 4) ? hi : 0u;
       s.epos += __popc(one & me.gmask);
     } else {
-      OctWords<R> io;
-#pragma unroll
-      for (int i = 0; i < 2 * R; i++) io.w[i] = t.w[i];
-      io = escape_general<R>(io, hits[0], Geo::NC > 1 ? hits[Geo::NC - 1] : 0u, cnt, s.epos, s.win.word, s.win.base, me.esc);
-#pragma unroll
-      for (int i = 0; i < 2 * R; i++) t.w[i] = io.w[i];
-      s.epos += io.tot;
+      s.epos += escape_general<R>(t.w, hits[0], upper, s.epos, s.win.word, s.win.base, me.esc, me.lane);
     }
     if (__builtin_expect(s.epos - s.win.base >= Geo::WINDOW / 2, 0)) {  // slide the window on (the load returns while tiles decode)
       s.win.base = s.epos & ~3u;
@@ -318,13 +305,6 @@ __device__ __forceinline__ void oct_finish(OctRow<R> &s, OctTile<R> &t, const Oc
     for (int i = 0; i < R; i++) s.acc[i] = fma2_bf16(t.w[2 * i + 1], t.xx[2 * i + 1], fma2_bf16(t.w[2 * i], t.xx[2 * i], s.acc[i]));
   }
 }
-
-#ifndef OC_BATCH4
-#define OC_BATCH4 1  // tiles decoded before the first of them is finished, four rows per warp
-#endif
-#ifndef OC_BATCH2
-#define OC_BATCH2 1  // the same with two rows or one row per warp
-#endif
 
 // R: rows a warp walks side by side; NQ: quads of four tiles in flight per thread; MAXW: most
 // warps a block may have (bounds the registers). Both sides of the ring move in quads: a quad
@@ -518,25 +498,13 @@ __global__ void __launch_bounds__(MAXW * 32, 1) r4_oct_kernel(const __grid_const
     const uint32_t token = cp_wait<NQ - 1>();  // all but the newest NQ - 1 groups have landed: this quad's has
     if (R == 1) __syncwarp();                  // a lane reads code words its neighbour copied
     if (cn == 4 && !partial) {
-      // four whole tiles, decoded a few at a time before their escapes and products, so that the
-      // table lookups of several tiles are in flight together; each slot is refilled, with a
-      // tile of the quad NQ ahead, once the quad is read
-      constexpr int B = R == 4 ? OC_BATCH4 : OC_BATCH2;
-      OctTile<R> t[B];
-      if constexpr (B == 4) {
-        oct_decode<R, 0>(t[0], me, at, xs, token), oct_decode<R, 1>(t[1], me, at, xs, token), oct_decode<R, 2>(t[2], me, at, xs, token), oct_decode<R, 3>(t[3], me, at, xs, token);
-        oct_finish<R>(s, t[0], me, fq & 1u, true), oct_finish<R>(s, t[1], me, fq & 2u, true), oct_finish<R>(s, t[2], me, fq & 4u, true), oct_finish<R>(s, t[3], me, fq & 8u, true);
-      } else if constexpr (B == 2) {
-        oct_decode<R, 0>(t[0], me, at, xs, token), oct_decode<R, 1>(t[1], me, at, xs, token);
-        oct_finish<R>(s, t[0], me, fq & 1u, true), oct_finish<R>(s, t[1], me, fq & 2u, true);
-        oct_decode<R, 2>(t[0], me, at, xs, token), oct_decode<R, 3>(t[1], me, at, xs, token);
-        oct_finish<R>(s, t[0], me, fq & 4u, true), oct_finish<R>(s, t[1], me, fq & 8u, true);
-      } else {
-        oct_decode<R, 0>(t[0], me, at, xs, token), oct_finish<R>(s, t[0], me, fq & 1u, true);
-        oct_decode<R, 1>(t[0], me, at, xs, token), oct_finish<R>(s, t[0], me, fq & 2u, true);
-        oct_decode<R, 2>(t[0], me, at, xs, token), oct_finish<R>(s, t[0], me, fq & 4u, true);
-        oct_decode<R, 3>(t[0], me, at, xs, token), oct_finish<R>(s, t[0], me, fq & 8u, true);
-      }
+      // four whole tiles; each slot is refilled, with a tile of the quad NQ ahead, once the quad
+      // is read
+      OctTile<R> t;
+      oct_decode<R, 0>(t, me, at, xs, token), oct_finish<R>(s, t, me, fq & 1u, true);
+      oct_decode<R, 1>(t, me, at, xs, token), oct_finish<R>(s, t, me, fq & 2u, true);
+      oct_decode<R, 2>(t, me, at, xs, token), oct_finish<R>(s, t, me, fq & 4u, true);
+      oct_decode<R, 3>(t, me, at, xs, token), oct_finish<R>(s, t, me, fq & 8u, true);
       if (R == 1) __syncwarp();  // the neighbour's reads too
       if (pn > 0) copy_tile<R, 0>(at, to_codes, praw, pcode, code_lane, s.acc[0]);
       if (pn > 1) copy_tile<R, 1>(at, to_codes, praw, pcode, code_lane, s.acc[0]);
