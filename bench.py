@@ -412,34 +412,68 @@ def run_ours(args) -> dict | None:
         nbytes = sum(l[4] for l in layers if l[0] in g) - 2 * group_k[gi] * (len(g) - 1)  # x is read once
         per_launch["+".join(g)] = {"us": round(us, 2), "gbs": round(nbytes / us / 1e3, 1), "frac_of_measured_hbm": round(nbytes / us / 1e3 / measured_peaks()["hbm_gbs"], 3)}
     note("per-shape timings done")
-    # ---- end to end through the public hook with host buffers
+    # ---- end to end through the public hook with host buffers: every step copies its inputs
+    # from pinned host memory, runs the step and copies the seven outputs back to pinned host
+    # memory, then synchronises. Measured twice: as eager calls, and with the same calls captured
+    # once per weight copy in a CUDA graph that every step replays (how a serving loop runs a
+    # fixed-shape step): the copies are nodes of the graph, so they are inside the timed region.
     k_list = sorted({k for _, _, k in SHAPES})
-    h_x = {k: torch.from_numpy(synthetic_input(k, rank).view(np.int16)).view(torch.bfloat16).pin_memory() for k in k_list}
+    h_x = {k: torch.from_numpy(xs_host[k].view(np.int16)).view(torch.bfloat16).pin_memory() for k in k_list}
     h_y = [torch.empty(n, dtype=torch.bfloat16).pin_memory() for _, n, _ in SHAPES]
     shape_index = {name: j for j, (name, _, _) in enumerate(SHAPES)}
 
-    def e2e_step(i: int):
+    def e2e_body(i: int):
         dx = {k: h_x[k].to(dev, non_blocking=True) for k in k_list}
-        for name, y in zip(out_names, step(i, dx)):  # the public hook (sharded groups with their collectives when N > 1)
+        for name, y in zip(out_names, step(i, dx)):  # the public hook (sharded groups with their collective when N > 1)
             j = shape_index[name]
             h_y[j].copy_(y.reshape(-1)[: SHAPES[j][1]], non_blocking=True)
+
+    def timed(run, n_steps: int) -> float:
+        for i in range(3):
+            run(i)
+        if world > 1:
+            dist.barrier()
+        ev0.record()
+        for i in range(n_steps):
+            run(i)
+        ev1.record()
+        torch.cuda.synchronize()
+        t_ms = ev0.elapsed_time(ev1) / n_steps
+        if world > 1:
+            t = torch.tensor([t_ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            t_ms = float(t.item())
+        return t_ms
+
+    def eager_step(i: int):
+        e2e_body(i)
         torch.cuda.synchronize()
 
     e2e_steps = 3 if args.quick else min(args.steps, 200)
-    for i in range(3):
-        e2e_step(i)
-    if world > 1:
-        dist.barrier()
-    ev0.record()
-    for i in range(e2e_steps):
-        e2e_step(i)
-    ev1.record()
-    torch.cuda.synchronize()
-    e2e_ms = ev0.elapsed_time(ev1) / e2e_steps
-    if world > 1:
-        t = torch.tensor([e2e_ms], device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        e2e_ms = float(t.item())
+    e2e_eager_ms = timed(eager_step, e2e_steps)
+    e2e_graphs = []
+    for c in range(copies):
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(side):
+            e2e_body(c)
+            side.synchronize()
+            with torch.cuda.graph(g, stream=side):
+                e2e_body(c)
+        torch.cuda.synchronize()
+        e2e_graphs.append(g)
+
+    def graph_step(i: int):
+        e2e_graphs[i % copies].replay()
+        torch.cuda.synchronize()
+
+    for j in range(len(h_y)):
+        h_y[j].zero_()
+    e2e_ms = timed(graph_step, e2e_steps)
+    if rank == 0:  # what came back to the host is the checked product (the first slice is rank 0's)
+        for name, (n, k, mods) in by_name.items():
+            want = mods[(e2e_steps - 1) % copies](xs[k]).reshape(-1).cpu()
+            if not torch.equal(h_y[shape_index[name]].view(torch.int16), want.view(torch.int16)):
+                raise SystemExit(f"bench: the end-to-end step returned a wrong {name} to the host")
     e2e_val = world * step_bytes / (e2e_ms * 1e-3) / 1e9
     note("end-to-end leg done")
 
@@ -498,7 +532,7 @@ def run_ours(args) -> dict | None:
         "speedup_vs_bf16_gemv_per_token": round(sum(v["bf16_gemv_us"] for v in per_shape.values()) / sum(v["us"] for v in per_shape.values()), 3) if per_shape else None,
         "expander": {"ms_per_layer": round(expand_ms, 3), "gbs": round(expand_bytes / expand_ms / 1e6, 1), "algorithmic_bytes": expand_bytes, "host_pack_s": round(host_pack_s, 2), "host_pack_cores": cpu_cores()},
         "roofline": {"bound": "hbm", "kernel": f"r4_oct_kernel (all {len(groups)} launches of a step), averaged over them", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"], "peak_source": peaks["source"], "bytes_per_launch": per_launch_bytes, "traffic": per_launch_bytes * NCU_TRAFFIC_RATIO, "traffic_source": "assumed, not measured in this run: DRAM read + write bytes of one ncu capture of the same kernel on the gate matrix, scaled to the average launch by its bytes"},
-        "e2e": {"value": e2e_val, "unit": UNIT, "ms_per_step": e2e_ms, "h2d_bytes_per_step": sum(2 * k for k in k_list), "d2h_bytes_per_step": sum(2 * n for _, n, _ in SHAPES), "api": "R4LinearGroup.__call__ (RowShardedGroup with several GPUs) on host-resident inputs, outputs copied back to pinned host memory"},
+        "e2e": {"value": e2e_val, "unit": UNIT, "ms_per_step": e2e_ms, "h2d_bytes_per_step": sum(2 * k for k in k_list), "d2h_bytes_per_step": sum(2 * n for _, n, _ in SHAPES), "api": "R4LinearGroup.__call__ (RowShardedGroup + gather_all with several GPUs) on host-resident inputs, outputs copied back to pinned host memory; the calls of one step are captured once in a CUDA graph (copies included) and every step replays it and synchronises", "eager_ms_per_step": e2e_eager_ms, "eager_value": world * step_bytes / (e2e_eager_ms * 1e-3) / 1e9},
         "gpu_launches": launches,
         "decode": decode,
         "prefill_gate_15360x3840": prefill,

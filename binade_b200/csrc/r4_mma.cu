@@ -23,11 +23,13 @@
 
 #include "common.cuh"
 #include "decode.cuh"
+#include "oct.cuh"
 
 namespace bn {
 
 constexpr int MMA_DECODE_WARPS = 14;  // decode warps of the shape used (measured: 14 x 8 rows 46 us, 28 x 4 rows 55 us on 15360 x 3840)
 constexpr int MMA_RPW = 8;            // weight rows per decode warp and stage
+constexpr int MMA_OCT_WARPS = 26;     // decode warps of the eight-threads-per-row kernel: 104 rows a block, 15360 rows in 148 blocks
 constexpr int MMA_BM = 128;                  // MMA M: rows of the A tile (the block's rows, then unused)
 constexpr int MMA_BK = 128;                  // k per stage: one R4 tile
 constexpr uint32_t MMA_A_STAGE = MMA_BM * MMA_BK * 2;  // 32 KB: two 64-k atoms of 128 rows x 128 B
@@ -49,6 +51,8 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map
   asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
 }
 __device__ __forceinline__ bool mm_bar_wait(uint32_t bar, uint32_t parity) {
+  // (a try with a suspend-time hint compiles to a sleep-and-poll loop of its own: more
+  // instructions for the same wait, measured, so the plain form is kept)
   for (uint32_t i = 0; i < MMA_SPIN_LIMIT; i++) {
     uint32_t ok;
     asm volatile(
@@ -104,6 +108,75 @@ struct MmaArgs {
 // Byte offset of (row r, 16-byte chunk c of the row's 128 bytes) inside a swizzled atom.
 __device__ __forceinline__ uint32_t swz(uint32_t r, uint32_t c) { return r * 128u + ((c ^ (r & 7u)) << 4); }
 
+// Shared addresses of a block's stage ring and barriers.
+struct MmaWindow {
+  uint32_t a_at, b_at, b_stage;      // A stages, B stages, bytes of a B stage
+  uint32_t full, empty, done, slot;  // full[S], empty[S], done, the word that receives the TMEM address
+};
+
+// The MMA warp: TMA copies of X and the MMAs of every k-tile. Returns false when a wait gave up.
+__device__ __forceinline__ bool mma_issue_side(const CUtensorMap *x_map, const MmaWindow &m, int T, int S, int BN, uint32_t tmem, uint32_t lane, bool ok) {
+  const uint32_t idesc = mma_idesc(MMA_BM, BN);
+  auto fetch_x = [&](int t, int s) {  // X tile of k-tile t into slot s, which must be free
+    const uint32_t b_s = m.b_at + (uint32_t)s * m.b_stage;
+    mm_bar_expect_tx(m.full + 8 * s, m.b_stage);
+    tma_load_2d(b_s, x_map, t * MMA_BK, 0, m.full + 8 * s);
+    tma_load_2d(b_s + (uint32_t)BN * 128u, x_map, t * MMA_BK + 64, 0, m.full + 8 * s);
+  };
+  if (lane == 0)
+    for (int t = 0; t < S && t < T; t++) fetch_x(t, t);
+  __syncwarp();
+  int s = 0, sp = 0;        // slot of tile t, slot of tile t - 1
+  uint32_t ph = 0, php = 0;  // parity of their current phases
+  for (int t = 0; t < T; t++) {
+    if (ok) ok = mm_bar_wait(m.full + 8 * s, ph);
+    tc_fence_after();
+    if (lane == 0 && ok) {
+      const uint32_t a_s = m.a_at + (uint32_t)s * MMA_A_STAGE, b_s = m.b_at + (uint32_t)s * m.b_stage;
+#pragma unroll
+      for (int j = 0; j < MMA_BK / 16; j++) {  // 16 k per MMA: 32 bytes further along the swizzled row
+        const uint64_t da = smem_desc(a_s + (j >> 2) * (MMA_BM * 128u) + (j & 3) * 32u);
+        const uint64_t db = smem_desc(b_s + (j >> 2) * ((uint32_t)BN * 128u) + (j & 3) * 32u);
+        mma_bf16(tmem, da, db, idesc, (t | j) != 0);
+      }
+      mma_commit(m.empty + 8 * s);  // arrives when these MMAs have read the stage
+    }
+    __syncwarp();
+    // The slot of the previous tile takes the X tile that will use it next. Waiting for that
+    // tile's MMAs here costs nothing (they were issued a whole stage ago), whereas waiting for
+    // the MMAs just issued would put their latency between every two stages.
+    if (t >= 1 && t - 1 + S < T) {
+      if (ok) ok = mm_bar_wait(m.empty + 8 * sp, php);
+      if (lane == 0 && ok) fetch_x(t - 1 + S, sp);
+      __syncwarp();
+    }
+    sp = s, php = ph;
+    if (++s == S) s = 0, ph ^= 1u;
+  }
+  if (lane == 0 && ok) mma_commit(m.done);
+  __syncwarp();
+  return ok;
+}
+
+// Warps 0..3: accumulators out of tensor memory (TMEM lane = weight row of the block), rounded to
+// BF16 and stored.
+__device__ __forceinline__ void mma_store_side(const MmaArgs &a, const MmaWindow &m, uint32_t tmem, uint32_t warp, uint32_t lane, int64_t row_base, int rows, bool ok) {
+  if (ok) ok = mm_bar_wait(m.done, 0);
+  tc_fence_after();
+  const int r = (int)(warp * 32 + lane);
+  if (!ok) return;
+  for (int c = 0; c < a.BN; c += 8) {
+    uint32_t v[8];
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+                 : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7])
+                 : "r"(tmem + ((warp * 32u) << 16) + (uint32_t)c));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 8; i++)
+      if (c + i < a.M && r < rows) a.y[(int64_t)(c + i) * a.y_stride + row_base + r] = f32_to_bf16_bits(__uint_as_float(v[i]));
+  }
+}
+
 // DW decode warps (plus the MMA warp), RPW weight rows per decode warp and stage: a block takes
 // up to DW * RPW <= 128 weight rows.
 template <int DW, int RPWT>
@@ -120,6 +193,7 @@ __global__ void __launch_bounds__((DW + 1) * 32, 1) r4_mma_kernel(const __grid_c
   const uint32_t a_at = base, b_at = a_at + (uint32_t)S * MMA_A_STAGE, lut_at = b_at + (uint32_t)S * b_stage;
   const uint32_t bar_at = lut_at + LUT_WORDS * 4u;  // full[S], empty[S], done, then the TMEM address
   const uint32_t full = bar_at, empty = bar_at + 8u * S, done = bar_at + 16u * S, slot = done + 8u;
+  const MmaWindow win{a_at, b_at, b_stage, full, empty, done, slot};
   uint8_t *const gen = mma_smem + (base - smem_addr(mma_smem));  // generic pointer to `base`
 
   const int64_t row_base = (int64_t)blockIdx.x * a.rows;
@@ -210,69 +284,153 @@ __global__ void __launch_bounds__((DW + 1) * 32, 1) r4_mma_kernel(const __grid_c
       if (++s == S) s = 0, ph ^= 1u;
     }
   } else if (warp == MMA_DECODE_WARPS) {
-    // ---------------------------------------------------------------- TMA for X, MMA issue
-    const uint32_t idesc = mma_idesc(MMA_BM, BN);
-    auto fetch_x = [&](int t, int s) {  // X tile of k-tile t into slot s, which must be free
-      const uint32_t b_s = b_at + (uint32_t)s * b_stage;
-      mm_bar_expect_tx(full + 8 * s, b_stage);
-      tma_load_2d(b_s, &x_map, t * MMA_BK, 0, full + 8 * s);
-      tma_load_2d(b_s + (uint32_t)BN * 128u, &x_map, t * MMA_BK + 64, 0, full + 8 * s);
-    };
-    if (lane == 0)
-      for (int t = 0; t < S && t < T; t++) fetch_x(t, t);
-    __syncwarp();
-    int s = 0, sp = 0;        // slot of tile t, slot of tile t - 1
-    uint32_t ph = 0, php = 0;  // parity of their current phases
-    for (int t = 0; t < T; t++) {
-      if (ok) ok = mm_bar_wait(full + 8 * s, ph);
-      tc_fence_after();
-      if (lane == 0 && ok) {
-        const uint32_t a_s = a_at + (uint32_t)s * MMA_A_STAGE, b_s = b_at + (uint32_t)s * b_stage;
-#pragma unroll
-        for (int j = 0; j < MMA_BK / 16; j++) {  // 16 k per MMA: 32 bytes further along the swizzled row
-          const uint64_t da = smem_desc(a_s + (j >> 2) * (MMA_BM * 128u) + (j & 3) * 32u);
-          const uint64_t db = smem_desc(b_s + (j >> 2) * ((uint32_t)BN * 128u) + (j & 3) * 32u);
-          mma_bf16(tmem, da, db, idesc, (t | j) != 0);
-        }
-        mma_commit(empty + 8 * s);  // arrives when these MMAs have read the stage
-      }
-      __syncwarp();
-      // The slot of the previous tile takes the X tile that will use it next. Waiting for that
-      // tile's MMAs here costs nothing (they were issued a whole stage ago), whereas waiting for
-      // the MMAs just issued would put their latency between every two stages.
-      if (t >= 1 && t - 1 + S < T) {
-        if (ok) ok = mm_bar_wait(empty + 8 * sp, php);
-        if (lane == 0 && ok) fetch_x(t - 1 + S, sp);
-        __syncwarp();
-      }
-      sp = s, php = ph;
-      if (++s == S) s = 0, ph ^= 1u;
-    }
-    if (lane == 0 && ok) mma_commit(done);
-    __syncwarp();
+    ok = mma_issue_side(&x_map, win, T, S, BN, tmem, lane, ok);
   }
-
-  // ------------------------------------------------------------------ epilogue: warps 0..3
-  if (warp < 4) {
-    if (ok) ok = mm_bar_wait(done, 0);
-    tc_fence_after();
-    const int r = (int)(warp * 32 + lane);  // TMEM lane = weight row of the block
-    if (ok) {
-      for (int c = 0; c < BN; c += 8) {
-        uint32_t v[8];
-        asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
-                     : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7])
-                     : "r"(tmem + ((warp * 32u) << 16) + (uint32_t)c));
-        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-        for (int i = 0; i < 8; i++)
-          if (c + i < a.M && r < rows) a.y[(int64_t)(c + i) * a.y_stride + row_base + r] = f32_to_bf16_bits(__uint_as_float(v[i]));
-      }
-    }
-  }
+  if (warp < 4) mma_store_side(a, win, tmem, warp, lane, row_base, rows, ok);
   tc_fence_before();
   __syncthreads();
   if (warp == MMA_DECODE_WARPS) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(a.tmem_cols) : "memory");
+}
+
+// The same GEMM with the decode side of the batch-1 matvec: eight threads per weight row (a thread
+// decodes 16 consecutive weights of every tile: two 16-byte chunks of the swizzled A row), four
+// rows per warp, up to 26 decode warps = 104 rows per block, every thread streaming its own bytes
+// through a private cp.async ring of D tiles. About half the instructions per weight of the
+// kernel above (one 16-byte and one 8-byte shared load bring what eight 4-byte and 2-byte global
+// loads brought; the escape patch runs once per four rows), which is what bounds both. Takes
+// M <= 128 (the rings need the shared memory that wider B stages would use) and K % 16 == 0.
+template <int MAXW, int D>
+__global__ void __launch_bounds__((MAXW + 1) * 32, 1) r4_mma_oct_kernel(const __grid_constant__ CUtensorMap x_map, MmaArgs a) {
+  constexpr int R = 4;
+  using Geo = OctGeom<R>;
+  constexpr uint32_t SLOT = Geo::SLOT, RING = D * SLOT;
+  extern __shared__ uint8_t mma_smem[];
+  const uint32_t lane = lane_id(), warp = threadIdx.x >> 5;
+  const int T = a.T, S = a.stages, BN = a.BN;
+  const int64_t K = a.K;
+  const uint32_t b_stage = (uint32_t)BN * MMA_BK * 2u;
+  // shared window: A stages | B stages | pair table | barriers | rings
+  const uint32_t base = (smem_addr(mma_smem) + 1023u) & ~1023u;
+  const uint32_t a_at = base, b_at = a_at + (uint32_t)S * MMA_A_STAGE, lut_at = b_at + (uint32_t)S * b_stage;
+  const uint32_t bar_at = lut_at + LUT_WORDS * 4u, ring_at = bar_at + 256u;
+  const MmaWindow win{a_at, b_at, b_stage, bar_at, bar_at + 8u * S, bar_at + 16u * S, bar_at + 16u * S + 8u};
+  uint8_t *const gen = mma_smem + (base - smem_addr(mma_smem));
+
+  const int64_t row_base = (int64_t)blockIdx.x * a.rows;
+  const int rows = (int)min((int64_t)a.rows, a.N - row_base);
+  const uint32_t active = (uint32_t)(rows + R - 1) / R;  // decode warps with rows
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < S; s++) mm_bar_init(win.full + 8 * s, active + 1), mm_bar_init(win.empty + 8 * s, 1);
+    mm_bar_init(win.done, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == MAXW) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(win.slot), "r"(a.tmem_cols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+
+  // ---- load side of a decode warp, started before the table is built
+  const uint32_t grp = lane >> 3, p = lane & 7u;
+  const uint32_t r = warp * R + grp;  // row of the A tile (and of the block)
+  const int64_t srow = row_base + min((int)r, rows - 1);  // a slot past the block's last row decodes that row again; its MMA row is never stored
+  const bool decoder = warp < active;
+  const bool partial = (K & 127) != 0;
+  const uint32_t pmax = (uint32_t)(K & 127) / 16u;  // threads that hold weights in a short last tile
+  const uint32_t ring = ring_at + warp * RING + lane * 16u, to_codes = 512u - lane * 8u;
+  const uint8_t *praw = a.w.raw + srow * K + p * 16u;
+  const uint8_t *pcode = reinterpret_cast<const uint8_t *>(a.w.codes) + srow * ((int64_t)T * 64) + p * 8u;
+  int pt = 0;  // first tile the load side has not asked for
+  // the next tile into the slot at `at`, as one cp.async group (an empty group past the row's
+  // end, so that "all but the newest D - 1 groups" always names the tile being decoded); in a
+  // short last tile the threads past the row's end copy thread 0's bytes and ignore them
+  auto load_tile = [&](uint32_t at) {
+    if (pt < T) {
+      const bool tail = partial && pt == T - 1 && p >= pmax;
+      copy_tile<R, 0>(at, to_codes, tail ? praw - p * 16u : praw, pcode, true, 0.0f);
+      praw += 128, pcode += 64, pt++;
+    }
+    cp_commit();
+  };
+  if (decoder) {
+#pragma unroll
+    for (int u = 0; u < D; u++) load_tile(ring + u * SLOT);
+  }
+
+  build_pair_lut(reinterpret_cast<uint32_t *>(gen + (lut_at - base)), a.w.table);  // syncs once inside
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  uint32_t tmem;
+  asm volatile("ld.shared.u32 %0, [%1];" : "=r"(tmem) : "r"(win.slot));
+
+  bool ok = true;
+
+  if (decoder) {
+    OctSelf me;
+    asm volatile("mov.u32 %0, 0;" : "=r"(me.ready)::"memory");  // after the barrier: orders the table reads
+    me.lane = lane, me.lane_hi = lane & ~7u, me.to_codes = to_codes, me.lut = lut_at + lane * 4u;
+    me.gmask = 0xFFu << (grp * 8u), me.ltg = me.gmask & lanemask_lt();
+    me.esc = a.w.esc, me.esc_cap = a.w.n_esc + 1;
+    const uint8_t *const flags = a.w.flags + srow * T;
+    uint32_t epos = __ldg(a.w.row_esc + srow);
+    EscWindow ew;
+    ew.base = epos & ~3u;
+    ew.word = window_load(me.esc, me.esc_cap, ew.base + p * 4u);
+    uint32_t nflag = p < 8u && (int)p < T ? (uint32_t)__ldg(flags + p) : 0u;  // this thread's flag byte of the next block of eight tiles
+    uint32_t fm = 0;
+    // the two 16-byte chunks of this thread in a stage: k 16p .. 16p+7 and 16p+8 .. 16p+15 of row r
+    const uint32_t a_off0 = (p >> 2) * (MMA_BM * 128u) + swz(r, 2u * (p & 3u)), a_off1 = (p >> 2) * (MMA_BM * 128u) + swz(r, 2u * (p & 3u) + 1u);
+    int s = 0;
+    uint32_t ph = 1;  // parity of the `empty` phase that frees slot s (first pass: slots start free)
+    // D tiles a round, so that tile ct + u sits in slot u (an immediate offset)
+    for (int c0 = 0; c0 < T; c0 += D) {
+#pragma unroll
+      for (int u = 0; u < D; u++) {
+        const int ct = c0 + u;
+        if (ct >= T) break;
+        const uint32_t at = ring + u * SLOT;
+        if ((ct & 7) == 0) {  // a new block of eight tiles: fold the flag bytes, fetch the next block's
+          const uint32_t v = __ballot_sync(BN_FULL, nflag != 0);
+          fm = (v | (v >> 8) | (v >> 16) | (v >> 24)) & 0xFFu;
+          const int nt = ct + 8 + (int)p;
+          nflag = p < 8u && nt < T ? (uint32_t)__ldg(flags + nt) : 0u;
+        }
+        const uint32_t token = cp_wait<D - 1>();  // all but the newest D - 1 groups have landed: this tile's has
+        uint32_t rr[R], cc[Geo::NC], w[2 * R];
+        asm("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(rr[0]), "=r"(rr[1]), "=r"(rr[2]), "=r"(rr[3]) : "r"(at), "r"(token));
+        asm("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(cc[0]), "=r"(cc[1]) : "r"(at + to_codes), "r"(token));
+#pragma unroll
+        for (int i = 0; i < R; i++) {
+          const uint32_t c = (i & 1) ? cc[i >> 1] >> 16 : cc[i >> 1];
+          w[2 * i] = (__byte_perm(rr[i], 0u, 0x1100) & 0x807F807Fu) | lut_read(me.lut + ((c << 7) & 0x7F80u), me.ready);
+          w[2 * i + 1] = (__byte_perm(rr[i], 0u, 0x3322) & 0x807F807Fu) | lut_read(me.lut + ((c >> 1) & 0x7F80u), me.ready);
+        }
+        if ((fm >> (ct & 7)) & 1u) oct_patch<R>(epos, ew, w, cc, me);
+        if (partial && ct == T - 1 && p >= pmax) {  // past the row's end: zeros (the columns of X there are zeros too, but 0 x Inf must not happen)
+#pragma unroll
+          for (int i = 0; i < 2 * R; i++) w[i] = 0u;
+        }
+        if (ct >= S && ok) ok = mm_bar_wait(win.empty + 8 * s, ph);
+        tc_fence_after();
+        const uint32_t a_s = a_at + (uint32_t)s * MMA_A_STAGE;
+        asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(a_s + a_off0), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]) : "memory");
+        asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(a_s + a_off1), "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7]) : "memory");
+        fence_async_smem();  // the tensor core reads shared memory through the async proxy
+        __syncwarp();
+        if (lane == 0) mm_bar_arrive(win.full + 8 * s);
+        if (++s == S) s = 0, ph ^= 1u;
+        load_tile(at);  // the slot just read takes the tile D further on
+      }
+    }
+    cp_wait<0>();
+  } else if (warp == MAXW) {
+    ok = mma_issue_side(&x_map, win, T, S, BN, tmem, lane, ok);
+  }
+  if (warp < 4) mma_store_side(a, win, tmem, warp, lane, row_base, rows, ok);
+  tc_fence_before();
+  __syncthreads();
+  if (warp == MAXW) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(a.tmem_cols) : "memory");
 }
 
 typedef CUresult (*TensorMapEncodeFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -308,18 +466,6 @@ int mma_rows(const bn_r4 *w, const uint16_t *x, int64_t x_stride, int64_t M, int
   a.T = (int)tiles(K), a.M = (int)M, a.BN = (int)((M + 15) / 16 * 16);
   a.tmem_cols = 32;
   while ((int)a.tmem_cols < a.BN) a.tmem_cols *= 2;
-  // an equal share of the rows for every SM, in whole warps' worth of rows
-  constexpr int dw = MMA_DECODE_WARPS, rpw = MMA_RPW;
-  int64_t rows = (N + mma_sms() - 1) / mma_sms();
-  rows = (rows + rpw - 1) / rpw * rpw;
-  if (rows > dw * rpw) rows = dw * rpw;
-  a.rows = (int)rows;
-  const uint32_t fixed = 1024 + LUT_WORDS * 4 + 256;  // alignment slack, pair table, barriers
-  const uint32_t per_stage = MMA_A_STAGE + (uint32_t)a.BN * MMA_BK * 2u;
-  int stages = (int)((MMA_SMEM_MAX - fixed) / per_stage);
-  if (stages > 4) stages = 4;
-  if (stages < 2) return -1;
-  a.stages = stages;
   // X as a 2-D tensor [M rows, K columns] of BF16; a box is 64 columns (one 128-byte swizzled row
   // each) of BN rows; rows past M and columns past K read as zeros
   CUtensorMap x_map;
@@ -327,6 +473,42 @@ int mma_rows(const bn_r4 *w, const uint16_t *x, int64_t x_stride, int64_t M, int
   const cuuint32_t box[2] = {64, (cuuint32_t)a.BN}, elem[2] = {1, 1};
   if (encode(&x_map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<uint16_t *>(x), dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
     return fail(BN_ERR_CUDA, "cuTensorMapEncodeTiled failed for the input rows");
+  const uint32_t fixed = 1024 + LUT_WORDS * 4 + 256;  // alignment slack, pair table, barriers
+  const uint32_t per_stage = MMA_A_STAGE + (uint32_t)a.BN * MMA_BK * 2u;
+  // eight threads per row where the rings fit beside at least two stages
+  if (K % 16 == 0 && !(((uintptr_t)w->raw | (uintptr_t)w->codes) & 15)) {
+    constexpr int ow = MMA_OCT_WARPS;
+    int64_t rows = (N + mma_sms() - 1) / mma_sms();
+    rows = (rows + 3) / 4 * 4;
+    if (rows > ow * 4) rows = ow * 4;
+    a.rows = (int)rows;
+    const unsigned grid = (unsigned)((N + rows - 1) / rows);
+    for (int slots = 4; slots >= 3; slots--) {
+      const uint32_t rings = (uint32_t)ow * slots * 768u;
+      if (fixed + rings + 2 * per_stage > MMA_SMEM_MAX) continue;
+      int stages = (int)((MMA_SMEM_MAX - fixed - rings) / per_stage);
+      a.stages = stages > 4 ? 4 : stages;
+      const uint32_t smem = fixed + rings + (uint32_t)a.stages * per_stage;
+      if (slots == 4) {
+        BN_CUDA(allow_smem(r4_mma_oct_kernel<ow, 4>, smem));
+        r4_mma_oct_kernel<ow, 4><<<grid, (ow + 1) * 32, smem, s>>>(x_map, a);
+      } else {
+        BN_CUDA(allow_smem(r4_mma_oct_kernel<ow, 3>, smem));
+        r4_mma_oct_kernel<ow, 3><<<grid, (ow + 1) * 32, smem, s>>>(x_map, a);
+      }
+      return launched("r4_mma_oct_kernel");
+    }
+  }
+  // an equal share of the rows for every SM, in whole warps' worth of rows
+  constexpr int dw = MMA_DECODE_WARPS, rpw = MMA_RPW;
+  int64_t rows = (N + mma_sms() - 1) / mma_sms();
+  rows = (rows + rpw - 1) / rpw * rpw;
+  if (rows > dw * rpw) rows = dw * rpw;
+  a.rows = (int)rows;
+  int stages = (int)((MMA_SMEM_MAX - fixed) / per_stage);
+  if (stages > 4) stages = 4;
+  if (stages < 2) return -1;
+  a.stages = stages;
   const uint32_t smem = fixed + (uint32_t)stages * per_stage;
   const unsigned grid = (unsigned)((N + rows - 1) / rows);
   BN_CUDA(allow_smem(r4_mma_kernel<dw, rpw>, smem));

@@ -529,6 +529,35 @@ def test_mma_rows_against_fp32(M, N, K):
     assert bool(((got - ref).abs() <= bound).all()), float(((got - ref).abs() - bound).max())
 
 
+@pytest.mark.parametrize("N,K,density", [(333, 1040, 0.0), (1000, 1200, 0.002), (260, 2064, 0.1), (15392, 640, 0.001), (120, 128, 0.5)])
+def test_mma_decodes_every_weight(N, K, density):
+    """The tensor-core path with eight threads per weight row (K % 16 == 0, M <= 128): one-hot
+    inputs over every column return every decoded weight exactly, with short last tiles, with
+    rows dense in escapes (window slides, several escapes per thread) and with the largest block
+    (104 rows on each of 148 SMs)."""
+    from binade_b200.cuda import r4
+
+    rng = np.random.default_rng(N + K)
+    u = weights(rng, (N, K), escapes=False)
+    if density:
+        rare = (0x5F80 + 0x80 * np.arange(60)).astype(np.uint16)  # 60 large finite exponents (no Inf: 0 x Inf would turn whole outputs into NaN): most of them escape
+        hit = rng.random(u.shape) < density
+        u[hit] = rng.choice(rare, int(hit.sum()))
+    m = r4.R4Linear(r4.transcode(packed_arrays(u)))
+    if density:
+        assert m._a["esc"].numel() - 1 > 0.5 * density * N * K
+    for M in (128, 64, 16):  # three ring depths / stage counts
+        for k0 in range(0, K, M):
+            n = min(M, K - k0)
+            x1 = torch.zeros((n, K), dtype=torch.bfloat16, device="cuda")
+            x1[torch.arange(n), torch.arange(k0, k0 + n)] = 1.0
+            want = u[:, k0 : k0 + n].T.copy()
+            want[want == 0x8000] = 0  # a sum that starts at +0 turns a lone -0 product into +0
+            assert np.array_equal(words(m.mma_rows(x1)), want), (M, k0)
+            if N > 2000 and k0 >= 2 * M:
+                break  # the big case: a few column blocks are enough
+
+
 def test_many_rows_rebuild_path():
     from binade_b200.cuda import r4
 
