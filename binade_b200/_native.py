@@ -18,7 +18,7 @@ _vp, _i64, _u64, _int = C.c_void_p, C.c_int64, C.c_uint64, C.c_int
 class R4Struct(C.Structure):
     """bn_r4: device pointers of one R4 matrix."""
 
-    _fields_ = [(n, _vp) for n in ("raw", "codes", "flags", "esc", "table", "row_esc")] + [("n_esc", _u64)]
+    _fields_ = [(n, _vp) for n in ("raw", "codes", "flags", "esc", "table", "row_esc")] + [("n_esc", _u64), ("esc_cols", _vp), ("col_esc", _vp)]
 
 
 _SIGNATURES = {
@@ -33,6 +33,7 @@ _SIGNATURES = {
         "bn_r4_finish": [_vp, _vp, _vp, _i64, _vp, _vp, _u64, _vp],
         "bn_rice_to_r4_static": [_vp, _vp, _u64, _vp, _vp, _i64, _i64, _vp, _vp, _vp, _vp, _u64, _vp, _vp],
         "bn_r4_decode": [C.POINTER(R4Struct), _i64, _i64, _i64, _i64, _i64, _vp, _vp],
+        "bn_r4_esc_columns": [C.POINTER(R4Struct), _i64, _i64, _vp, _vp, _vp],
         "bn_r4_lookup": [C.POINTER(R4Struct), _i64, _vp, _i64, _i64, _vp, _vp],
         "bn_rice_lookup": [_vp, _vp, _u64, _vp, _vp, _vp, _i64, _i64, _vp, _i64, _vp, _vp],
         "bn_f1_offsets": [_vp, _vp, _u64, _i64, _i64, _vp, _vp, _vp, _vp, _vp],

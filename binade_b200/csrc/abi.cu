@@ -21,4 +21,4 @@ int fail_cuda(cudaError_t e, const char *where) {
 }  // namespace bn
 
 extern "C" const char *bn_last_error(void) { return bn::g_error; }
-extern "C" int bn_abi_version(void) { return 200; }
+extern "C" int bn_abi_version(void) { return 201; }

@@ -134,11 +134,35 @@ __device__ __forceinline__ uint32_t escape_general(uint32_t (&w)[2 * R], uint32_
   return tot;
 }
 
+// Column-ordered escapes (bn_r4::esc_cols, col_esc): a thread walks the stream of a column it owns
+// with a cursor of its own; `word` is the aligned word of esc_cols that holds byte q.
+struct EscStream {
+  uint32_t q, word;
+};
+__device__ __forceinline__ void stream_open(EscStream &e, const uint8_t *__restrict__ esc_cols, uint32_t q) {
+  e.q = q;
+  e.word = __ldg(reinterpret_cast<const uint32_t *>(esc_cols + (q & ~3u)));
+}
+// Applies the escapes h (bit 4j: weight j of the column's eight in this tile) to the pair words
+// w[B .. B+3]. Threads call it on their own (no warp-wide operation inside).
+template <int B, int N>
+__device__ __forceinline__ void stream_patch(uint32_t h, EscStream &e, const uint8_t *__restrict__ esc_cols, uint32_t (&w)[N]) {
+  do {
+    const uint32_t bit = (uint32_t)__ffs((int)h) - 1u;
+    const uint32_t v = __byte_perm(e.word, 0u, 0x4440u | (e.q & 3u));
+    or_into<B>(bit >> 3, v << (7u + ((bit & 4u) << 2)), w);
+    e.q++;
+    if ((e.q & 3u) == 0) e.word = __ldg(reinterpret_cast<const uint32_t *>(esc_cols + e.q));  // used at the column's next escape at the earliest
+    h &= h - 1u;
+  } while (h);
+}
+
 // What a thread needs to know about itself and its row's matrix while it decodes.
 struct OctSelf {
   uint32_t lane, lane_hi, to_codes, lut, ready, gmask, ltg;  // lane_hi: first lane of this thread's row
   const uint8_t *esc;
   uint64_t esc_cap;
+  const uint8_t *esc_cols;
 };
 
 // Applies a flagged tile's escapes to the pair words w of this thread (cc: its code registers)

@@ -106,6 +106,7 @@ struct OctRow {
   float acc[R];
   uint32_t epos;  // the row's escape cursor
   EscWindow win;
+  EscStream col[(R + 1) / 2];  // with column-ordered escapes instead: one stream per code register
 };
 
 // One tile of this thread's row, decoded: pair words (escapes not yet applied), the matching
@@ -132,9 +133,20 @@ __device__ __forceinline__ void oct_decode(OctTile<R> &t, const OctSelf &me, uin
 // Applies the tile's escapes, if any row of the warp has some, and adds its products.
 //   flagged  some row of the warp holds a code 15 in this tile (warp-uniform)
 //   live     this thread holds weights in the tile (false only in a row's short last tile)
-template <int R>
+template <int R, bool COLS>
 __device__ __forceinline__ void oct_finish(OctRow<R> &s, OctTile<R> &t, const OctSelf &me, bool flagged, bool live) {
-  if (flagged) oct_patch<R>(s.epos, s.win, t.w, t.cc, me);
+  if (flagged) {
+    if constexpr (COLS) {
+      const uint32_t h0 = hits15(t.cc[0]);
+      if (h0) stream_patch<0>(h0, s.col[0], me.esc_cols, t.w);
+      if constexpr (R == 4) {
+        const uint32_t h1 = hits15(t.cc[1]);
+        if (h1) stream_patch<4>(h1, s.col[1], me.esc_cols, t.w);
+      }
+    } else {
+      oct_patch<R>(s.epos, s.win, t.w, t.cc, me);
+    }
+  }
   if (live) {  // columns >= K are skipped, not added as zeros
 #pragma unroll
     for (int i = 0; i < R; i++) s.acc[i] = fma2_bf16(t.w[2 * i + 1], t.xx[2 * i + 1], fma2_bf16(t.w[2 * i], t.xx[2 * i], s.acc[i]));
@@ -145,8 +157,9 @@ __device__ __forceinline__ void oct_finish(OctRow<R> &s, OctTile<R> &t, const Oc
 // warps a block may have (bounds the registers). Both sides of the ring move in quads: a quad
 // holds up to four consecutive tiles of one row (fewer at the row's end), so slot addresses
 // inside a quad are immediates.
-template <int R, int NQ, int MAXW>
+template <int R, int NQ, int MAXW, bool COLS>
 __global__ void __launch_bounds__(MAXW * 32, 1) r4_oct_kernel(const __grid_constant__ OctArgs a) {
+  static_assert(!COLS || R > 1, "a column (eight weights) is owned by one thread only with two or four rows a warp");
   using Geo = OctGeom<R>;
   constexpr uint32_t SLOT = Geo::SLOT, QUAD = Geo::QUAD;
   extern __shared__ __align__(128) uint8_t smem_raw[];
@@ -193,12 +206,13 @@ __global__ void __launch_bounds__(MAXW * 32, 1) r4_oct_kernel(const __grid_const
   int pt = 0;
   bool plive = pg < G;
   const uint8_t *praw = nullptr, *pcode = nullptr;
-  uint32_t m_flag = 0, m_epos = 0;  // next group's first flag byte of this thread, escape cursor
+  uint32_t m_flag = 0, m_epos = 0, m_col = 0;  // next group's first flag byte of this thread, escape cursor, column starts
   auto aim = [&]() {  // point the load side at group pg and fetch its small per-row data
     const int64_t srow = row0 + min(row_of(pg), N - 1);
     praw = mat.raw + srow * K + p * (4u * R);
     pcode = reinterpret_cast<const uint8_t *>(mat.codes) + srow * row_codes + p * (2u * R);
     m_epos = __ldg(mat.row_esc + srow);
+    if constexpr (COLS) m_col = R == 4 ? __ldg(reinterpret_cast<const uint32_t *>(mat.col_esc + srow * 16) + p) : (uint32_t)__ldg(mat.col_esc + srow * 16 + p);
     m_flag = p < 8u && (int)p < T ? (uint32_t)__ldg(mat.flags + srow * T + p) : 0u;
   };
   // tiles of the load side's next quad
@@ -221,7 +235,7 @@ __global__ void __launch_bounds__(MAXW * 32, 1) r4_oct_kernel(const __grid_const
   };
 
   if (plive) aim();
-  uint32_t c_epos = m_epos, c_flag = m_flag;  // the first group's, before the load side moves on
+  uint32_t c_epos = m_epos, c_flag = m_flag, c_col = m_col;  // the first group's, before the load side moves on
 #pragma unroll
   for (int q = 0; q < NQ; q++) {
     const int n = load_count();
@@ -269,7 +283,7 @@ __global__ void __launch_bounds__(MAXW * 32, 1) r4_oct_kernel(const __grid_const
   int ct = 0;        // tile of it
   int64_t c_r = row_of(cg);
   const uint8_t *c_flags = nullptr;  // flag bytes of this thread's row
-  me.esc = mat.esc, me.esc_cap = mat.n_esc + 1;
+  me.esc = mat.esc, me.esc_cap = mat.n_esc + 1, me.esc_cols = mat.esc_cols;
   uint32_t fm = 0;      // bit u: some row of the warp flags tile (ct & ~7) + u
   uint32_t nflag = 0;   // this thread's flag byte of the next block of eight tiles (threads p < 8)
   uint32_t xs = xs0;
@@ -279,8 +293,13 @@ __global__ void __launch_bounds__(MAXW * 32, 1) r4_oct_kernel(const __grid_const
     c_flags = mat.flags + srow * T;
     s.epos = c_epos;
     nflag = c_flag;
-    s.win.base = s.epos & ~3u;
-    s.win.word = window_load(me.esc, me.esc_cap, s.win.base + p * 4u);
+    if constexpr (COLS) {  // this thread's columns: 2p and 2p + 1 (R = 4: both halves of c_col) or p
+      stream_open(s.col[0], me.esc_cols, c_epos + (c_col & 0xFFFFu));
+      if constexpr (R == 4) stream_open(s.col[1], me.esc_cols, c_epos + (c_col >> 16));
+    } else {
+      s.win.base = s.epos & ~3u;
+      s.win.word = window_load(me.esc, me.esc_cap, s.win.base + p * 4u);
+    }
     xs = xs0;
 #pragma unroll
     for (int i = 0; i < R; i++) s.acc[i] = 0.0f;
@@ -314,7 +333,7 @@ __global__ void __launch_bounds__(MAXW * 32, 1) r4_oct_kernel(const __grid_const
     if (cg >= G) return false;
     ct = 0;
     c_r = row_of(cg);
-    c_epos = m_epos, c_flag = m_flag;  // fetched when the load side crossed into this group
+    c_epos = m_epos, c_flag = m_flag, c_col = m_col;  // fetched when the load side crossed into this group
     begin_group();
     return true;
   };
@@ -336,10 +355,10 @@ __global__ void __launch_bounds__(MAXW * 32, 1) r4_oct_kernel(const __grid_const
       // four whole tiles; each slot is refilled, with a tile of the quad NQ ahead, once the quad
       // is read
       OctTile<R> t;
-      oct_decode<R, 0>(t, me, at, xs, token), oct_finish<R>(s, t, me, fq & 1u, true);
-      oct_decode<R, 1>(t, me, at, xs, token), oct_finish<R>(s, t, me, fq & 2u, true);
-      oct_decode<R, 2>(t, me, at, xs, token), oct_finish<R>(s, t, me, fq & 4u, true);
-      oct_decode<R, 3>(t, me, at, xs, token), oct_finish<R>(s, t, me, fq & 8u, true);
+      oct_decode<R, 0>(t, me, at, xs, token), oct_finish<R, COLS>(s, t, me, fq & 1u, true);
+      oct_decode<R, 1>(t, me, at, xs, token), oct_finish<R, COLS>(s, t, me, fq & 2u, true);
+      oct_decode<R, 2>(t, me, at, xs, token), oct_finish<R, COLS>(s, t, me, fq & 4u, true);
+      oct_decode<R, 3>(t, me, at, xs, token), oct_finish<R, COLS>(s, t, me, fq & 8u, true);
       if (R == 1) __syncwarp();  // the neighbour's reads too
       if (pn > 0) copy_tile<R, 0>(at, to_codes, praw, pcode, code_lane, s.acc[0]);
       if (pn > 1) copy_tile<R, 1>(at, to_codes, praw, pcode, code_lane, s.acc[0]);
@@ -350,7 +369,7 @@ __global__ void __launch_bounds__(MAXW * 32, 1) r4_oct_kernel(const __grid_const
         const bool live = !(partial && ct + u == T - 1) || p < pmax;
         OctTile<R> t;
         oct_decode<R, 0>(t, me, at + u * SLOT, xs + u * 512u, token);
-        oct_finish<R>(s, t, me, (fq >> u) & 1u, live);
+        oct_finish<R, COLS>(s, t, me, (fq >> u) & 1u, live);
       }
       if (R == 1) __syncwarp();
       load_quad_slow(at, pn, s.acc[0]);
@@ -385,9 +404,9 @@ uint32_t oct_smem(uint32_t warps, uint32_t ring) {
   return need <= OC_SMEM_MAX ? need : 0;
 }
 
-template <int R, int NQ, int MAXW>
-int launch_oct_as(OctArgs a, unsigned blocks, unsigned slots, unsigned warps, cudaStream_t s) {
-  auto kern = r4_oct_kernel<R, NQ, MAXW>;
+template <int R, int NQ, int MAXW, bool COLS>
+int launch_oct_with(OctArgs a, unsigned blocks, unsigned slots, unsigned warps, cudaStream_t s) {
+  auto kern = r4_oct_kernel<R, NQ, MAXW, COLS>;
   a.smem = oct_smem(warps, NQ * OctGeom<R>::QUAD);
   if (!a.smem || warps > MAXW || NQ * 4 >= a.T) return -1;  // the ring must be shorter than a row (see the kernel's load side)
   BN_CUDA(allow_smem(kern, OC_SMEM_MAX));
@@ -399,6 +418,17 @@ int launch_oct_as(OctArgs a, unsigned blocks, unsigned slots, unsigned warps, cu
   cfg.attrs = attr, cfg.numAttrs = 1;
   BN_CUDA(cudaLaunchKernelEx(&cfg, kern, a));
   return launched("r4_oct_kernel");
+}
+
+// The variant for column-ordered escapes when every matrix of the launch carries them.
+template <int R, int NQ, int MAXW>
+int launch_oct_as(const OctArgs &a, unsigned blocks, unsigned slots, unsigned warps, cudaStream_t s) {
+  if constexpr (R > 1) {
+    bool cols = true;
+    for (int i = 0; i < a.nmat; i++) cols = cols && a.w[i].esc_cols && a.w[i].col_esc;
+    if (cols) return launch_oct_with<R, NQ, MAXW, true>(a, blocks, slots, warps, s);
+  }
+  return launch_oct_with<R, NQ, MAXW, false>(a, blocks, slots, warps, s);
 }
 
 // Rows a warp walks side by side for `rows` output rows spread over `blocks` blocks: four when
@@ -481,7 +511,7 @@ static int oct_launch(OctArgs &a, int64_t slots, cudaStream_t s) {
 }
 
 static bool oct_aligned(const bn_r4 *w, const uint16_t *x) {
-  return ((reinterpret_cast<uintptr_t>(w->raw) | reinterpret_cast<uintptr_t>(w->codes) | reinterpret_cast<uintptr_t>(x)) & 15) == 0 && (reinterpret_cast<uintptr_t>(w->esc) & 3) == 0;
+  return ((reinterpret_cast<uintptr_t>(w->raw) | reinterpret_cast<uintptr_t>(w->codes) | reinterpret_cast<uintptr_t>(x)) & 15) == 0 && ((reinterpret_cast<uintptr_t>(w->esc) | reinterpret_cast<uintptr_t>(w->esc_cols) | reinterpret_cast<uintptr_t>(w->col_esc)) & 3) == 0;
 }
 
 // Up to four matrices of the same K against one x; -1 when the shape is outside the kernel's coverage.

@@ -54,7 +54,24 @@ def _call(fn, *args):
 
 
 def r4_struct(a: dict) -> _native.R4Struct:
-    return _native.R4Struct(*(a[k].data_ptr() for k in R4_KEYS), a["esc"].numel() - 1)
+    """bn_r4 of an R4 dict; the column-ordered escapes ride along when the dict holds them."""
+    cols = (a["esc_cols"].data_ptr(), a["col_esc"].data_ptr()) if "esc_cols" in a else (None, None)
+    return _native.R4Struct(*(a[k].data_ptr() for k in R4_KEYS), a["esc"].numel() - 1, *cols)
+
+
+def r4_esc_columns(a: dict) -> None:
+    """Adds `esc_cols` (uint8 [n_esc + 8]) and `col_esc` (int16-typed uint16 [rows, 16]) to an R4
+    dict: every row's escape bytes regrouped by column of eight weights, which lets a thread of
+    the batch-1 kernels walk its own escapes (bn_r4_esc_columns). Shapes the kernels do not take
+    (K % 16) are left alone."""
+    rows, K = a["raw"].shape
+    if "esc_cols" in a or K % 16 or K > 65520:
+        return
+    dev = a["raw"].device
+    esc_cols = torch.empty(a["esc"].numel() - 1 + 8, dtype=torch.uint8, device=dev)
+    col_esc = torch.empty((rows, 16), dtype=torch.int16, device=dev)
+    _call("bn_r4_esc_columns", ctypes.byref(r4_struct(a)), rows, K, _p(esc_cols), _p(col_esc))
+    a["esc_cols"], a["col_esc"] = esc_cols, col_esc
 
 
 def rice_ranks(meta: torch.Tensor, bits: torch.Tensor, roff: torch.Tensor, K: int):

@@ -146,6 +146,7 @@ class _R4:
         self._a = a
         self.N, self.K = a["raw"].shape
         self.T = -(-self.K // TILE)
+        ck.r4_esc_columns(a)  # derived once per matrix: the batch-1 kernels walk escapes by column
         self._struct = ck.r4_struct(a)  # device addresses of the arrays above, which this object keeps alive
 
     def _matvec(self, x: torch.Tensor) -> torch.Tensor:

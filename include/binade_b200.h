@@ -47,7 +47,15 @@ int bn_abi_version(void);
  *   table   [256]      exponent by rank (only entries 0..14 are read by the kernels)
  *   row_esc [N]        number of escapes before each row
  *   n_esc              escapes in `esc` (which holds n_esc + 1 bytes): lets the kernels fetch a
- *                      row's escape bytes ahead of use without reading past the array        */
+ *                      row's escape bytes ahead of use without reading past the array
+ * Not part of the reference's layout, optional (NULL: the kernels use `esc`), derived from the
+ * arrays above by bn_r4_esc_columns for the batch-1 kernels:
+ *   esc_cols [n_esc+8] the same escape bytes with every row's run reordered by column: first
+ *                      the escapes of weights k with (k % 128) / 8 == 0 in row order, then
+ *                      those of column 1, ... 15; zero padding behind
+ *   col_esc  [N*16]    where column c of row r starts, counted from row_esc[r]
+ * With these a thread that owns a column of a row walks its escape bytes with a cursor of its
+ * own, instead of the row's threads agreeing on positions with ballots for every flagged tile. */
 typedef struct bn_r4 {
   const uint8_t *raw;
   const uint16_t *codes;
@@ -56,6 +64,8 @@ typedef struct bn_r4 {
   const uint8_t *table;
   const uint32_t *row_esc;
   uint64_t n_esc;
+  const uint8_t *esc_cols;   /* optional (both or neither, else NULL): see bn_r4_esc_columns */
+  const uint16_t *col_esc;
 } bn_r4;
 
 /* ------------------------------------------------------------------ 2. CUDA entry points -- */
@@ -119,6 +129,12 @@ int bn_r4_finish(const uint32_t *row_cnt, const uint8_t *esc_tmp, const uint32_t
 int bn_rice_to_r4_static(const uint8_t *meta, const uint32_t *bits, uint64_t nwords, const uint32_t *roff,
                          const uint8_t *table, int64_t R, int64_t K, uint16_t *codes, uint8_t *flags,
                          uint32_t *row_esc, uint8_t *esc, uint64_t esc_cap, uint32_t *info, void *stream);
+
+/* Column-ordered escapes of an R4 matrix of N rows (see bn_r4): esc_cols [w->n_esc + 8] (4-byte
+ * aligned) and col_esc [N*16] from w's codes, flags, esc and row_esc. K % 16 == 0. The caller
+ * stores the two pointers into its bn_r4 afterwards. */
+int bn_r4_esc_columns(const bn_r4 *w, int64_t N, int64_t K, uint8_t *esc_cols, uint16_t *col_esc,
+                      void *stream);
 
 /* R4 -> dense BF16 [N,K]; output row r is storage row (r / NB) * RS + R0 + r % NB.
  * Replaces r4_decode, binade/mlx/cuda_kernels.py:897-916. */

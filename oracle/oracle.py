@@ -420,6 +420,32 @@ def c_ranks_of(w):
     return raw, table, ranks
 
 
+def esc_columns(a: dict):
+    """The derived arrays of bn_r4_esc_columns for an R4 dict of this module: (esc_cols uint8
+    [n_esc + 8], col_esc uint16 [R, 16]). Every row's run of escape bytes is regrouped by column
+    c = (k % 128) // 8 of the escaped weight k (row order kept inside a column); col_esc[r, c]
+    counts the row's escapes in columns below c. Not a reference structure: it restates the
+    definition in include/binade_b200.h so that the GPU builder can be checked."""
+    K = a["shape"][-1]
+    R = a["row_esc"].size
+    T = -(-K // TILE)
+    codes = np.ascontiguousarray(a["codes"], np.uint16).reshape(R, T * 32)
+    nib = np.stack([(codes >> (4 * j)) & 15 for j in range(4)], axis=-1).reshape(R, T * TILE)
+    rows, ks = np.nonzero(nib == 15)  # row-major: the order of `esc`
+    col = (ks % TILE) // 8
+    n = rows.size
+    esc = np.ascontiguousarray(a["esc"], np.uint8)
+    if n != esc.size - 1:
+        raise ValueError(f"{n} codes 15 but {esc.size - 1} escape bytes")
+    order = np.lexsort((np.arange(n), col, rows))
+    esc_cols = np.zeros(n + 8, np.uint8)
+    esc_cols[:n] = esc[:n][order]
+    per = np.zeros((R, 16), np.int64)
+    np.add.at(per, (rows, col), 1)
+    col_esc = (np.cumsum(per, axis=1) - per).astype(np.uint16)
+    return esc_cols, col_esc
+
+
 def pack_r4(w: np.ndarray) -> dict:
     """BF16 words [R,K] -> full R4 dict via the C oracle (for building kernel test inputs)."""
     R, K = w.shape

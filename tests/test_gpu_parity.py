@@ -408,6 +408,37 @@ def test_matvec_rows_dense_with_escapes(dense_escapes):
     assert np.array_equal(words(got)[0], o.c_r4_matvec(want, xw[0], N, K))
 
 
+@pytest.mark.parametrize("N,K,density", [(2200, 1280, 0.02), (2200, 1280, 0.5), (15392, 640, 0.003), (5000, 1200, 0.01), (300, 2064, 0.2), (37, 768, 0.05)])
+def test_escape_columns_and_both_layouts(N, K, density):
+    """bn_r4_esc_columns against its definition restated in numpy, and the one-row kernel with and
+    without the derived arrays (a thread walking its own column of escapes, or the row's threads
+    agreeing on positions): the same bits, for four and two rows a warp, short last tiles, rows
+    with hundreds of escapes and several escapes in one code word."""
+    from binade_b200.cuda import kernels as ck
+    from binade_b200.cuda import r4
+
+    rng = np.random.default_rng(N + K)
+    u = weights(rng, (N, K))
+    rare = bf16_words((2.0 ** np.arange(-60, 60, 1.5)).astype(np.float32))
+    hit = rng.random((N, K)) < density
+    u[hit] = rare[rng.integers(0, len(rare), int(hit.sum()))]
+    a = r4.transcode(packed_arrays(u))
+    plain = dict(a)  # the standard arrays only
+    ck.r4_esc_columns(a)
+    want = o.pack_r4(u)
+    esc_cols, col_esc = o.esc_columns(want)
+    n = want["esc"].size - 1
+    assert n > 0.5 * density * N * K
+    assert np.array_equal(a["esc_cols"].cpu().numpy(), esc_cols)
+    assert np.array_equal(a["col_esc"].cpu().numpy().view(np.uint16), col_esc)
+    xw = bf16_words(rng.standard_normal((1, K)) * 1e-3)
+    x = dev(xw).view(torch.bfloat16)
+    y = o.c_r4_matvec(want, xw[0], N, K)
+    assert "esc_cols" not in plain
+    assert np.array_equal(words(ck.r4_matvec(plain, x, N, K))[0], y)
+    assert np.array_equal(words(ck.r4_matvec(a, x, N, K))[0], y)
+
+
 def test_linear_group_one_launch():
     """q, k, v (and gate, up) through bn_r4_rows_multi: the same bits as one call per matrix,
     for group sizes 1..4, unequal row counts, and a row count that is not a multiple of four."""

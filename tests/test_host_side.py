@@ -31,7 +31,7 @@ def test_abi_exports_every_declared_symbol():
             assert hasattr(lib, name), name
             exported.add(name)
     assert declared == exported
-    assert _native.load("cuda").bn_abi_version() == 200
+    assert _native.load("cuda").bn_abi_version() == 201
 
 
 def test_bad_arguments_are_refused_without_a_gpu():
