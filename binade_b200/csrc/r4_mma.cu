@@ -299,7 +299,7 @@ __global__ void __launch_bounds__((DW + 1) * 32, 1) r4_mma_kernel(const __grid_c
 // kernel above (one 16-byte and one 8-byte shared load bring what eight 4-byte and 2-byte global
 // loads brought; the escape patch runs once per four rows), which is what bounds both. Takes
 // M <= 128 (the rings need the shared memory that wider B stages would use) and K % 16 == 0.
-template <int MAXW, int D>
+template <int MAXW, int D, bool COLS>
 __global__ void __launch_bounds__((MAXW + 1) * 32, 1) r4_mma_oct_kernel(const __grid_constant__ CUtensorMap x_map, MmaArgs a) {
   constexpr int R = 4;
   using Geo = OctGeom<R>;
@@ -371,12 +371,19 @@ __global__ void __launch_bounds__((MAXW + 1) * 32, 1) r4_mma_oct_kernel(const __
     asm volatile("mov.u32 %0, 0;" : "=r"(me.ready)::"memory");  // after the barrier: orders the table reads
     me.lane = lane, me.lane_hi = lane & ~7u, me.to_codes = to_codes, me.lut = lut_at + lane * 4u;
     me.gmask = 0xFFu << (grp * 8u), me.ltg = me.gmask & lanemask_lt();
-    me.esc = a.w.esc, me.esc_cap = a.w.n_esc + 1;
+    me.esc = a.w.esc, me.esc_cap = a.w.n_esc + 1, me.esc_cols = a.w.esc_cols;
     const uint8_t *const flags = a.w.flags + srow * T;
     uint32_t epos = __ldg(a.w.row_esc + srow);
-    EscWindow ew;
-    ew.base = epos & ~3u;
-    ew.word = window_load(me.esc, me.esc_cap, ew.base + p * 4u);
+    EscWindow ew{};
+    EscStream col[2]{};  // with column-ordered escapes: this thread's columns 2p and 2p + 1
+    if constexpr (COLS) {
+      const uint32_t starts = __ldg(reinterpret_cast<const uint32_t *>(a.w.col_esc + srow * 16) + p);
+      stream_open(col[0], a.w.esc_cols, epos + (starts & 0xFFFFu));
+      stream_open(col[1], a.w.esc_cols, epos + (starts >> 16));
+    } else {
+      ew.base = epos & ~3u;
+      ew.word = window_load(me.esc, me.esc_cap, ew.base + p * 4u);
+    }
     uint32_t nflag = p < 8u && (int)p < T ? (uint32_t)__ldg(flags + p) : 0u;  // this thread's flag byte of the next block of eight tiles
     uint32_t fm = 0;
     // the two 16-byte chunks of this thread in a stage: k 16p .. 16p+7 and 16p+8 .. 16p+15 of row r
@@ -406,7 +413,15 @@ __global__ void __launch_bounds__((MAXW + 1) * 32, 1) r4_mma_oct_kernel(const __
           w[2 * i] = (__byte_perm(rr[i], 0u, 0x1100) & 0x807F807Fu) | lut_read(me.lut + ((c << 7) & 0x7F80u), me.ready);
           w[2 * i + 1] = (__byte_perm(rr[i], 0u, 0x3322) & 0x807F807Fu) | lut_read(me.lut + ((c >> 1) & 0x7F80u), me.ready);
         }
-        if ((fm >> (ct & 7)) & 1u) oct_patch<R>(epos, ew, w, cc, me);
+        if ((fm >> (ct & 7)) & 1u) {
+          if constexpr (COLS) {
+            const uint32_t h0 = hits15(cc[0]), h1 = hits15(cc[1]);
+            if (h0) stream_patch<0>(h0, col[0], a.w.esc_cols, w);
+            if (h1) stream_patch<4>(h1, col[1], a.w.esc_cols, w);
+          } else {
+            oct_patch<R>(epos, ew, w, cc, me);
+          }
+        }
         if (partial && ct == T - 1 && p >= pmax) {  // past the row's end: zeros (the columns of X there are zeros too, but 0 x Inf must not happen)
 #pragma unroll
           for (int i = 0; i < 2 * R; i++) w[i] = 0u;
@@ -489,13 +504,10 @@ int mma_rows(const bn_r4 *w, const uint16_t *x, int64_t x_stride, int64_t M, int
       int stages = (int)((MMA_SMEM_MAX - fixed - rings) / per_stage);
       a.stages = stages > 4 ? 4 : stages;
       const uint32_t smem = fixed + rings + (uint32_t)a.stages * per_stage;
-      if (slots == 4) {
-        BN_CUDA(allow_smem(r4_mma_oct_kernel<ow, 4>, smem));
-        r4_mma_oct_kernel<ow, 4><<<grid, (ow + 1) * 32, smem, s>>>(x_map, a);
-      } else {
-        BN_CUDA(allow_smem(r4_mma_oct_kernel<ow, 3>, smem));
-        r4_mma_oct_kernel<ow, 3><<<grid, (ow + 1) * 32, smem, s>>>(x_map, a);
-      }
+      const bool cols = w->esc_cols && w->col_esc && !(((uintptr_t)w->esc_cols | (uintptr_t)w->col_esc) & 3);
+      auto kern = slots == 4 ? (cols ? r4_mma_oct_kernel<ow, 4, true> : r4_mma_oct_kernel<ow, 4, false>) : (cols ? r4_mma_oct_kernel<ow, 3, true> : r4_mma_oct_kernel<ow, 3, false>);
+      BN_CUDA(allow_smem(kern, smem));
+      kern<<<grid, (ow + 1) * 32, smem, s>>>(x_map, a);
       return launched("r4_mma_oct_kernel");
     }
   }

@@ -246,8 +246,8 @@ __global__ void __launch_bounds__(MAXW * 32, 1) r4_oct_kernel(const __grid_const
 
   // ---- x and the pair table into shared memory (whole block)
   {
-    if (threadIdx.x < 16) s_tab[threadIdx.x] = threadIdx.x < 15 ? (uint32_t)__ldg(mat.table + threadIdx.x) : 0u;
     pdl_wait();  // x may be the previous kernel's output; the weights above are not
+    const uint32_t tab = threadIdx.x < 15 ? (uint32_t)__ldg(mat.table + threadIdx.x) : 0u;  // in flight together with the loads of x below
     // x: a tile's 256 bytes sit in the unused halves of table entries 2t and 2t+1, placed so that
     // the threads of a row cover all banks with each of their reads: with R = 4, thread p reads
     // values 16p .. 16p+7 from the first half and 16p+8 .. 16p+15 from the second, both at byte
@@ -259,6 +259,7 @@ __global__ void __launch_bounds__(MAXW * 32, 1) r4_oct_kernel(const __grid_const
       const uint32_t half = R == 4 ? q & 1u : q >> 3, piece = R == 4 ? q >> 1 : q & 7u;
       *reinterpret_cast<uint4 *>(smem_raw + (OC_LUT - base) + (2u * t + half) * 256u + 128u + piece * 16u) = v;
     }
+    if (threadIdx.x < 16) s_tab[threadIdx.x] = tab;
     __syncthreads();
     // entry `code` holds table[code & 15] << 7 | table[code >> 4] << 23 in each of its 32 lanes'
     // words: one 16-byte store writes four lanes

@@ -437,6 +437,8 @@ def test_escape_columns_and_both_layouts(N, K, density):
     assert "esc_cols" not in plain
     assert np.array_equal(words(ck.r4_matvec(plain, x, N, K))[0], y)
     assert np.array_equal(words(ck.r4_matvec(a, x, N, K))[0], y)
+    xm = dev(bf16_words(rng.standard_normal((16, K)) * 1e-3)).view(torch.bfloat16)  # the tensor-core kernel, both layouts
+    assert np.array_equal(words(ck.r4_mma(plain, xm, N, K)), words(ck.r4_mma(a, xm, N, K)))
 
 
 def test_linear_group_one_launch():
