@@ -40,6 +40,7 @@ NOMINAL_HBM_GBS = 8000.0
 # DRAM bytes (read + write) over algorithmic bytes of one matvec launch, from one ncu capture of
 # the batch-1 kernel on the gate matrix (89.1 MB read + 3.9 MB written for 89.06 MB); the JSON
 # line labels the figure as assumed from that capture, scaled to the average launch by bytes.
+GRAPH_ROUNDS = 8  # a timed graph holds this many steps per weight copy
 NCU_TRAFFIC_RATIO = 93.0 / 89.06
 OUTLIERS = 1e-3  # fraction of weights scaled x64 (the benchmark's distribution)
 GROUPS = (("q", "k", "v"), ("o",), ("gate", "up"), ("down",))  # projections sharing an input: one launch each
@@ -291,15 +292,21 @@ def run_ours(args) -> dict | None:
         exchanges = [make_exchange(max_bytes=2 * sum(by_name[nm][0] for nm in out_names) + 256) for c in range(copies)]
         pushed = exchanges[0] is not None
 
-        def step(i: int, inputs=None):
+        xstream = torch.cuda.Stream()  # the exchange's own stream in the timed region
+
+        def step(i: int, inputs=None, overlap: bool = False):
+            # overlap: the exchange of this step runs on `xstream` while the current stream goes
+            # on with the next step's products; the caller joins `xstream` before it ends
             inputs = inputs or xs
             slices = [y for grp, k in zip(stepper[i % copies], group_k) for y in grp(inputs[k], gather=False)]
-            return gather_all(slices, exchange=exchanges[i % copies])
+            return gather_all(slices, exchange=exchanges[i % copies], stream=xstream if overlap else None)
 
     else:
         stepper = [[r4.R4LinearGroup([by_name[nm][2][c] for nm in g]) for g in groups] for c in range(copies)]
 
-        def step(i: int, inputs=None):
+        xstream = None
+
+        def step(i: int, inputs=None, overlap: bool = False):
             inputs = inputs or xs
             return [y for grp, k in zip(stepper[i % copies], group_k) for y in grp(inputs[k])]
 
@@ -323,7 +330,7 @@ def run_ours(args) -> dict | None:
 
     note("parity checked")
     # ---- timed region: W warm-up steps, then exactly K steps as replays of a CUDA graph that
-    # holds one step per weight copy (plus a shorter graph for K % copies)
+    # holds GRAPH_ROUNDS steps per weight copy (plus a shorter graph for the remainder)
     for i in range(max(args.warmup, 3)):
         step(i)
     torch.cuda.synchronize()
@@ -336,17 +343,19 @@ def run_ours(args) -> dict | None:
             step(0)
             side.synchronize()
             with torch.cuda.graph(g, stream=side):
-                for i in range(n_steps):
-                    step(i)
+                outs = [step(i, overlap=True) for i in range(n_steps)]
+                if xstream is not None:
+                    side.wait_stream(xstream)  # the graph ends when its last exchange has
         torch.cuda.synchronize()
         g.replay()  # untimed: graph upload
         torch.cuda.synchronize()
-        return g
+        return g, outs
 
     note("warm-up done")
-    full, rem = divmod(args.steps, copies)
-    g_full = capture(copies) if full else None
-    g_rem = capture(rem) if rem else None
+    per_graph = copies * GRAPH_ROUNDS
+    full, rem = divmod(args.steps, per_graph)
+    g_full, outs_full = capture(per_graph) if full else (None, [])
+    g_rem, outs_rem = capture(rem) if rem else (None, [])
     note("graphs captured")
     if world > 1:
         dist.barrier()
@@ -371,6 +380,13 @@ def run_ours(args) -> dict | None:
     for ex in exchanges:
         if ex is not None:
             ex.check()  # a wait that ran out on any rank voids the run
+    # what the timed graphs left in their output buffers is what the checked eager step gives
+    for outs in (outs_full, outs_rem):
+        for c, got in enumerate(outs):
+            want = step(c)
+            torch.cuda.synchronize()
+            if not all(torch.equal(a, b) for a, b in zip(got, want)):
+                raise SystemExit(f"bench: the timed graph's outputs of step {c} differ from the checked step (rank {rank}); refusing to report a number")
     note(f"timed region done: {ms_per_step * 1e3:.1f} us per step")
     value = world * step_bytes / (ms_per_step * 1e-3) / 1e9
 
@@ -523,7 +539,7 @@ def run_ours(args) -> dict | None:
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
         "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16 weights (R4 coded), fp32 accumulate", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "copies_rotated": copies, "bytes_per_step": step_bytes, "launches_per_step": [" + ".join(g) for g in groups], "l2": f"each step streams {step_bytes / 1e6:.0f} MB of distinct weights (> 126 MB L2), {copies} copies rotated", "timing": "CUDA-graph replays (one step per weight copy per graph), CUDA events, max over ranks", "collective": ("peer-store all-gather kernel over NVLink (bn_push_gather)" if pushed else "NCCL all-gather") + " of the seven projection outputs, one per step" if world > 1 else "none"},
+        "config": {"workload": WORKLOAD, "copies_rotated": copies, "bytes_per_step": step_bytes, "launches_per_step": [" + ".join(g) for g in groups], "l2": f"each step streams {step_bytes / 1e6:.0f} MB of distinct weights (> 126 MB L2), {copies} copies rotated", "timing": f"CUDA-graph replays ({copies * GRAPH_ROUNDS} steps per graph, rotating the weight copies), CUDA events, max over ranks", "collective": ("peer-store all-gather kernel over NVLink (bn_push_gather)" if pushed else "NCCL all-gather") + " of the seven projection outputs, one per step, on a second stream: it overlaps the next step's products (steps are independent) and every graph ends after its last exchange" if world > 1 else "none"},
         "pct_of_nominal_8tbs": round(100 * value / world / NOMINAL_HBM_GBS, 2),
         "bits_per_weight": {"file_format2": round(bits_file / numel, 3), "r4_in_memory": round(bits_r4 / numel, 3)},
         "parity": parity,

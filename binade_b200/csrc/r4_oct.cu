@@ -253,11 +253,23 @@ __global__ void __launch_bounds__(MAXW * 32, 1) r4_oct_kernel(const __grid_const
     // values 16p .. 16p+7 from the first half and 16p+8 .. 16p+15 from the second, both at byte
     // 16p of the half; with R = 2 or 1 the tile is simply cut in two
     const uint4 *x8 = reinterpret_cast<const uint4 *>(a.x + (a.ei ? (int64_t)a.xi[slot] * K : 0));
-    for (int i = threadIdx.x; i < T * 16; i += blockDim.x) {
-      const uint32_t t = (uint32_t)i >> 4, q = (uint32_t)i & 15u;  // tile, 16-byte piece of the tile
-      const uint4 v = (int64_t)i * 8 < K ? __ldg(x8 + i) : make_uint4(0, 0, 0, 0);
-      const uint32_t half = R == 4 ? q & 1u : q >> 3, piece = R == 4 ? q >> 1 : q & 7u;
-      *reinterpret_cast<uint4 *>(smem_raw + (OC_LUT - base) + (2u * t + half) * 256u + 128u + piece * 16u) = v;
+    // (four loads in flight per thread: with few warps and a long row, one load per round would
+    // put several memory latencies in front of the first product)
+    constexpr int XB = 4;
+    for (int i0 = threadIdx.x; i0 < T * 16; i0 += blockDim.x * XB) {
+      uint4 v[XB];
+#pragma unroll
+      for (int j = 0; j < XB; j++) {
+        const int i = i0 + j * (int)blockDim.x;
+        v[j] = i < T * 16 && (int64_t)i * 8 < K ? __ldg(x8 + i) : make_uint4(0, 0, 0, 0);
+      }
+#pragma unroll
+      for (int j = 0; j < XB; j++) {
+        const int i = i0 + j * (int)blockDim.x;
+        const uint32_t t = (uint32_t)i >> 4, q = (uint32_t)i & 15u;  // tile, 16-byte piece of the tile
+        const uint32_t half = R == 4 ? q & 1u : q >> 3, piece = R == 4 ? q >> 1 : q & 7u;
+        if (i < T * 16) *reinterpret_cast<uint4 *>(smem_raw + (OC_LUT - base) + (2u * t + half) * 256u + 128u + piece * 16u) = v[j];
+      }
     }
     if (threadIdx.x < 16) s_tab[threadIdx.x] = tab;
     __syncthreads();

@@ -223,16 +223,27 @@ def make_exchange(group=None, max_bytes: int = 1 << 20):
     return ex if int(flag.item()) == 1 else None
 
 
-def gather_all(slices, group=None, exchange=None):
+def gather_all(slices, group=None, exchange=None, stream=None):
     """One collective for up to eight single-row slices [.., w_j] of evenly sharded projections:
     returns their full rows [.., world * w_j] in rank order = row order. Through the peer-store
     kernel when an exchange is given and the slices can be pushed as they are, else one library
-    all-gather of the slices laid side by side."""
+    all-gather of the slices laid side by side.
+
+    With `stream`, the collective runs there, ordered after the work already queued on the
+    current stream, and the current stream goes on without it (the next products overlap the
+    exchange). The caller makes whatever reads the results wait for `stream`
+    (`torch.cuda.current_stream().wait_stream(stream)`)."""
     import torch.distributed as dist
 
     world = dist.get_world_size(group)
     if world == 1:
         return list(slices)
+    if stream is not None:
+        stream.wait_stream(torch.cuda.current_stream())
+        for y in slices:
+            y.record_stream(stream)
+        with torch.cuda.stream(stream):
+            return gather_all(slices, group, exchange)
     if exchange is not None:
         fast = exchange.gather_rows(list(slices))
         if fast is not None:
