@@ -46,6 +46,11 @@ def _rank_main(rank: int, world: int, port: int, N: int, K: int, out_dir: str):
             ok = ok and torch.equal(a.view(torch.int16), full.view(torch.int16)) and torch.equal(b.view(torch.int16), full.view(torch.int16))
             both = bd.gather_all(grp(x, gather=False) + grp(x, gather=False), exchange=exchange)
             ok = ok and len(both) == 4 and all(torch.equal(t.view(torch.int16), full.view(torch.int16)) for t in both)
+            # the same collective on a stream of its own (the small-block kernel), joined afterwards
+            side = torch.cuda.Stream()
+            beside = bd.gather_all(grp(x, gather=False), exchange=exchange, stream=side)
+            torch.cuda.current_stream().wait_stream(side)
+            ok = ok and len(beside) == 2 and all(torch.equal(t.view(torch.int16), full.view(torch.int16)) for t in beside)
         if ex is not None:
             ex.check()
     with open(os.path.join(out_dir, f"ok{rank}"), "w") as f:
