@@ -37,11 +37,11 @@ SHAPES = [("q", 4096, 3840), ("k", 2048, 3840), ("v", 2048, 3840), ("o", 3840, 4
 WORKLOAD = "config2: Rice->R4 expansion + batch-1 fused R4 matvec, 7 matrices of a 12B-class layer (q 4096x3840, k/v 2048x3840, o 3840x4096, gate/up 15360x3840, down 3840x15360), N(0,0.02) BF16 with 0.1% x64 outliers, x ~ N(0,1)"
 METRIC, UNIT = "r4_matvec_hbm_gbs", "GB/s"
 NOMINAL_HBM_GBS = 8000.0
-# DRAM bytes (read + write) over algorithmic bytes of one matvec launch, from one ncu capture of
-# the batch-1 kernel on the gate matrix (89.1 MB read + 3.9 MB written for 89.06 MB); the JSON
-# line labels the figure as assumed from that capture, scaled to the average launch by bytes.
 GRAPH_ROUNDS = 8  # a timed graph holds this many steps per weight copy
-NCU_TRAFFIC_RATIO = 93.0 / 89.06
+# DRAM bytes (read + write) over algorithmic bytes of one matvec launch, from one ncu capture of
+# the batch-1 kernel on the gate matrix (89.6 MB read + 4.9 MB written for 89.06 MB); the JSON
+# line labels the figure as assumed from that capture, scaled to the average launch by bytes.
+NCU_TRAFFIC_RATIO = 94.5 / 89.06
 OUTLIERS = 1e-3  # fraction of weights scaled x64 (the benchmark's distribution)
 GROUPS = (("q", "k", "v"), ("o",), ("gate", "up"), ("down",))  # projections sharing an input: one launch each
 
@@ -217,8 +217,9 @@ def run_ours(args) -> dict | None:
 
     o.set_threads(cpu_cores())
     layers, expand_ms, expand_bytes, host_pack_s, bits_file, bits_r4 = [], 0.0, 0, 0.0, 0, 0
+    columns_ms = 0.0  # building the column-ordered escapes, per layer
     numel = 0
-    parity = {"matrices": 0, "expander_arrays": "bit-identical to the oracle", "dense_decode": "bit-identical to the source words", "matvec": "bit-identical to the oracle (documented order)"}
+    parity = {"matrices": 0, "expander_arrays": "bit-identical to the oracle", "escape_columns": "identical to their definition restated in numpy", "dense_decode": "bit-identical to the source words", "matvec": "bit-identical to the oracle (documented order)"}
     xs_host = {k: synthetic_input(k, 0) for k in {k for _, _, k in SHAPES}}  # every rank multiplies the same input, as row-sharded layers do
     for name, n, k in SHAPES:
         u = synthetic_weight(name, n, k, rank)
@@ -256,7 +257,18 @@ def run_ours(args) -> dict | None:
             if not (np.array_equal(as_np(got_t[0], np.uint16), want["codes"]) and np.array_equal(as_np(got_t[1], np.uint8), want["flags"]) and np.array_equal(as_np(got_t[2], np.uint8), want["esc"]) and np.array_equal(as_np(got_t[3], np.uint32), want["row_esc"])):
                 raise SystemExit(f"bench: expander output of {name} differs from the oracle; refusing to report a number")
         del scratch, codes, flags, esc
-        m0 = r4.R4Linear(a)
+        m0 = r4.R4Linear(a)  # adds the column-ordered escapes the batch-1 kernels walk (derived arrays, not in the reference's layout)
+        want_cols, want_starts = o.esc_columns(want)
+        if not (np.array_equal(as_np(a["esc_cols"], np.uint8), want_cols) and np.array_equal(as_np(a["col_esc"], np.uint16).reshape(n, 16), want_starts)):
+            raise SystemExit(f"bench: column-ordered escapes of {name} differ from their definition restated in numpy; refusing to report a number")
+        cols_tmp, starts_tmp = torch.empty_like(a["esc_cols"]), torch.empty_like(a["col_esc"])
+        ev0.record()
+        for _ in range(reps):
+            _native.call("cuda", "bn_r4_esc_columns", ctypes.byref(ck.r4_struct(a)), n, k, P(cols_tmp), P(starts_tmp), stream)
+        ev1.record()
+        torch.cuda.synchronize()
+        columns_ms += ev0.elapsed_time(ev1) / reps
+        del cols_tmp, starts_tmp
         if not np.array_equal(as_np(m0.dense().view(torch.int16), np.uint16).reshape(n, k), u):
             raise SystemExit(f"bench: dense decode of {name} differs from the source words; refusing to report a number")
         got_y = as_np(m0(ck.to_device(xs_host[k]).view(torch.bfloat16)).view(torch.int16), np.uint16)
@@ -546,7 +558,7 @@ def run_ours(args) -> dict | None:
         "shapes": per_shape,
         "launches": per_launch,
         "speedup_vs_bf16_gemv_per_token": round(sum(v["bf16_gemv_us"] for v in per_shape.values()) / sum(v["us"] for v in per_shape.values()), 3) if per_shape else None,
-        "expander": {"ms_per_layer": round(expand_ms, 3), "gbs": round(expand_bytes / expand_ms / 1e6, 1), "algorithmic_bytes": expand_bytes, "host_pack_s": round(host_pack_s, 2), "host_pack_cores": cpu_cores()},
+        "expander": {"ms_per_layer": round(expand_ms, 3), "gbs": round(expand_bytes / expand_ms / 1e6, 1), "algorithmic_bytes": expand_bytes, "esc_columns_ms_per_layer": round(columns_ms, 3), "host_pack_s": round(host_pack_s, 2), "host_pack_cores": cpu_cores()},
         "roofline": {"bound": "hbm", "kernel": f"r4_oct_kernel (all {len(groups)} launches of a step), averaged over them", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"], "peak_source": peaks["source"], "bytes_per_launch": per_launch_bytes, "traffic": per_launch_bytes * NCU_TRAFFIC_RATIO, "traffic_source": "assumed, not measured in this run: DRAM read + write bytes of one ncu capture of the same kernel on the gate matrix, scaled to the average launch by its bytes"},
         "e2e": {"value": e2e_val, "unit": UNIT, "ms_per_step": e2e_ms, "h2d_bytes_per_step": sum(2 * k for k in k_list), "d2h_bytes_per_step": sum(2 * n for _, n, _ in SHAPES), "api": "R4LinearGroup.__call__ (RowShardedGroup + gather_all with several GPUs) on host-resident inputs, outputs copied back to pinned host memory; the calls of one step are captured once in a CUDA graph (copies included) and every step replays it and synchronises", "eager_ms_per_step": e2e_eager_ms, "eager_value": world * step_bytes / (e2e_eager_ms * 1e-3) / 1e9},
         "gpu_launches": launches,
