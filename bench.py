@@ -730,7 +730,40 @@ def moe_parallel_leg(torch, dist, dev, rank: int, world: int) -> dict:
             whole(x[:B], idx[:B])
         e1.record()
         torch.cuda.synchronize()
-        out[str(B)] = {"us": round(float(t.item()), 1), "single_gpu_layer_us_eager": round(e0.elapsed_time(e1) * 1e3 / 20, 1), "tokens_per_rank": each, "experts_per_rank": per, "checked": "bit-identical to the single-GPU layer on every rank", "timing": "eager launches (torch glue + 2 all-to-all + 2 gather kernels), CUDA events, max over ranks"}
+        single_us = e0.elapsed_time(e1) * 1e3 / 20
+        # the same forward captured once in a CUDA graph (fixed shapes, no host synchronisation
+        # inside, the all-to-alls are nodes of the graph) and replayed; the ranks agree that all
+        # of them captured it before any of them replays
+        graph_us, captured, gph, yg = None, 1, None, None
+        try:
+            gph = torch.cuda.CUDAGraph()
+            cap = torch.cuda.Stream()
+            cap.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(cap):
+                with torch.cuda.graph(gph, stream=cap):
+                    yg = ep(x[mine], idx[mine])
+            torch.cuda.synchronize()
+        except Exception as e:  # noqa: BLE001 - reported in the JSON line, the eager number stands
+            captured, graph_us = 0, f"not captured: {type(e).__name__}"
+        flag = torch.tensor([captured], device=dev)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        if int(flag.item()):
+            gph.replay()
+            torch.cuda.synchronize()
+            if not torch.equal(yg.view(torch.int16), want.view(torch.int16)):
+                raise SystemExit(f"bench: the captured expert-parallel forward differs from the single-GPU layer at {B} tokens (rank {rank})")
+            dist.barrier()
+            e0.record()
+            for _ in range(20):
+                gph.replay()
+            e1.record()
+            torch.cuda.synchronize()
+            tg = torch.tensor([e0.elapsed_time(e1) * 1e3 / 20], device=dev)
+            dist.all_reduce(tg, op=dist.ReduceOp.MAX)
+            graph_us = round(float(tg.item()), 1)
+        elif captured:
+            graph_us = "not captured on another rank"
+        out[str(B)] = {"us": round(float(t.item()), 1), "graph_replay_us": graph_us, "single_gpu_layer_us_eager": round(single_us, 1), "tokens_per_rank": each, "experts_per_rank": per, "checked": "bit-identical to the single-GPU layer on every rank", "timing": "us: eager launches (torch glue + 2 all-to-all + 2 gather kernels); graph_replay_us: the forward captured once and replayed; CUDA events, max over ranks"}
     return out
 
 
