@@ -262,12 +262,20 @@ def run_ours(args) -> dict | None:
         if not (np.array_equal(as_np(a["esc_cols"], np.uint8), want_cols) and np.array_equal(as_np(a["col_esc"], np.uint16).reshape(n, 16), want_starts)):
             raise SystemExit(f"bench: column-ordered escapes of {name} differ from their definition restated in numpy; refusing to report a number")
         cols_tmp, starts_tmp = torch.empty_like(a["esc_cols"]), torch.empty_like(a["col_esc"])
+        # (a short kernel: its calls are replayed from a CUDA graph so that the events time the
+        # device work and not the host's launch rate)
+        struct_a, cols_graph = ck.r4_struct(a), torch.cuda.CUDAGraph()
+        with torch.cuda.graph(cols_graph):
+            capture_stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+            for _ in range(reps):
+                _native.call("cuda", "bn_r4_esc_columns", ctypes.byref(struct_a), n, k, P(cols_tmp), P(starts_tmp), capture_stream)
+        cols_graph.replay()
         ev0.record()
-        for _ in range(reps):
-            _native.call("cuda", "bn_r4_esc_columns", ctypes.byref(ck.r4_struct(a)), n, k, P(cols_tmp), P(starts_tmp), stream)
+        cols_graph.replay()
         ev1.record()
         torch.cuda.synchronize()
         columns_ms += ev0.elapsed_time(ev1) / reps
+        del cols_graph
         del cols_tmp, starts_tmp
         if not np.array_equal(as_np(m0.dense().view(torch.int16), np.uint16).reshape(n, k), u):
             raise SystemExit(f"bench: dense decode of {name} differs from the source words; refusing to report a number")

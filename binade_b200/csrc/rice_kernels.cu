@@ -280,6 +280,193 @@ __global__ void __launch_bounds__(RICE_THREADS) rice_kernel(RiceArgs a) {
   }
 }
 
+// ---------------------------------------------------------------------------------------------
+// Rice stream -> R4 arrays with several rows per warp (the expander's kernel for matrices with
+// enough rows). A row's tiles are a chain and a plane of a tile is a chain too, so the decode is
+// bound by the instructions it issues per plane step, not by bytes; the one-row-per-warp kernel
+// above spends a whole warp instruction stream on every plane step of one row, and in the late
+// planes only a handful of its 128 weights are still alive. Here LPR lanes own a row (8 lanes x
+// 16 weights, or 16 lanes x 8), so one plane step of the warp serves 4 (or 2) rows: the scan over
+// alive counts is a shuffle scan inside the LPR lanes, a lane deposits its up to 16 plane bits
+// through the 4-bit deposit table nibble by nibble, and ranks, codes and escape tests are done
+// four weights at a time on bytes packed in a register. The warp's rows walk their tiles in step
+// (same tile index, their own bit cursors); a plane loop runs to the largest qmax of the warp's
+// rows and ends early once no lane holds a live weight.
+// Rows past R repeat row R-1 and write nothing.
+// ---------------------------------------------------------------------------------------------
+template <int LPR>
+__global__ void __launch_bounds__(RICE_THREADS) rice_r4_wide_kernel(RiceArgs a) {
+  constexpr int RPW = 32 / LPR;    // rows per warp
+  constexpr int WPL = 128 / LPR;   // weights per lane and tile
+  constexpr int NIB = WPL / 4;     // registers of four byte-packed weights
+  __shared__ uint8_t tbl[256];
+  __shared__ uint8_t deposit[256];  // alive | bits << 4 -> the low bits of `bits`, in order, on the set positions of `alive`
+  {
+    const uint32_t al = threadIdx.x & 15u;
+    uint32_t b = threadIdx.x >> 4, out = 0;
+    for (int i = 0; i < 4; i++)
+      if ((al >> i) & 1u) out |= (b & 1u) << i, b >>= 1;
+    deposit[threadIdx.x] = (uint8_t)out;
+    tbl[threadIdx.x] = a.table[threadIdx.x];
+    __syncthreads();
+  }
+  const uint32_t lane = lane_id(), p = lane & (LPR - 1), first = lane & ~(uint32_t)(LPR - 1);
+  const int warps = RICE_THREADS / 32;
+  const int T = a.T;
+  const int64_t K = a.K;
+  // inclusive sum over the LPR lanes of a row
+  auto row_scan = [&](uint32_t v) {
+#pragma unroll
+    for (int d = 1; d < LPR; d <<= 1) {
+      const uint32_t n = __shfl_up_sync(BN_FULL, v, d, LPR);
+      if (p >= (uint32_t)d) v += n;
+    }
+    return v;
+  };
+  for (int64_t row0 = ((int64_t)blockIdx.x * warps + (threadIdx.x >> 5)) * RPW; row0 < a.R; row0 += (int64_t)gridDim.x * warps * RPW) {
+    const bool valid = row0 + lane / LPR < a.R;
+    const int64_t row = valid ? row0 + lane / LPR : a.R - 1;
+    const uint32_t w0 = a.roff[row];
+    const uint64_t w_end = row + 1 < a.R ? (uint64_t)a.roff[row + 1] : a.nwords;
+    const uint32_t *row_words = a.bits + w0;
+    const uint32_t avail = (uint64_t)w0 < a.nwords ? (uint32_t)min(a.nwords - w0, (uint64_t)0xFFFFFFFFu) : 0u;
+    // pull the row's stream toward the SM: one 128-byte line per lane and round, up to 4 KB a row
+    for (uint32_t i = 0; i < 4096u / (LPR * 128u); i++) {
+      const uint64_t at = (uint64_t)w0 + (i * LPR + p) * 32u;
+      if (at < w_end && at < a.nwords) asm volatile("prefetch.global.L1 [%0];" ::"l"(a.bits + at));
+    }
+    // scratch for the most escapes the row's meta bytes allow (a tile can hold a rank >= 15 only
+    // if its largest representable rank reaches 15)
+    uint32_t bound = 0;
+    for (int t = (int)p; t < T; t += LPR) {
+      const uint32_t m = a.meta[row * T + t], k = m & 3u, qmax = m >> 2;
+      if (((qmax << k) | ((1u << k) - 1u)) >= 15u) bound += (uint32_t)min(BN_TILE, (int)K - t * BN_TILE);
+    }
+#pragma unroll
+    for (int o = LPR / 2; o >= 1; o >>= 1) bound += __shfl_xor_sync(BN_FULL, bound, o);
+    unsigned long long base = 0;
+    if (p == 0 && valid && bound) base = atomicAdd(reinterpret_cast<unsigned long long *>(a.counters + 4), (unsigned long long)bound);
+    base = __shfl_sync(BN_FULL, base, first);
+    const uint64_t esc_base = base;
+    const bool esc_room = base + bound <= a.esc_cap;
+    if (p == 0 && valid) a.tmp_off[row] = (uint32_t)base;
+
+    uint32_t cur = 0, row_escapes = 0;
+    uint32_t m_next = a.meta[row * T];
+    for (int t = 0; t < T; t++) {
+      const uint32_t m = m_next;
+      if (t + 1 < T) m_next = a.meta[row * T + t + 1];
+      const uint32_t k = m & 3u, qmax = m >> 2, km = (1u << k) - 1u;
+      const int n = min(BN_TILE, (int)K - t * BN_TILE);
+      const uint32_t nv = (uint32_t)max(0, min(WPL, n - (int)p * WPL));
+      // low bits of the lane's weights: nv * k <= 48 bits
+      const uint32_t nb = nv * k, lo_at = cur + p * WPL * k;
+      uint32_t lo0 = nb ? row_bits(row_words, avail, lo_at, min(nb, 32u)) : 0u;
+      uint32_t lo1 = nb > 32u ? row_bits(row_words, avail, lo_at + 32u, nb - 32u) : 0u;
+      cur += (uint32_t)n * k;
+      // unary planes
+      uint32_t q[NIB];
+#pragma unroll
+      for (int i = 0; i < NIB; i++) q[i] = 0u;
+      uint32_t alive = (1u << nv) - 1u;
+      uint32_t planes = qmax;  // the warp runs to the largest qmax of its rows
+#pragma unroll
+      for (int o = 16; o >= LPR; o >>= 1) planes = max(planes, __shfl_xor_sync(BN_FULL, planes, o));
+      for (uint32_t j = 0; j < planes; j++) {
+        if (j >= qmax) alive = 0u;  // a weight alive after the last plane has q = qmax: nothing more to read
+        const uint32_t c = __popc(alive);
+        if (!__any_sync(BN_FULL, c != 0)) break;
+        const uint32_t upto = row_scan(c), tot = __shfl_sync(BN_FULL, upto, first + LPR - 1);
+        if (!__any_sync(BN_FULL, tot > 1u)) {
+          // every row has at most one weight left: its remaining planes are a run of ones closed
+          // by a zero (or by reaching qmax); count it in one go
+          uint32_t used = 0;
+          if (c) {
+            const uint32_t rem = qmax - j;
+            uint32_t ones = 0;
+            for (uint32_t done = 0; done < rem; done += 32) {
+              const uint32_t take = min(32u, rem - done);
+              const uint32_t b = row_bits(row_words, avail, cur + done, take);
+              const uint32_t run = __ffs(~b) - 1;  // 32 when b is all ones (ffs(0) = 0 wraps)
+              if (run < take) { ones += run; break; }
+              ones += take;
+            }
+            used = min(ones + 1, rem);
+            const uint32_t i = __ffs(alive) - 1;
+#pragma unroll
+            for (int r = 0; r < NIB; r++)
+              if ((i >> 2) == (uint32_t)r) q[r] += ones << (8 * (i & 3u));
+          }
+          const uint32_t holders = __ballot_sync(BN_FULL, c != 0) & (((LPR == 32 ? 0u : (1u << LPR)) - 1u) << first);
+          const uint32_t owner = holders ? __ffs(holders) - 1 : lane;
+          cur += __shfl_sync(BN_FULL, used, owner);
+          break;
+        }
+        uint32_t b = c ? row_bits(row_words, avail, cur + upto - c, c) : 0u;
+        uint32_t next = 0;
+#pragma unroll
+        for (int r = 0; r < NIB; r++) {
+          const uint32_t al = (alive >> (4 * r)) & 15u;
+          const uint32_t d = deposit[al | ((b & 15u) << 4)];  // the plane's bits at the alive positions
+          b >>= __popc(al);
+          next |= d << (4 * r);
+          q[r] += (d * 0x00204081u) & 0x01010101u;  // bit i -> byte i: one more for the survivors
+        }
+        alive = next;
+        cur += tot;
+      }
+      // ranks, codes and escape tests, four weights (bytes of a register) at a time
+      uint32_t code_words[NIB / 2 > 0 ? NIB / 2 : 1], rank4[NIB], hit = 0;
+#pragma unroll
+      for (int r = 0; r < NIB; r++) {
+        // the four weights' low bits, k each, spread to one byte each
+        const uint32_t x = lo0 & ((1u << (4 * k)) - 1u);
+        lo0 = __funnelshift_r(lo0, lo1, 4 * k), lo1 >>= 4 * k;
+        const uint32_t pair0 = x & ((1u << (2 * k)) - 1u), pair1 = x >> (2 * k);
+        const uint32_t both = km | (km << 8);
+        const uint32_t low4 = ((pair0 | (pair0 << (8 - k))) & both) | (((pair1 | (pair1 << (8 - k))) & both) << 16);
+        const uint32_t r4 = (((q[r] & ((0xFFu >> k) * 0x01010101u)) << k) | low4);
+        rank4[r] = r4;
+        // bit 7 of a byte of t: its rank is >= 15
+        const uint32_t tt = (((r4 & 0x7F7F7F7Fu) + 0x71717171u) | r4) & 0x80808080u;
+        const uint32_t full = (tt >> 7) * 15u;             // 0x0F in the bytes that escape
+        uint32_t c4 = (r4 | full) & 0x0F0F0F0Fu;           // min(rank, 15) per byte
+        c4 = (c4 | (c4 >> 4)) & 0x00FF00FFu;
+        c4 = (c4 | (c4 >> 8)) & 0xFFFFu;                   // four nibbles
+        if (r & 1) code_words[r >> 1] |= c4 << 16;
+        else code_words[r >> 1] = c4;
+        hit |= (((tt >> 7) * 0x00204081u >> 21) & 15u) << (4 * r);  // bytes' flags gathered into four bits
+      }
+      if (valid) {
+        uint16_t *dst = a.codes + ((row * T + t) * 32 + p * (WPL / 4));
+        if (NIB == 4) *reinterpret_cast<uint2 *>(dst) = make_uint2(code_words[0], code_words[NIB / 2 > 1 ? 1 : 0]);
+        else *reinterpret_cast<uint32_t *>(dst) = code_words[0];
+      }
+      uint32_t flag = 0;
+      if (__any_sync(BN_FULL, hit != 0)) {
+        const uint32_t hc = __popc(hit), upto = row_scan(hc), tot = __shfl_sync(BN_FULL, upto, first + LPR - 1);
+        if (valid && esc_room && hit) {
+          uint64_t at = esc_base + row_escapes + upto - hc;
+#pragma unroll
+          for (int r = 0; r < NIB; r++)
+#pragma unroll
+            for (int i = 0; i < 4; i++)
+              if ((hit >> (4 * r + i)) & 1u) a.esc_tmp[at++] = tbl[(rank4[r] >> (8 * i)) & 0xFFu];
+        }
+        row_escapes += tot;
+        flag = tot != 0;
+      }
+      if (p == 0 && valid) a.flags[row * T + t] = (uint8_t)flag;
+    }
+    if (p == 0 && valid) {
+      const uint32_t rend = w0 + ((cur + 31u) >> 5);
+      a.row_cnt[row] = row_escapes;
+      if (row_escapes) atomicAdd(a.counters + 2, row_escapes);
+      if ((uint64_t)rend != w_end) atomicMax(a.counters + 1, (uint32_t)(a.R - row));
+    }
+  }
+}
+
 // row_esc = exclusive prefix sum of row_cnt, by one block (load-time, R up to a few 10^5).
 __global__ void __launch_bounds__(1024) scan_rows_kernel(const uint32_t *row_cnt, int64_t R, uint32_t *row_esc) {
   __shared__ uint32_t part[1024];
@@ -363,6 +550,28 @@ static int rice_grid(int64_t R) {
   return (int)(blocks < cap ? blocks : cap);
 }
 
+// The expander's kernel for R rows: four rows a warp when the matrix has rows for that on every
+// SM, two from half of that, else one row a warp (the general kernel): fewer instructions per
+// row against fewer warps to hide a plane step's latency.
+static int launch_rice_r4(const RiceArgs &a, cudaStream_t s) {
+  int dev = 0, sms = 148;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  // measured on 3840-wide rows (ms, one / two / four rows a warp): 15360 rows 0.31 / 0.24 / 0.22,
+  // 4096 rows 0.116 / 0.107 / 0.122, 2048 rows 0.077 / 0.095 / 0.116; 3840 rows of 15360: 0.39 / 0.35 / 0.40
+  const int lpr = a.R >= (int64_t)sms * 48 ? 8 : a.R >= (int64_t)sms * 24 ? 16 : 32;
+  if (lpr == 8) {
+    rice_r4_wide_kernel<8><<<rice_grid((a.R + 3) / 4), RICE_THREADS, 0, s>>>(a);
+    return launched("rice_r4_wide_kernel<8>");
+  }
+  if (lpr == 16) {
+    rice_r4_wide_kernel<16><<<rice_grid((a.R + 1) / 2), RICE_THREADS, 0, s>>>(a);
+    return launched("rice_r4_wide_kernel<16>");
+  }
+  rice_kernel<RICE_R4><<<rice_grid(a.R), RICE_THREADS, 0, s>>>(a);
+  return launched("rice_kernel<r4>");
+}
+
 static int check_stream(const uint8_t *meta, const uint32_t *bits, const uint32_t *roff, int64_t R, int64_t K) {
   if (!meta || !bits || !roff) return fail(BN_ERR_ARG, "null Rice stream array");
   if (R < 0 || K <= 0) return fail(BN_ERR_ARG, "bad matrix size");
@@ -415,8 +624,7 @@ extern "C" int bn_rice_to_r4(const uint8_t *meta, const uint32_t *bits, uint64_t
   RiceArgs a{};
   a.meta = meta, a.bits = bits, a.nwords = nwords, a.roff = roff, a.table = table, a.R = R, a.K = K, a.T = (int)tiles(K);
   a.codes = codes, a.flags = flags, a.row_cnt = row_cnt, a.esc_tmp = esc_tmp, a.esc_cap = esc_cap, a.tmp_off = tmp_off, a.counters = counters;
-  rice_kernel<RICE_R4><<<rice_grid(R), RICE_THREADS, 0, (cudaStream_t)stream>>>(a);
-  return launched("rice_kernel<r4>");
+  return launch_rice_r4(a, (cudaStream_t)stream);
 }
 
 extern "C" int bn_r4_finish(const uint32_t *row_cnt, const uint8_t *esc_tmp, const uint32_t *tmp_off, int64_t R, uint32_t *row_esc, uint8_t *esc, uint64_t esc_bytes, void *stream) {
@@ -513,8 +721,7 @@ extern "C" int bn_rice_to_r4_static(const uint8_t *meta, const uint32_t *bits, u
     RiceArgs a{};
     a.meta = meta, a.bits = bits, a.nwords = nwords, a.roff = roff, a.table = table, a.R = R, a.K = K, a.T = (int)tiles(K);
     a.codes = codes, a.flags = flags, a.row_cnt = row_esc, a.esc_tmp = esc_tmp, a.esc_cap = (uint64_t)STATIC_MAX_WEIGHTS, a.tmp_off = tmp_off, a.counters = counters;
-    rice_kernel<RICE_R4><<<rice_grid(R), RICE_THREADS, 0, s>>>(a);
-    if (int e = launched("rice_kernel<r4>")) return e;
+    if (int e = launch_rice_r4(a, s)) return e;
     scan_rows_kernel<<<1, 1024, 0, s>>>(row_esc, R, row_esc);
     if (int e = launched("scan_rows_kernel")) return e;
   }

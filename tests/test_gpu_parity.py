@@ -178,6 +178,33 @@ def test_transcode_matches_oracle(N, K):
     assert a["shape"] == (N, K) and r4.r4_bytes(a) == sum(want[k].nbytes for k in ("raw", "codes", "flags", "esc", "table", "row_esc"))
 
 
+@pytest.mark.parametrize("N,K,kind", [(7201, 260, "normal"), (3601, 132, "normal"), (7107, 4, "normal"), (3553, 3840, "normal"), (7300, 512, "uniform"), (3700, 384, "uniform"), (7200, 640, "mixed"), (3602, 1000, "mixed"), (7110, 128, "const")])
+def test_transcode_many_rows(N, K, kind):
+    """Row counts at which the expander runs four (N >= 7104) or two (N >= 3552) rows a warp:
+    the arrays against the oracle, for short last tiles, a row count that leaves the last warp
+    partly empty, uniformly random words (nearly every weight escapes, every plane count up to the
+    format's largest), a mix of both by row, and a constant tensor (no unary plane at all)."""
+    from binade_b200.cuda import r4
+
+    rng = np.random.default_rng(N + K)
+    if kind == "normal":
+        u = weights(rng, (N, K))
+    elif kind == "uniform":
+        u = rng.integers(0, 1 << 16, size=(N, K), dtype=np.uint16)
+    elif kind == "mixed":
+        u = weights(rng, (N, K))
+        rows = rng.random(N) < 0.3
+        u[rows] = rng.integers(0, 1 << 16, size=(int(rows.sum()), K), dtype=np.uint16)
+    else:
+        u = np.full((N, K), 0x3C00, np.uint16)
+    want = o.pack_r4(u)
+    a = r4.transcode(packed_arrays(u))
+    for k, dt in (("codes", np.uint16), ("flags", np.uint8), ("esc", np.uint8), ("row_esc", np.uint32)):
+        got = a[k].cpu().numpy()
+        assert np.array_equal(got.view(dt) if got.dtype.itemsize == np.dtype(dt).itemsize else got, want[k]), k
+    assert np.array_equal(words(r4.R4Linear(a).dense()), u)
+
+
 def test_transcode_all_escapes_grows_scratch():
     """Uniform exponents: nearly every weight escapes, far beyond the default scratch size."""
     from binade_b200.cuda import r4
