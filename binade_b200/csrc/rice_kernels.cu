@@ -292,26 +292,30 @@ __global__ void __launch_bounds__(RICE_THREADS) rice_kernel(RiceArgs a) {
 // four weights at a time on bytes packed in a register. The warp's rows walk their tiles in step
 // (same tile index, their own bit cursors); a plane loop runs to the largest qmax of the warp's
 // rows and ends early once no lane holds a live weight.
-// Rows past R repeat row R-1 and write nothing.
+// Rows past R repeat row R-1 and write nothing. Blocks are two warps: with larger blocks the SMs
+// of a launch end up with 24 or 32 warps each (three or four blocks) and the launch waits for the
+// fuller ones.
 // ---------------------------------------------------------------------------------------------
+constexpr int RICE_WIDE_THREADS = 64;
+
 template <int LPR>
-__global__ void __launch_bounds__(RICE_THREADS) rice_r4_wide_kernel(RiceArgs a) {
+__global__ void __launch_bounds__(RICE_WIDE_THREADS) rice_r4_wide_kernel(RiceArgs a) {
   constexpr int RPW = 32 / LPR;    // rows per warp
   constexpr int WPL = 128 / LPR;   // weights per lane and tile
   constexpr int NIB = WPL / 4;     // registers of four byte-packed weights
   __shared__ uint8_t tbl[256];
   __shared__ uint8_t deposit[256];  // alive | bits << 4 -> the low bits of `bits`, in order, on the set positions of `alive`
-  {
-    const uint32_t al = threadIdx.x & 15u;
-    uint32_t b = threadIdx.x >> 4, out = 0;
+  for (uint32_t e = threadIdx.x; e < 256; e += RICE_WIDE_THREADS) {
+    const uint32_t al = e & 15u;
+    uint32_t b = e >> 4, out = 0;
     for (int i = 0; i < 4; i++)
       if ((al >> i) & 1u) out |= (b & 1u) << i, b >>= 1;
-    deposit[threadIdx.x] = (uint8_t)out;
-    tbl[threadIdx.x] = a.table[threadIdx.x];
-    __syncthreads();
+    deposit[e] = (uint8_t)out;
+    tbl[e] = a.table[e];
   }
+  __syncthreads();
   const uint32_t lane = lane_id(), p = lane & (LPR - 1), first = lane & ~(uint32_t)(LPR - 1);
-  const int warps = RICE_THREADS / 32;
+  const int warps = RICE_WIDE_THREADS / 32;
   const int T = a.T;
   const int64_t K = a.K;
   // inclusive sum over the LPR lanes of a row
@@ -560,13 +564,12 @@ static int launch_rice_r4(const RiceArgs &a, cudaStream_t s) {
   // measured on 3840-wide rows (ms, one / two / four rows a warp): 15360 rows 0.31 / 0.24 / 0.22,
   // 4096 rows 0.116 / 0.107 / 0.122, 2048 rows 0.077 / 0.095 / 0.116; 3840 rows of 15360: 0.39 / 0.35 / 0.40
   const int lpr = a.R >= (int64_t)sms * 48 ? 8 : a.R >= (int64_t)sms * 24 ? 16 : 32;
-  if (lpr == 8) {
-    rice_r4_wide_kernel<8><<<rice_grid((a.R + 3) / 4), RICE_THREADS, 0, s>>>(a);
-    return launched("rice_r4_wide_kernel<8>");
-  }
-  if (lpr == 16) {
-    rice_r4_wide_kernel<16><<<rice_grid((a.R + 1) / 2), RICE_THREADS, 0, s>>>(a);
-    return launched("rice_r4_wide_kernel<16>");
+  if (lpr == 8 || lpr == 16) {
+    const int64_t warps = (a.R * lpr + 31) / 32, per_block = RICE_WIDE_THREADS / 32;
+    const int64_t blocks = min((warps + per_block - 1) / per_block, (int64_t)sms * 32);
+    if (lpr == 8) rice_r4_wide_kernel<8><<<(unsigned)blocks, RICE_WIDE_THREADS, 0, s>>>(a);
+    else rice_r4_wide_kernel<16><<<(unsigned)blocks, RICE_WIDE_THREADS, 0, s>>>(a);
+    return launched("rice_r4_wide_kernel");
   }
   rice_kernel<RICE_R4><<<rice_grid(a.R), RICE_THREADS, 0, s>>>(a);
   return launched("rice_kernel<r4>");
