@@ -34,6 +34,9 @@ _SIGNATURES = {
         "bn_rice_to_r4_static": [_vp, _vp, _u64, _vp, _vp, _i64, _i64, _vp, _vp, _vp, _vp, _u64, _vp, _vp],
         "bn_r4_decode": [C.POINTER(R4Struct), _i64, _i64, _i64, _i64, _i64, _vp, _vp],
         "bn_r4_esc_columns": [C.POINTER(R4Struct), _i64, _i64, _vp, _vp, _vp],
+        "bn_bf16_split_hist": [_vp, _i64, _vp, _vp, _vp],
+        "bn_rice_encode_plan": [_vp, _vp, _i64, _i64, _vp, _vp, _vp, _vp, _vp],
+        "bn_rice_encode_write": [_vp, _vp, _vp, _vp, _i64, _i64, _vp, _u64, _vp],
         "bn_r4_lookup": [C.POINTER(R4Struct), _i64, _vp, _i64, _i64, _vp, _vp],
         "bn_rice_lookup": [_vp, _vp, _u64, _vp, _vp, _vp, _i64, _i64, _vp, _i64, _vp, _vp],
         "bn_f1_offsets": [_vp, _vp, _u64, _i64, _i64, _vp, _vp, _vp, _vp, _vp],

@@ -74,6 +74,48 @@ def r4_esc_columns(a: dict) -> None:
     a["esc_cols"], a["col_esc"] = esc_cols, col_esc
 
 
+def split_hist(u: torch.Tensor):
+    """int16 BF16 words (any shape, contiguous, on the device) -> (raw uint8 [numel], hist int64
+    numpy [256] of the exponent bytes; reading the histogram synchronises)."""
+    raw = torch.empty(u.numel(), dtype=torch.uint8, device=u.device)
+    hist = torch.empty(256, dtype=torch.int32, device=u.device)
+    _call("bn_bf16_split_hist", _p(u), u.numel(), _p(raw), _p(hist))
+    return raw, hist.cpu().numpy().view(np.uint32).astype(np.int64)
+
+
+def rice_encode_ranked(u: torch.Tensor, rank_d: torch.Tensor):
+    """int16 BF16 words [R, K] on the device and the device copy of the exponent -> rank table ->
+    (meta uint8 [R*T], bits int32 [nwords], roff int32 [R]) of these rows' own stream."""
+    R, K = u.shape
+    T = -(-K // TILE)
+    dev = u.device
+    meta = torch.empty(R * T, dtype=torch.uint8, device=dev)
+    row_words, roff = torch.empty(R, dtype=torch.int32, device=dev), torch.empty(R, dtype=torch.int32, device=dev)
+    total = torch.zeros(1, dtype=torch.int64, device=dev)
+    _call("bn_rice_encode_plan", _p(u), _p(rank_d), R, K, _p(meta), _p(row_words), _p(roff), _p(total))
+    nwords = int(total.item())
+    if nwords >= 1 << 32:
+        raise ValueError(f"{nwords} words overflow uint32 row offsets")
+    bits = torch.empty(nwords, dtype=torch.int32, device=dev)
+    _call("bn_rice_encode_write", _p(u), _p(rank_d), _p(meta), _p(roff), R, K, _p(bits) if nwords else None, nwords)
+    return meta, bits, roff
+
+
+def rice_encode(w: torch.Tensor) -> dict:
+    """BF16 weights [.., K] on the device (bfloat16 or int16 words) -> the format-2 arrays as
+    device tensors {"raw", "table", "meta", "bits", "roff", "shape"}, bit for bit what the host
+    packer writes (pack.pack). Two small host reads on the way: the exponent histogram (the rank
+    table is built on the host like the reference does) and the stream's length in words."""
+    from ..format import rank_table
+
+    shape = tuple(w.shape)
+    u = w.contiguous().view(torch.int16).reshape(-1, shape[-1])
+    raw, hist = split_hist(u)
+    table, rank = rank_table(hist)
+    meta, bits, roff = rice_encode_ranked(u, to_device(rank))
+    return {"raw": raw.reshape(shape), "table": to_device(table), "meta": meta, "bits": bits, "roff": roff, "shape": shape}
+
+
 def rice_ranks(meta: torch.Tensor, bits: torch.Tensor, roff: torch.Tensor, K: int):
     """(ranks uint8 [R, ceil(K/128)*128], rend int32-typed uint32 [R])."""
     R, T = roff.numel(), -(-K // TILE)

@@ -82,9 +82,17 @@ def _raw(u: np.ndarray) -> np.ndarray:
     return out
 
 
-def pack(w: np.ndarray, chunk: int = CHUNK) -> dict:
-    """BF16 words (uint16, [.., K]) -> {"raw", "table", "meta", "bits", "roff", "shape"}."""
+def pack(w: np.ndarray, chunk: int = CHUNK, gpu: bool = False) -> dict:
+    """BF16 words (uint16, [.., K]) -> {"raw", "table", "meta", "bits", "roff", "shape"}.
+    gpu: encode on the CUDA device (the same arrays, bit for bit; the reference and the default
+    path encode on host cores)."""
     w = np.ascontiguousarray(w, np.uint16)
+    if gpu:
+        from .cuda import kernels as ck
+
+        d = ck.rice_encode(ck.to_device(w.view(np.int16)))
+        host = lambda t, dt: t.cpu().numpy().view(dt)
+        return {"raw": host(d["raw"], np.uint8).reshape(w.shape), "table": host(d["table"], np.uint8), "meta": host(d["meta"], np.uint8), "bits": host(d["bits"], np.uint32), "roff": host(d["roff"], np.uint32), "shape": tuple(w.shape)}
     rows = w.reshape(-1, w.shape[-1])
     hist = np.zeros(256, np.int64)
     _histogram(rows, hist)
@@ -99,19 +107,32 @@ def bits_per_weight(p: dict) -> float:
     return (8 * numel + 8 * p["table"].size + 8 * p["meta"].size + 32 * p["bits"].size + 32 * p["roff"].size) / numel
 
 
-def pack_tensor(w: st.Writer, info: st.TensorInfo, chunk: int = CHUNK, version: str = VERSION) -> dict:
+def pack_tensor(w: st.Writer, info: st.TensorInfo, chunk: int = CHUNK, version: str = VERSION, gpu: bool = False) -> dict:
+    """gpu: histogram, raw bytes and the Rice streams on the CUDA device (the same bytes)."""
     if version != "2":
         raise NotImplementedError("only format 2 (Rice) is implemented")
+    if gpu:
+        from .cuda import kernels as ck
     hist = np.zeros(256, np.int64)
     for span in spans(info, chunk):
-        _histogram(np.ascontiguousarray(st.read(info, span)), hist)
+        u = np.ascontiguousarray(st.read(info, span))
+        if gpu:
+            hist += ck.split_hist(ck.to_device(u.view(np.int16)))[1]
+        else:
+            _histogram(u, hist)
     table, rank = rank_table(hist)
     metas, streams, offsets, base = [], [], [], 0
     w.begin(info.name + ".raw", "U8", info.shape)
     for span in spans(info, chunk):
         u = np.ascontiguousarray(st.read(info, span))
-        w.write(_raw(u))
-        meta, words, roff = rice.encode_words(u, rank)
+        if gpu:
+            d = ck.to_device(u.view(np.int16))
+            w.write(ck.split_hist(d)[0].cpu().numpy().reshape(u.shape))
+            meta, words, roff = (t.cpu().numpy() for t in ck.rice_encode_ranked(d, ck.to_device(rank)))
+            words, roff = words.view(np.uint32), roff.view(np.uint32)
+        else:
+            w.write(_raw(u))
+            meta, words, roff = rice.encode_words(u, rank)
         metas.append(meta)
         streams.append(words)
         offsets.append(roff.astype(np.uint64) + np.uint64(base))
@@ -145,7 +166,7 @@ def _header_room(infos, classes, metadata, version) -> int:
     return room + len(json.dumps(metadata)) + 4096
 
 
-def pack_model(src: Path, out: Path, classes=CLASSES, chunk: int = CHUNK, log=print, version: str = VERSION) -> dict:
+def pack_model(src: Path, out: Path, classes=CLASSES, chunk: int = CHUNK, log=print, version: str = VERSION, gpu: bool = False) -> dict:
     if version == "1":
         raise NotImplementedError("format 1 is not implemented in this package")
     if version not in PARTS:
@@ -166,7 +187,7 @@ def pack_model(src: Path, out: Path, classes=CLASSES, chunk: int = CHUNK, log=pr
         for info in mine:
             t0 = time.perf_counter()
             if info.name in packed:
-                stats[info.name] = pack_tensor(writer, info, chunk, version)
+                stats[info.name] = pack_tensor(writer, info, chunk, version, gpu)
                 written = [f"{info.name}.{s}" for s in PARTS[version]]
                 log(f"packed {info.name} {info.shape}: {stats[info.name]['bits'] / info.numel:.3f} bits/weight, {time.perf_counter() - t0:.1f}s")
             else:
@@ -205,8 +226,9 @@ def main():
     ap.add_argument("--revision")
     ap.add_argument("--classes", default=",".join(CLASSES))
     ap.add_argument("--format", default=VERSION, choices=sorted(PARTS), help="2: Rice (decoded to R4 at load)")
+    ap.add_argument("--gpu", action="store_true", help="encode on the CUDA device instead of the host cores (same bytes)")
     args = ap.parse_args()
-    r = pack_model(st.resolve(args.model, args.revision), args.out, tuple(args.classes.split(",")), version=args.format)
+    r = pack_model(st.resolve(args.model, args.revision), args.out, tuple(args.classes.split(",")), version=args.format, gpu=args.gpu)
     print(
         f"{r['input_bytes'] / 1e9:.2f} GB -> {r['output_bytes'] / 1e9:.2f} GB ({r['output_bytes'] / r['input_bytes']:.1%}); "
         f"packed weights {r['packed_bits'] / r['packed_numel']:.3f} bits/weight; {r['seconds'] / 60:.1f} min"

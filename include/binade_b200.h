@@ -130,6 +130,25 @@ int bn_rice_to_r4_static(const uint8_t *meta, const uint32_t *bits, uint64_t nwo
                          const uint8_t *table, int64_t R, int64_t K, uint16_t *codes, uint8_t *flags,
                          uint32_t *row_esc, uint8_t *esc, uint64_t esc_cap, uint32_t *info, void *stream);
 
+/* ---- Rice (format 2) encoder on the device: BF16 words [R,K] in device memory -> the file
+ * arrays, bit for bit what binade/rice.py:57-125 (encode_ranks, choose) and the host encoder of
+ * this library write. Three calls, two small reads by the host in between (the exponent histogram,
+ * from which the host builds the rank table as binade/format.py:34-42 does, and the number of
+ * stream words, to size `bits`):
+ *   bn_bf16_split_hist    raw [n] = sign << 7 | mantissa of every word, hist [256] = counts of the
+ *                         exponent bytes (binade/bf16.py split + the histogram of pack_tensor)
+ *   bn_rice_encode_plan   meta [R*T] (k | qmax << 2 per tile, smallest cost, ties to the smaller k),
+ *                         row_words [R], roff [R] = exclusive prefix sum, total [1] = words of the
+ *                         stream as uint64 (2^32 or more does not fit the format's uint32 offsets)
+ *   bn_rice_encode_write  bits [nwords]: every word of every row's stream (rows start on a word)
+ * `rank` is the device copy of the 256-entry exponent -> rank table. */
+int bn_bf16_split_hist(const uint16_t *w, int64_t n, uint8_t *raw, uint32_t *hist, void *stream);
+int bn_rice_encode_plan(const uint16_t *w, const uint8_t *rank, int64_t R, int64_t K, uint8_t *meta,
+                        uint32_t *row_words, uint32_t *roff, uint64_t *total, void *stream);
+int bn_rice_encode_write(const uint16_t *w, const uint8_t *rank, const uint8_t *meta,
+                         const uint32_t *roff, int64_t R, int64_t K, uint32_t *bits, uint64_t nwords,
+                         void *stream);
+
 /* Column-ordered escapes of an R4 matrix of N rows (see bn_r4): esc_cols [w->n_esc + 8] (4-byte
  * aligned) and col_esc [N*16] from w's codes, flags, esc and row_esc. K % 16 == 0. The caller
  * stores the two pointers into its bn_r4 afterwards. */

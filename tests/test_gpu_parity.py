@@ -72,6 +72,73 @@ def torch_same_order(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
     return acc[..., 0].to(torch.bfloat16)
 
 
+# ------------------------------------------------------------------------------ Rice encode on the GPU
+@pytest.mark.parametrize("shape,kind", [((64, 704), "normal"), ((160, 2112), "normal"), ((300, 260), "normal"), ((48, 100), "normal"), ((40, 4), "normal"), ((7, 1), "normal"), ((17, 15360), "normal"), ((5, 2, 384), "normal"), ((64, 1024), "uniform"), ((3, 16384), "uniform"), ((33, 130), "all_patterns"), ((20, 512), "const"), ((9, 257), "one_outlier")])
+def test_rice_encode_on_gpu_matches_host(shape, kind):
+    """bn_bf16_split_hist / bn_rice_encode_plan / bn_rice_encode_write against the host encoder
+    (itself pinned to the reference's streams): every file array byte for byte, for short last
+    tiles, K < 4, K not a multiple of 4, 3-D tensors, uniformly random words (large qmax, every
+    k), every BF16 pattern, a constant tensor (no unary plane) and a lone outlier per tile (the
+    longest unary runs); and the decoder gives the words back."""
+    from binade_b200 import pack, unpack
+    from binade_b200.cuda import kernels as ck
+
+    rng = np.random.default_rng(sum(shape))
+    if kind == "normal":
+        u = weights(rng, shape)
+    elif kind == "uniform":
+        u = rng.integers(0, 1 << 16, size=shape, dtype=np.uint16)
+    elif kind == "all_patterns":
+        u = np.resize(np.arange(1 << 16, dtype=np.uint16), shape)
+    elif kind == "const":
+        u = np.full(shape, 0x3C00, np.uint16)
+    else:
+        u = np.full(shape, 0x3C00, np.uint16)
+        u[:, ::97] = 0x7F7F
+        u[:, 5::89] = 0x0001
+    want = pack.pack(u)
+    got = ck.rice_encode(ck.to_device(u.view(np.int16)))
+    assert got["shape"] == want["shape"]
+    for key, dt in (("raw", np.uint8), ("table", np.uint8), ("meta", np.uint8), ("bits", np.uint32), ("roff", np.uint32)):
+        a = got[key].cpu().numpy()
+        a = a.view(dt) if a.dtype.itemsize == np.dtype(dt).itemsize else a
+        assert np.array_equal(a.reshape(want[key].shape), want[key]), key
+    via_numpy = pack.pack(u, gpu=True)
+    assert all(np.array_equal(via_numpy[key], want[key]) for key in ("raw", "table", "meta", "bits", "roff"))
+    assert np.array_equal(unpack.unpack(via_numpy), u)
+
+
+def test_pack_model_on_gpu_is_byte_identical_to_the_reference(tmp_path):
+    """pack_model(gpu=True): the packed shard is the file the reference's packer wrote (the same
+    golden file the host path is held to), chunked so that a tensor is encoded in several spans."""
+    from binade_b200 import pack
+
+    src = tmp_path / "src"
+    src.mkdir()
+    for f in (GOLDEN / "packed_model" / "src").iterdir():
+        (src / f.name).write_bytes(f.read_bytes())
+    out = tmp_path / "packed"
+    pack.pack_model(src, out, chunk=5000, log=lambda *_: None, version="2", gpu=True)
+    want = GOLDEN / "packed_model" / "packed" / "model.safetensors"
+    assert (out / "model.safetensors").read_bytes() == want.read_bytes()
+
+
+@pytest.mark.parametrize("case", CASES)
+def test_rice_encode_on_gpu_golden(case):
+    """The reference's own streams (golden cases written by its encoder) from the GPU encoder."""
+    from binade_b200.cuda import kernels as ck
+
+    g = CODEC[case]
+    exps = g["exps"].astype(np.uint16)
+    u = (exps << 7).astype(np.uint16)  # words whose exponent bytes are the case's
+    got = ck.rice_encode(ck.to_device(u.view(np.int16)))
+    if "table" in g:
+        assert np.array_equal(got["table"].cpu().numpy(), g["table"])
+    assert np.array_equal(got["meta"].cpu().numpy(), g["meta"])
+    assert np.array_equal(got["bits"].cpu().numpy().view(np.uint32), g["bits"])
+    assert np.array_equal(got["roff"].cpu().numpy().view(np.uint32), g["roff"])
+
+
 # ------------------------------------------------------------------------------ Rice decode
 @pytest.mark.parametrize("case", CASES)
 def test_rice_ranks_golden(case):
@@ -217,6 +284,30 @@ def test_transcode_all_escapes_grows_scratch():
     assert np.array_equal(a["esc"].cpu().numpy(), want["esc"])
     assert np.array_equal(a["row_esc"].cpu().numpy().view(np.uint32), want["row_esc"])
     assert np.array_equal(words(r4.R4Linear(a).dense()), u)
+
+
+def test_streamed_load_equals_plain_load():
+    """stream_r4 (reader thread -> pinned buffers -> copy stream -> expander) gives the arrays
+    that reading every file array and transcoding it gives, for every packed weight of the golden
+    packed model, in the order asked for; a name that is not packed raises at that name."""
+    from binade_b200.cuda import r4
+    from binade_b200.cuda.stream_load import stream_r4
+    from binade_b200.unpack import PackedModel
+
+    pm = PackedModel(GOLDEN / "packed_model" / "packed")
+    plain = {name: r4.transcode(h) for name, h in r4.holders(pm).items()}
+    assert len(plain) >= 3
+    seen = []
+    for name, a in stream_r4(pm, slots=2):
+        seen.append(name)
+        for key in ("raw", "codes", "flags", "esc", "table", "row_esc"):
+            assert torch.equal(a[key].reshape(-1), plain[name][key].reshape(-1)), (name, key)
+        assert a["shape"] == plain[name]["shape"]
+    assert seen == list(pm.packed)
+    back = list(pm.packed)[::-1]
+    assert [n for n, _ in stream_r4(pm, names=back, slots=1)] == back
+    with pytest.raises(KeyError):
+        list(stream_r4(pm, names=["no.such.weight"]))
 
 
 def test_transcode_rejects_bad_input():
