@@ -218,8 +218,9 @@ def run_ours(args) -> dict | None:
     o.set_threads(cpu_cores())
     layers, expand_ms, expand_bytes, host_pack_s, bits_file, bits_r4 = [], 0.0, 0, 0.0, 0, 0
     columns_ms = 0.0  # building the column-ordered escapes, per layer
+    gpu_pack_s = 0.0  # the GPU Rice encoder on the same matrices (wall clock with its two host reads)
     numel = 0
-    parity = {"matrices": 0, "expander_arrays": "bit-identical to the oracle", "escape_columns": "identical to their definition restated in numpy", "dense_decode": "bit-identical to the source words", "matvec": "bit-identical to the oracle (documented order)"}
+    parity = {"matrices": 0, "expander_arrays": "bit-identical to the oracle", "escape_columns": "identical to their definition restated in numpy", "gpu_encoder": "file arrays identical to the host packer's", "dense_decode": "bit-identical to the source words", "matvec": "bit-identical to the oracle (documented order)"}
     xs_host = {k: synthetic_input(k, 0) for k in {k for _, _, k in SHAPES}}  # every rank multiplies the same input, as row-sharded layers do
     for name, n, k in SHAPES:
         u = synthetic_weight(name, n, k, rank)
@@ -228,6 +229,17 @@ def run_ours(args) -> dict | None:
         host_pack_s += time.perf_counter() - t0
         d = {key: ck.to_device(p[key]) for key in ("raw", "table", "meta", "bits", "roff")}
         torch.cuda.synchronize()
+        # the same arrays from the GPU encoder (words already on the device), checked and timed
+        u_dev = ck.to_device(u.view(np.int16))
+        enc = ck.rice_encode(u_dev)
+        if not all(torch.equal(enc[key].reshape(-1).view(torch.uint8), d[key].reshape(-1).view(torch.uint8)) for key in ("raw", "table", "meta", "bits", "roff")):
+            raise SystemExit(f"bench: GPU Rice encoder output of {name} differs from the host packer's; refusing to report a number")
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        ck.rice_encode(u_dev)
+        torch.cuda.synchronize()
+        gpu_pack_s += time.perf_counter() - t0
+        del enc, u_dev
         a = r4.transcode(d)  # the public call (allocates outputs, reads 32 bytes of counters back)
         # the expander's kernels alone, through the C ABI into preallocated buffers
         T_ = -(-k // 128)
@@ -566,7 +578,7 @@ def run_ours(args) -> dict | None:
         "shapes": per_shape,
         "launches": per_launch,
         "speedup_vs_bf16_gemv_per_token": round(sum(v["bf16_gemv_us"] for v in per_shape.values()) / sum(v["us"] for v in per_shape.values()), 3) if per_shape else None,
-        "expander": {"ms_per_layer": round(expand_ms, 3), "gbs": round(expand_bytes / expand_ms / 1e6, 1), "algorithmic_bytes": expand_bytes, "esc_columns_ms_per_layer": round(columns_ms, 3), "host_pack_s": round(host_pack_s, 2), "host_pack_cores": cpu_cores()},
+        "expander": {"ms_per_layer": round(expand_ms, 3), "gbs": round(expand_bytes / expand_ms / 1e6, 1), "algorithmic_bytes": expand_bytes, "esc_columns_ms_per_layer": round(columns_ms, 3), "host_pack_s": round(host_pack_s, 2), "host_pack_cores": cpu_cores(), "gpu_pack_s": round(gpu_pack_s, 4)},
         "roofline": {"bound": "hbm", "kernel": f"r4_oct_kernel (all {len(groups)} launches of a step), averaged over them", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"], "peak_source": peaks["source"], "bytes_per_launch": per_launch_bytes, "traffic": per_launch_bytes * NCU_TRAFFIC_RATIO, "traffic_source": "assumed, not measured in this run: DRAM read + write bytes of one ncu capture of the same kernel on the gate matrix, scaled to the average launch by its bytes"},
         "e2e": {"value": e2e_val, "unit": UNIT, "ms_per_step": e2e_ms, "h2d_bytes_per_step": sum(2 * k for k in k_list), "d2h_bytes_per_step": sum(2 * n for _, n, _ in SHAPES), "api": "R4LinearGroup.__call__ (RowShardedGroup + gather_all with several GPUs) on host-resident inputs, outputs copied back to pinned host memory; the calls of one step are captured once in a CUDA graph (copies included) and every step replays it and synchronises", "eager_ms_per_step": e2e_eager_ms, "eager_value": world * step_bytes / (e2e_eager_ms * 1e-3) / 1e9},
         "gpu_launches": launches,
