@@ -55,6 +55,7 @@ _SIGNATURES = {
         "bn_host_rank_table": [_vp, _vp, _vp],
         "bn_host_rice_encode": [_vp, _vp, _i64, _i64, _vp, _vp, _vp, _u64, C.POINTER(_u64), _int],
         "bn_host_rice_encode_ranks": [_vp, _i64, _i64, _vp, _vp, _vp, _u64, C.POINTER(_u64), _int],
+        "bn_host_f1_encode": [_vp, _vp, _i64, _i64, _vp, _vp, _u64, _vp, _u64, _vp, _int],
     },
 }
 _FILES = {"cuda": "libbinade_b200.so", "host": "libbinade_b200_host.so"}

@@ -183,6 +183,104 @@ int encode_rows(const RankRows &src, int64_t R, int64_t K, uint8_t *meta, uint32
   return BN_OK;
 }
 
+
+// ---------------------------------------------------------------------------------------------
+// Format 1 (binade/format.py): fixed-width codes with escapes. A tile of 128 ranks (rows padded
+// with rank 0) is stored with b bits per code in exactly 4 b words, code i at bits i b .., LSB
+// first; in escape mode the code 2^b - 1 stands for "next byte of the escape stream", which holds
+// the weight's exponent. meta = b | 16 (escape mode). The width is the cheapest of: fixed
+// (b = bit length of the largest rank, 128 b bits) and escape widths 1..4 (128 b + 8 per escaped
+// weight); ties go to fixed, then to the smaller escape width (binade/format.py:46-60).
+// ---------------------------------------------------------------------------------------------
+inline void f1_choose(const uint8_t *r, int *b_out, bool *esc_out) {
+  int rmax = 0;
+  for (int i = 0; i < TILE; i++) rmax = std::max(rmax, (int)r[i]);
+  int fixed_b = 0;
+  while ((1 << fixed_b) <= rmax) fixed_b++;
+  int64_t best = (int64_t)TILE * fixed_b;
+  int b = fixed_b;
+  bool esc = false;
+  for (int w = 1; w <= 4; w++) {
+    int over = 0;
+    for (int i = 0; i < TILE; i++) over += r[i] >= (1 << w) - 1;
+    const int64_t c = (int64_t)TILE * w + 8 * over;
+    if (c < best) best = c, b = w, esc = true;
+  }
+  *b_out = b, *esc_out = esc;
+}
+
+int f1_encode(const uint16_t *w, const uint8_t *rank, int64_t R, int64_t K, uint8_t *meta, uint32_t *idx, uint64_t cap_idx, uint8_t *esc, uint64_t cap_esc, uint64_t *counts, int threads) {
+  const int64_t T = (K + TILE - 1) / TILE;
+  const int nt = pick_threads(threads, R);
+  std::vector<uint64_t> row_words((size_t)R), row_esc((size_t)R);
+  auto run = [&](auto &&fn) {
+    std::vector<std::thread> pool;
+    const int64_t per = (R + nt - 1) / nt;
+    for (int i = 0; i < nt; i++) {
+      const int64_t r0 = std::min<int64_t>(R, i * per), r1 = std::min<int64_t>(R, r0 + per);
+      if (r0 < r1) pool.emplace_back(fn, r0, r1);
+    }
+    for (auto &t : pool) t.join();
+  };
+  auto tile_ranks = [&](int64_t row, int64_t t, uint8_t *r) {
+    const int n = (int)std::min<int64_t>(TILE, K - t * TILE);
+    const uint16_t *src = w + row * K + t * TILE;
+    for (int i = 0; i < n; i++) r[i] = rank[(src[i] >> 7) & 0xFF];
+    for (int i = n; i < TILE; i++) r[i] = 0;  // padding: the most common exponent
+    return n;
+  };
+  // pass 1: widths, and how many words and escapes each row takes
+  run([&](int64_t r0, int64_t r1) {
+    uint8_t r[TILE];
+    for (int64_t row = r0; row < r1; row++) {
+      uint64_t words = 0, escapes = 0;
+      for (int64_t t = 0; t < T; t++) {
+        tile_ranks(row, t, r);
+        int b;
+        bool em;
+        f1_choose(r, &b, &em);
+        meta[row * T + t] = (uint8_t)(b | (em ? 16 : 0));
+        words += 4 * (uint64_t)b;
+        if (em)
+          for (int i = 0; i < TILE; i++) escapes += r[i] >= (1 << b) - 1;
+      }
+      row_words[(size_t)row] = words, row_esc[(size_t)row] = escapes;
+    }
+  });
+  uint64_t nw = 0, ne = 0;
+  std::vector<uint64_t> w_at((size_t)R), e_at((size_t)R);
+  for (int64_t row = 0; row < R; row++) w_at[(size_t)row] = nw, e_at[(size_t)row] = ne, nw += row_words[(size_t)row], ne += row_esc[(size_t)row];
+  counts[0] = nw, counts[1] = ne;
+  if ((nw && !idx) || nw > cap_idx || (ne && !esc) || ne > cap_esc) return fail(BN_ERR_CAPACITY, "format-1 buffers too small (size them from counts)");
+  // pass 2: the index words and the escape bytes, every row at its own place
+  run([&](int64_t r0, int64_t r1) {
+    uint8_t r[TILE];
+    for (int64_t row = r0; row < r1; row++) {
+      uint32_t *out = idx + w_at[(size_t)row];
+      uint8_t *eout = esc + e_at[(size_t)row];
+      for (int64_t t = 0; t < T; t++) {
+        const int n = tile_ranks(row, t, r);
+        const uint8_t m = meta[row * T + t];
+        const int b = m & 15;
+        const bool em = (m & 16) != 0;
+        const int cmax = (1 << b) - 1;
+        uint64_t acc = 0;
+        int fill = 0;
+        for (int i = 0; i < TILE; i++) {
+          int code = r[i];
+          if (em && code >= cmax) {
+            code = cmax;
+            *eout++ = (uint8_t)(i < n ? (w[row * K + t * TILE + i] >> 7) & 0xFF : 0);  // (padding never escapes: its rank is 0 and cmax >= 1)
+          }
+          acc |= (uint64_t)code << fill, fill += b;
+          if (fill >= 32) *out++ = (uint32_t)acc, acc >>= 32, fill -= 32;
+        }
+      }
+    }
+  });
+  return BN_OK;
+}
+
 }  // namespace
 
 extern "C" int bn_host_rice_encode(const uint16_t *w, const uint8_t *rank, int64_t R, int64_t K, uint8_t *meta, uint32_t *roff, uint32_t *words, uint64_t cap_words, uint64_t *nwords, int threads) {
@@ -193,4 +291,9 @@ extern "C" int bn_host_rice_encode(const uint16_t *w, const uint8_t *rank, int64
 extern "C" int bn_host_rice_encode_ranks(const uint8_t *ranks, int64_t R, int64_t K, uint8_t *meta, uint32_t *roff, uint32_t *words, uint64_t cap_words, uint64_t *nwords, int threads) {
   if (!ranks || !meta || !roff || !nwords || R < 0 || K <= 0) return fail(BN_ERR_ARG, "bn_host_rice_encode_ranks: null pointer or bad size");
   return encode_rows(RankRows{ranks, nullptr, nullptr}, R, K, meta, roff, words, cap_words, nwords, threads);
+}
+
+extern "C" int bn_host_f1_encode(const uint16_t *w, const uint8_t *rank, int64_t R, int64_t K, uint8_t *meta, uint32_t *idx, uint64_t cap_idx, uint8_t *esc, uint64_t cap_esc, uint64_t *counts, int threads) {
+  if (!w || !rank || !meta || !counts || R < 0 || K <= 0) return fail(BN_ERR_ARG, "bn_host_f1_encode: null pointer or bad size");
+  return f1_encode(w, rank, R, K, meta, idx, cap_idx, esc, cap_esc, counts, threads);
 }

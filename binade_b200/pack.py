@@ -24,12 +24,12 @@ import numpy as np
 
 from . import _native, rice, st
 from .classify import MIN_DIM, classify
-from .format import TILE, rank_table
+from .format import TILE, encode_words as f1_encode_words, rank_table
 
 VERSION = "2"
 CLASSES = ("linear", "embed", "ple", "mm")
 CHUNK = 1 << 24  # weights per read
-PARTS = {"2": ("raw", "table", "meta", "bits", "roff")}
+PARTS = {"1": ("raw", "table", "meta", "idx", "esc"), "2": ("raw", "table", "meta", "bits", "roff")}
 KNOWN_SUFFIXES = ("raw", "table", "meta", "idx", "esc", "bits", "roff")  # of either on-disk format
 REPO = Path(__file__).resolve().parents[1]
 
@@ -108,9 +108,12 @@ def bits_per_weight(p: dict) -> float:
 
 
 def pack_tensor(w: st.Writer, info: st.TensorInfo, chunk: int = CHUNK, version: str = VERSION, gpu: bool = False) -> dict:
-    """gpu: histogram, raw bytes and the Rice streams on the CUDA device (the same bytes)."""
-    if version != "2":
-        raise NotImplementedError("only format 2 (Rice) is implemented")
+    """gpu: histogram, raw bytes and the Rice streams on the CUDA device (the same bytes; format 2
+    only). version "1": fixed-width codes with escapes (binade/format.py), encoded on host cores."""
+    if version not in PARTS:
+        raise ValueError(f"unknown Binade format {version!r}")
+    if version == "1":
+        return _pack_tensor_f1(w, info, chunk)
     if gpu:
         from .cuda import kernels as ck
     hist = np.zeros(256, np.int64)
@@ -149,6 +152,30 @@ def pack_tensor(w: st.Writer, info: st.TensorInfo, chunk: int = CHUNK, version: 
     return {"numel": info.numel, "distinct": int((hist > 0).sum()), "ntiles": int(meta.size), "bits": bits}
 
 
+def _pack_tensor_f1(w: st.Writer, info: st.TensorInfo, chunk: int = CHUNK) -> dict:
+    """Format 1 of one tensor: raw, table, meta, idx, esc (reference: binade/pack.py:72-93). Tiles
+    are whole per row, so the spans' arrays simply follow each other."""
+    hist = np.zeros(256, np.int64)
+    for span in spans(info, chunk):
+        _histogram(np.ascontiguousarray(st.read(info, span)), hist)
+    table, rank = rank_table(hist)
+    metas, words, escapes = [], [], []
+    w.begin(info.name + ".raw", "U8", info.shape)
+    for span in spans(info, chunk):
+        u = np.ascontiguousarray(st.read(info, span))
+        w.write(_raw(u))
+        meta, idx, esc = f1_encode_words(u, rank)
+        metas.append(meta), words.append(idx), escapes.append(esc)
+    w.end()
+    meta, idx, esc = np.concatenate(metas), np.concatenate(words), np.concatenate(escapes)
+    w.add(info.name + ".table", table)
+    w.add(info.name + ".meta", meta)
+    w.add(info.name + ".idx", idx)
+    w.add(info.name + ".esc", esc)
+    bits = 8 * info.numel + 8 * table.size + 8 * meta.size + 32 * idx.size + 8 * esc.size
+    return {"numel": info.numel, "distinct": int((hist > 0).sum()), "ntiles": int(meta.size), "escapes": int(esc.size), "bits": bits}
+
+
 def copy_tensor(w: st.Writer, info: st.TensorInfo, chunk: int = CHUNK) -> None:
     w.begin(info.name, info.dtype, info.shape)
     if len(info.shape) < 2:
@@ -167,10 +194,10 @@ def _header_room(infos, classes, metadata, version) -> int:
 
 
 def pack_model(src: Path, out: Path, classes=CLASSES, chunk: int = CHUNK, log=print, version: str = VERSION, gpu: bool = False) -> dict:
-    if version == "1":
-        raise NotImplementedError("format 1 is not implemented in this package")
     if version not in PARTS:
         raise ValueError(f"unknown Binade format {version!r}")
+    if version == "1" and gpu:
+        raise ValueError("the GPU encoder writes format 2 only")
     src, out = Path(src), Path(out)
     started = time.perf_counter()
     out.mkdir(parents=True, exist_ok=True)
@@ -225,7 +252,7 @@ def main():
     ap.add_argument("--out", type=Path, required=True)
     ap.add_argument("--revision")
     ap.add_argument("--classes", default=",".join(CLASSES))
-    ap.add_argument("--format", default=VERSION, choices=sorted(PARTS), help="2: Rice (decoded to R4 at load)")
+    ap.add_argument("--format", default=VERSION, choices=sorted(PARTS), help="2: Rice (smaller; decoded to R4 at load), 1: fixed-width codes with escapes")
     ap.add_argument("--gpu", action="store_true", help="encode on the CUDA device instead of the host cores (same bytes)")
     args = ap.parse_args()
     r = pack_model(st.resolve(args.model, args.revision), args.out, tuple(args.classes.split(",")), version=args.format, gpu=args.gpu)

@@ -312,6 +312,15 @@ int bn_host_rice_encode(const uint16_t *w, const uint8_t *rank, int64_t R, int64
 int bn_host_rice_encode_ranks(const uint8_t *ranks, int64_t R, int64_t K, uint8_t *meta, uint32_t *roff,
                               uint32_t *words, uint64_t cap_words, uint64_t *nwords, int threads);
 
+/* Format-1 encoder (binade/format.py:46-101: choose, pack_codes, encode) straight from BF16 words:
+ * meta [R*T] = b | 16 (escape mode), idx = the tiles' index words (a tile of width b is 4 b
+ * words), esc = exponent bytes of the escaped weights in tensor order. counts[0], counts[1] =
+ * words and escapes needed; BN_ERR_CAPACITY when a buffer is smaller (call once with zero
+ * capacities to size them). */
+int bn_host_f1_encode(const uint16_t *w, const uint8_t *rank, int64_t R, int64_t K, uint8_t *meta,
+                      uint32_t *idx, uint64_t cap_idx, uint8_t *esc, uint64_t cap_esc,
+                      uint64_t *counts, int threads);
+
 #ifdef __cplusplus
 }
 #endif

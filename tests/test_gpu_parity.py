@@ -286,15 +286,21 @@ def test_transcode_all_escapes_grows_scratch():
     assert np.array_equal(words(r4.R4Linear(a).dense()), u)
 
 
-def test_streamed_load_equals_plain_load():
+@pytest.mark.parametrize("which", ["packed", "packed_v1"])
+def test_streamed_load_equals_plain_load(which):
     """stream_r4 (reader thread -> pinned buffers -> copy stream -> expander) gives the arrays
     that reading every file array and transcoding it gives, for every packed weight of the golden
-    packed model, in the order asked for; a name that is not packed raises at that name."""
+    packed models (format 2 and format 1, both written by the reference's packer), in the order
+    asked for; the unpacked tensors are the source model's; a name that is not packed raises."""
+    from binade_b200 import st
     from binade_b200.cuda import r4
     from binade_b200.cuda.stream_load import stream_r4
     from binade_b200.unpack import PackedModel
 
-    pm = PackedModel(GOLDEN / "packed_model" / "packed")
+    pm = PackedModel(GOLDEN / "packed_model" / which)
+    source = {i.name: i for i in st.list_tensors(GOLDEN / "packed_model" / "src")}
+    for name in pm.packed:
+        assert np.array_equal(pm.tensor(name), st.read(source[name])), name
     plain = {name: r4.transcode(h) for name, h in r4.holders(pm).items()}
     assert len(plain) >= 3
     seen = []

@@ -134,6 +134,60 @@ def test_pack_model_is_byte_identical_to_the_reference(tmp_path):
         pack.pack_model(src, tmp_path / "x", version="3")
 
 
+def test_pack_model_format1_is_byte_identical_to_the_reference(tmp_path):
+    """pack_model(version="1"): the shard the reference's packer wrote for the same source model
+    (tests/golden/make_golden_format1_model.py), byte for byte, index included."""
+    src, out = _source_model(tmp_path), tmp_path / "packed1"
+    report = pack.pack_model(src, out, chunk=5000, log=lambda *_: None, version="1")
+    want = GOLDEN / "packed_model" / "packed_v1"
+    got = (out / "model.safetensors").read_bytes()
+    assert got == (want / "model.safetensors").read_bytes()
+    assert hashlib.sha256(got).hexdigest() == (GOLDEN / "packed_model" / "SHA256_v1").read_text().split()[0]
+    assert (out / st.INDEX).read_text() == (want / st.INDEX).read_text()
+    assert pack.pack_meta(out) == pack.quant("1")
+    infos = {i.name: i for i in st.list_tensors(out)}
+    assert "lm_head.weight.idx" in infos and "lm_head.weight.esc" in infos and "lm_head.weight.bits" not in infos
+    assert report["packed_bits"] < 16 * report["packed_numel"]
+    with pytest.raises(ValueError):
+        pack.pack_model(src, tmp_path / "y", version="1", gpu=True)
+
+
+@pytest.mark.parametrize("shape", [(16, 512), (8, 128), (6, 1280), (5, 100), (3, 1), (40, 4), (2, 2000)])
+def test_format1_encoder_matches_the_restated_reference(shape):
+    """format.encode_words (C++, all cores) against the numpy restatement of binade/format.py on
+    short last tiles, rows shorter than a tile, rare large exponents (escape mode) and uniformly
+    random words (fixed widths up to 8 bits)."""
+    from binade_b200 import format as fmt
+
+    rng = np.random.default_rng(sum(shape))
+    for kind in ("normal", "uniform", "const"):
+        if kind == "normal":
+            w = (rng.standard_normal(shape) * 0.02).astype(np.float32)
+            u = (w.view(np.uint32) >> 16).astype(np.uint16)
+            u.reshape(-1)[3::17] = 0x7F80 - 0x0080 * rng.integers(1, 40, size=u.reshape(-1)[3::17].shape).astype(np.uint16)
+        elif kind == "uniform":
+            u = rng.integers(0, 1 << 16, size=shape, dtype=np.uint16)
+        else:
+            u = np.full(shape, 0x3C00, np.uint16)
+        exps = ((u >> 7) & 0xFF).astype(np.uint8)
+        table, rank = fmt.rank_table(np.bincount(exps.ravel(), minlength=256))
+        meta, idx, esc = fmt.encode_words(u, rank)
+        want_meta, want_idx, want_esc = o.np_f1_encode(exps, table, rank)
+        assert np.array_equal(meta, want_meta) and np.array_equal(idx, want_idx) and np.array_equal(esc, want_esc), kind
+        assert np.array_equal(o.np_f1_decode(meta, idx, esc, table, *shape), exps)
+
+
+def test_format1_encoder_golden():
+    """The reference's own format-1 arrays (tests/golden/format1.npz, written by its encoder)."""
+    from binade_b200 import format as fmt
+
+    f1, r4 = golden("format1.npz"), golden("r4_layout.npz")
+    assert len(f1) >= 3
+    for case in f1:
+        meta, idx, esc = fmt.encode_words(r4[case]["w"], r4[case]["rank"])
+        assert np.array_equal(meta, f1[case]["meta"]) and np.array_equal(idx, f1[case]["idx"]) and np.array_equal(esc, f1[case]["esc"]), case
+
+
 def test_st_reader_and_writer(tmp_path):
     rng = np.random.default_rng(1)
     a = rng.integers(0, 1 << 16, size=(6, 10), dtype=np.uint16)
