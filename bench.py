@@ -654,9 +654,26 @@ def prefill_leg(torch, dev, graph_us, rows=(2, 4, 8, 16, 32, 128, 256, 512, 2048
         # sum |w x| (an output that nearly cancels is many of its own ulps away after any reordering)
         scale = torch.exp2(torch.floor(torch.log2((x.float().abs() @ w.float().abs().T).clamp_min(1e-30))) - 7)
         rel = ((got.float() - ref.float()).abs() / scale).max().item()
-        out[str(M)] = {"us": round(us, 1), "cublas_bf16_us": round(us_ref, 1), "vs_cublas": round(us_ref / us, 3), "path": path, "max_ulp": int(ulp.max().item()), "outputs_not_identical": round(float((ulp > 0).float().mean().item()), 5), "outputs_beyond_1_ulp": round(float((ulp > 1).float().mean().item()), 6), "max_err_in_ulps_of_sum_abs": round(rel, 4)}
+        # and against cuBLAS itself on the pre-decoded weight: how many outputs carry the same bits
+        same_as_cublas = float((got.view(torch.int16) == torch.matmul(x, w.T).view(torch.int16)).float().mean().item())
+        out[str(M)] = {"us": round(us, 1), "cublas_bf16_us": round(us_ref, 1), "vs_cublas": round(us_ref / us, 3), "path": path, "outputs_identical_to_cublas": round(same_as_cublas, 6), "max_ulp": int(ulp.max().item()), "outputs_not_identical": round(float((ulp > 0).float().mean().item()), 5), "outputs_beyond_1_ulp": round(float((ulp > 1).float().mean().item()), 6), "max_err_in_ulps_of_sum_abs": round(rel, 4)}
         if M <= r4.MMA_MAX_ROWS * r4.MMA_MAX_PASSES:
             out[str(M)]["rebuild_us"] = round(graph_us(lambda i: x @ m.dense().reshape(n, k).T, iters=10), 1)
+    # the order of cuBLAS: the split-K count with which the tensor-core kernel gives the bits of
+    # torch's BF16 matmul on the decoded weight, for this matrix and for the down projection
+    # (long K: cuBLAS splits K for few rows), each checked on fresh inputs
+    if any(M <= r4.MMA_MAX_ROWS for M in rows):
+        mirror = {}
+        for name, nn_, kk_ in (("gate_15360x3840", n, k), ("down_3840x15360", 3840, 15360)):
+            wd = w if (nn_, kk_) == (n, k) else ck.to_device(synthetic_weight("down", nn_, kk_)).view(torch.bfloat16)
+            md = m if wd is w else r4.R4Linear(r4.from_dense(wd))
+            plan = md.mirror_cublas(rows=(8, 16, 32, 128))
+            same = {}
+            for M, split in plan.items():
+                xm = torch.randn((M, kk_), device=dev, generator=torch.Generator(device=dev).manual_seed(1000 + M)).to(torch.bfloat16)
+                same[str(M)] = {"split_k": split, "outputs_identical_to_cublas": round(float((md.mma_rows(xm).view(torch.int16) == (xm @ wd.T).view(torch.int16)).float().mean().item()), 6)}
+            mirror[name] = same
+        out["cublas_order"] = mirror
     return out
 
 

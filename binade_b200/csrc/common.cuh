@@ -49,7 +49,7 @@ int direct_matvec(const bn_r4 *w, const uint16_t *x, int64_t N, int64_t K, uint1
 int direct_gather(const bn_r4 *w, const uint16_t *x, const uint32_t *xi, const uint32_t *ei, int64_t G, int64_t n, int64_t K, int64_t RS, int64_t R0, int64_t split, uint16_t *y, uint16_t *y2, cudaStream_t s);
 
 // Tensor-core decode GEMM for up to 128 input rows (r4_mma.cu); -1 outside its coverage.
-int mma_rows(const bn_r4 *w, const uint16_t *x, int64_t x_stride, int64_t M, int64_t N, int64_t K, uint16_t *y, int64_t y_stride, cudaStream_t s);
+int mma_rows(const bn_r4 *w, const uint16_t *x, int64_t x_stride, int64_t M, int64_t N, int64_t K, uint16_t *y, int64_t y_stride, int split, cudaStream_t s);
 int mma_status(int *status);
 int exchange_status(int *status);  // exchange.cu
 int exchange_status_reset();

@@ -103,6 +103,10 @@ struct MmaArgs {
   int T, M, BN, stages;
   int rows;  // weight rows per block (a multiple of MMA_RPW, at most MMA_ROWS)
   uint32_t tmem_cols;
+  // split-K as cuBLAS does it for few input rows and long K: `split` equal slices of the K tiles,
+  // each summed from zero into its own accumulator (BN columns apart in tensor memory), the
+  // slices' fp32 sums added in slice order, then one rounding to BF16
+  int split, slice_tiles;
 };
 
 // Byte offset of (row r, 16-byte chunk c of the row's 128 bytes) inside a swizzled atom.
@@ -115,7 +119,7 @@ struct MmaWindow {
 };
 
 // The MMA warp: TMA copies of X and the MMAs of every k-tile. Returns false when a wait gave up.
-__device__ __forceinline__ bool mma_issue_side(const CUtensorMap *x_map, const MmaWindow &m, int T, int S, int BN, uint32_t tmem, uint32_t lane, bool ok) {
+__device__ __forceinline__ bool mma_issue_side(const CUtensorMap *x_map, const MmaWindow &m, int T, int S, int BN, int slice_tiles, uint32_t tmem, uint32_t lane, bool ok) {
   const uint32_t idesc = mma_idesc(MMA_BM, BN);
   auto fetch_x = [&](int t, int s) {  // X tile of k-tile t into slot s, which must be free
     const uint32_t b_s = m.b_at + (uint32_t)s * m.b_stage;
@@ -128,6 +132,8 @@ __device__ __forceinline__ bool mma_issue_side(const CUtensorMap *x_map, const M
   __syncwarp();
   int s = 0, sp = 0;        // slot of tile t, slot of tile t - 1
   uint32_t ph = 0, php = 0;  // parity of their current phases
+  int in_slice = 0;          // tile index inside the current K slice
+  uint32_t acc = tmem;       // the slice's accumulator
   for (int t = 0; t < T; t++) {
     if (ok) ok = mm_bar_wait(m.full + 8 * s, ph);
     tc_fence_after();
@@ -137,7 +143,7 @@ __device__ __forceinline__ bool mma_issue_side(const CUtensorMap *x_map, const M
       for (int j = 0; j < MMA_BK / 16; j++) {  // 16 k per MMA: 32 bytes further along the swizzled row
         const uint64_t da = smem_desc(a_s + (j >> 2) * (MMA_BM * 128u) + (j & 3) * 32u);
         const uint64_t db = smem_desc(b_s + (j >> 2) * ((uint32_t)BN * 128u) + (j & 3) * 32u);
-        mma_bf16(tmem, da, db, idesc, (t | j) != 0);
+        mma_bf16(acc, da, db, idesc, (in_slice | j) != 0);
       }
       mma_commit(m.empty + 8 * s);  // arrives when these MMAs have read the stage
     }
@@ -152,6 +158,7 @@ __device__ __forceinline__ bool mma_issue_side(const CUtensorMap *x_map, const M
     }
     sp = s, php = ph;
     if (++s == S) s = 0, ph ^= 1u;
+    if (++in_slice == slice_tiles) in_slice = 0, acc += (uint32_t)BN;
   }
   if (lane == 0 && ok) mma_commit(m.done);
   __syncwarp();
@@ -166,14 +173,19 @@ __device__ __forceinline__ void mma_store_side(const MmaArgs &a, const MmaWindow
   const int r = (int)(warp * 32 + lane);
   if (!ok) return;
   for (int c = 0; c < a.BN; c += 8) {
-    uint32_t v[8];
-    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
-                 : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7])
-                 : "r"(tmem + ((warp * 32u) << 16) + (uint32_t)c));
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+    float sum[8];
+    for (int sl = 0; sl < a.split; sl++) {  // the slices' sums, added in slice order
+      uint32_t v[8];
+      asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+                   : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7])
+                   : "r"(tmem + ((warp * 32u) << 16) + (uint32_t)(sl * a.BN + c)));
+      asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+      for (int i = 0; i < 8; i++) sum[i] = sl ? sum[i] + __uint_as_float(v[i]) : __uint_as_float(v[i]);
+    }
 #pragma unroll
     for (int i = 0; i < 8; i++)
-      if (c + i < a.M && r < rows) a.y[(int64_t)(c + i) * a.y_stride + row_base + r] = f32_to_bf16_bits(__uint_as_float(v[i]));
+      if (c + i < a.M && r < rows) a.y[(int64_t)(c + i) * a.y_stride + row_base + r] = f32_to_bf16_bits(sum[i]);
   }
 }
 
@@ -284,7 +296,7 @@ __global__ void __launch_bounds__((DW + 1) * 32, 1) r4_mma_kernel(const __grid_c
       if (++s == S) s = 0, ph ^= 1u;
     }
   } else if (warp == MMA_DECODE_WARPS) {
-    ok = mma_issue_side(&x_map, win, T, S, BN, tmem, lane, ok);
+    ok = mma_issue_side(&x_map, win, T, S, BN, a.slice_tiles, tmem, lane, ok);
   }
   if (warp < 4) mma_store_side(a, win, tmem, warp, lane, row_base, rows, ok);
   tc_fence_before();
@@ -440,7 +452,7 @@ __global__ void __launch_bounds__((MAXW + 1) * 32, 1) r4_mma_oct_kernel(const __
     }
     cp_wait<0>();
   } else if (warp == MAXW) {
-    ok = mma_issue_side(&x_map, win, T, S, BN, tmem, lane, ok);
+    ok = mma_issue_side(&x_map, win, T, S, BN, a.slice_tiles, tmem, lane, ok);
   }
   if (warp < 4) mma_store_side(a, win, tmem, warp, lane, row_base, rows, ok);
   tc_fence_before();
@@ -472,15 +484,17 @@ static int mma_sms() {
 }
 
 // Fused decode GEMM for up to 256 input rows (the MMA's largest N); -1 when the shape is outside its coverage.
-int mma_rows(const bn_r4 *w, const uint16_t *x, int64_t x_stride, int64_t M, int64_t N, int64_t K, uint16_t *y, int64_t y_stride, cudaStream_t s) {
+int mma_rows(const bn_r4 *w, const uint16_t *x, int64_t x_stride, int64_t M, int64_t N, int64_t K, uint16_t *y, int64_t y_stride, int split, cudaStream_t s) {
   if (M < 1 || M > 256 || K % 8 || x_stride % 8 || N < 1 || ((uintptr_t)x & 15)) return -1;
+  if (split < 1 || tiles(K) % split || ((M + 15) / 16 * 16) * split > 512) return -1;  // whole tiles per slice, all accumulators in tensor memory
   TensorMapEncodeFn encode = tensor_map_encoder();
   if (!encode) return fail(BN_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
   MmaArgs a{};
   a.w = *w, a.y = y, a.N = N, a.K = K, a.y_stride = y_stride;
   a.T = (int)tiles(K), a.M = (int)M, a.BN = (int)((M + 15) / 16 * 16);
+  a.split = split, a.slice_tiles = a.T / split;
   a.tmem_cols = 32;
-  while ((int)a.tmem_cols < a.BN) a.tmem_cols *= 2;
+  while ((int)a.tmem_cols < a.BN * split) a.tmem_cols *= 2;
   // X as a 2-D tensor [M rows, K columns] of BF16; a box is 64 columns (one 128-byte swizzled row
   // each) of BN rows; rows past M and columns past K read as zeros
   CUtensorMap x_map;
@@ -541,11 +555,16 @@ int mma_status(int *status) {
 
 }  // namespace bn
 
-extern "C" int bn_r4_mma(const uint16_t *x, int64_t x_stride, const bn_r4 *w, int64_t M, int64_t N, int64_t K, uint16_t *y, int64_t y_stride, void *stream) {
+extern "C" int bn_r4_mma_split(const uint16_t *x, int64_t x_stride, const bn_r4 *w, int64_t M, int64_t N, int64_t K, uint16_t *y, int64_t y_stride, int split, void *stream) {
   if (!w || !w->raw || !w->codes || !w->flags || !w->esc || !w->table || !w->row_esc) return bn::fail(BN_ERR_ARG, "bn_r4_mma: null R4 array");
   if (!x || !y || N < 0 || K <= 0 || M < 1 || M > 256) return bn::fail(BN_ERR_ARG, "bn_r4_mma: bad size (1 <= M <= 256) or null pointer");
   if (K % 8 || x_stride % 8) return bn::fail(BN_ERR_ARG, "bn_r4_mma needs K % 8 == 0 and x rows 16-byte aligned");
+  if (split < 1) return bn::fail(BN_ERR_ARG, "bn_r4_mma_split: split must be at least 1");
   if (N == 0) return BN_OK;
-  const int e = bn::mma_rows(w, x, x_stride, M, N, K, y, y_stride, (cudaStream_t)stream);
-  return e == -1 ? bn::fail(BN_ERR_ARG, "bn_r4_mma: shape does not fit shared memory") : e;
+  const int e = bn::mma_rows(w, x, x_stride, M, N, K, y, y_stride, split, (cudaStream_t)stream);
+  return e == -1 ? bn::fail(BN_ERR_ARG, "bn_r4_mma: shape does not fit shared or tensor memory, or the K tiles do not divide into the slices") : e;
+}
+
+extern "C" int bn_r4_mma(const uint16_t *x, int64_t x_stride, const bn_r4 *w, int64_t M, int64_t N, int64_t K, uint16_t *y, int64_t y_stride, void *stream) {
+  return bn_r4_mma_split(x, x_stride, w, M, N, K, y, y_stride, 1, stream);
 }

@@ -290,12 +290,13 @@ def r4_gather_grouped(a: dict, x: torch.Tensor, xi: torch.Tensor, ei: torch.Tens
     return (y, y2) if split else y
 
 
-def r4_mma(a: dict, x: torch.Tensor, N: int, K: int) -> torch.Tensor:
+def r4_mma(a: dict, x: torch.Tensor, N: int, K: int, split: int = 1) -> torch.Tensor:
     """x [M, K] (1 <= M <= 256, bfloat16, contiguous rows, K % 8 == 0) -> [M, N] through the fused
-    decode GEMM on the tensor cores (tcgen05); accumulation order is the hardware's."""
+    decode GEMM on the tensor cores (tcgen05); accumulation order is the hardware's. split: the K
+    tiles in that many equal slices, summed apart and added in fp32 (cuBLAS's split-K order)."""
     M = x.shape[0]
     y = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
-    _call("bn_r4_mma", _p(x), x.stride(0), ctypes.byref(r4_struct(a)), M, N, K, _p(y), N)
+    _call("bn_r4_mma_split", _p(x), x.stride(0), ctypes.byref(r4_struct(a)), M, N, K, _p(y), N, split)
     return y
 
 

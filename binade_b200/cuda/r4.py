@@ -178,16 +178,45 @@ class _R4:
         M = x.numel() // self.K
         return ck.r4_rows(self._a, x.reshape(M, self.K).contiguous(), self.N, self.K).reshape(*x.shape[:-1], self.N)
 
-    def mma_rows(self, x: torch.Tensor) -> torch.Tensor:
+    def mma_rows(self, x: torch.Tensor, split: int | None = None) -> torch.Tensor:
         """x [..., K] -> [..., N] through the tensor-core decode GEMM, 256 rows a pass (weights
-        decoded to BF16 inside the kernel and read once; the sum over K in the hardware's order)."""
+        decoded to BF16 inside the kernel and read once; the sum over K in the hardware's order:
+        16 k per MMA step, in order, from zero). split: the K tiles in that many equal slices,
+        summed apart and added in fp32; default: what `mirror_cublas` found for this row count,
+        else 1."""
         M = x.numel() // self.K
         x2 = x.reshape(M, self.K).contiguous()
+        if split is None:
+            split = getattr(self, "_cublas_split", {}).get(M, 1)
         if M <= MMA_MAX_ROWS:
-            y = ck.r4_mma(self._a, x2, self.N, self.K)
+            y = ck.r4_mma(self._a, x2, self.N, self.K, split)
         else:  # a pass over the weights per 256 rows: still cheaper than rebuilding them for a few passes
-            y = torch.cat([ck.r4_mma(self._a, x2[m0 : m0 + MMA_MAX_ROWS], self.N, self.K) for m0 in range(0, M, MMA_MAX_ROWS)])
+            y = torch.cat([ck.r4_mma(self._a, x2[m0 : m0 + MMA_MAX_ROWS], self.N, self.K, split) for m0 in range(0, M, MMA_MAX_ROWS)])
         return y.reshape(*x.shape[:-1], self.N)
+
+    def mirror_cublas(self, rows=(8, 16, 32, 64, 128, 256), seed: int = 0) -> dict:
+        """For each row count M, find the split-K count with which `mma_rows` reproduces, bit for
+        bit, this device's BF16 GEMM (`x @ W.T` of torch, i.e. cuBLAS) on the decoded weight, and
+        remember it for later `mma_rows` calls of that row count. The reference reads cuBLASLt's
+        heuristic and mirrors its split-K schemes (binade/mlx/cublas_plan.py:84-192); here the
+        plan is found by trying: on B200 cuBLAS sums 16 k per tensor-core step in order from zero,
+        as this kernel does, and for few rows and long K cuts K in two halves whose fp32 sums it
+        adds. Returns {M: split, or None when no candidate matches}. Needs the dense weight for
+        the comparison (rebuilt once, freed on return)."""
+        dense = self.dense().reshape(self.N, self.K)
+        g = torch.Generator(device=dense.device).manual_seed(seed)
+        found, self._cublas_split = {}, getattr(self, "_cublas_split", {})
+        for M in rows:
+            x = torch.randn((M, self.K), device=dense.device, generator=g).to(torch.bfloat16)
+            want = (x @ dense.T).view(torch.int16)
+            found[M] = None
+            for split in (1, 2, 3, 4, 6, 8):
+                if self.T % split or split * (-(-M // 16) * 16) > 512:
+                    continue
+                if torch.equal(self.mma_rows(x, split).view(torch.int16), want):
+                    found[M] = self._cublas_split[M] = split
+                    break
+        return found
 
     def _rows(self, x: torch.Tensor) -> torch.Tensor:
         M = x.numel() // self.K

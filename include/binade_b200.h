@@ -194,6 +194,16 @@ int bn_f1_to_r4(const uint8_t *meta, const uint32_t *idx, uint64_t nwords, const
 int bn_r4_mma(const uint16_t *x, int64_t x_stride, const bn_r4 *w, int64_t M, int64_t N, int64_t K,
               uint16_t *y, int64_t y_stride, void *stream);
 
+/* The same product with the K tiles cut into `split` equal slices, each summed from zero in its
+ * own tensor-memory accumulator, the slices' fp32 sums added in slice order and rounded once:
+ * the order cuBLAS uses on B200 when it splits K (few input rows, long K; measured: split = 2,
+ * fp32 partials). With the split cuBLAS picks for a shape (1 where it does not split) the output
+ * carries the bits of a BF16 GEMM on the decoded weight. Replaces the split-K mirroring of
+ * binade/mlx/cublas_plan.py:84-192 and the reducers binade/mlx/cuda_kernels.py:685-702.
+ * ceil(K/128) % split == 0 and split * (M rounded up to 16) <= 512. */
+int bn_r4_mma_split(const uint16_t *x, int64_t x_stride, const bn_r4 *w, int64_t M, int64_t N,
+                    int64_t K, uint16_t *y, int64_t y_stride, int split, void *stream);
+
 /* Embedding lookup from an R4 table of `rows` rows: out [n,K] row i = BF16 row ids[i]; an id
  * >= rows gives a row of zeros. Replaces R4Embedding.__call__, binade/mlx/r4.py:308-322 (a graph
  * of elementwise array ops there; one kernel here, no host synchronisation either). */

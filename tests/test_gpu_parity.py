@@ -715,6 +715,38 @@ def test_mma_decodes_every_weight(N, K, density):
                 break  # the big case: a few column blocks are enough
 
 
+@pytest.mark.parametrize("N,K", [(384, 1024), (520, 3840), (256, 15360), (128, 16384)])
+def test_mma_rows_in_the_order_of_cublas(N, K):
+    """Split-K in the kernel (every slice from zero in its own accumulator, fp32 sums added in
+    slice order) against the same sums built from one-slice calls; and `mirror_cublas`: for every
+    row count a split is found with which the outputs are, bit for bit, those of torch's BF16
+    matmul on the decoded weight, also where cuBLAS itself splits K (long K, few rows)."""
+    from binade_b200.cuda import kernels as ck
+    from binade_b200.cuda import r4
+
+    rng = np.random.default_rng(N + K)
+    u = weights(rng, (N, K), escapes=False)
+    u.reshape(-1)[3::173] = 0x5F80
+    m = r4.R4Linear(r4.transcode(packed_arrays(u)))
+    w = dev(u).view(torch.bfloat16)
+    x = torch.randn((24, K), device="cuda").to(torch.bfloat16)
+    # two slices summed by hand from fp32 partials of cuBLAS on the halves (no split there: K / 2 is short or the rows are padded)
+    half = K // 2
+    if (K // 128) % 2 == 0:
+        xp = torch.zeros((256, K), dtype=torch.bfloat16, device="cuda")
+        xp[:24] = x
+        parts = [torch.mm(xp[:, k0 : k0 + half].contiguous(), w[:, k0 : k0 + half].contiguous().T, out_dtype=torch.float32)[:24] for k0 in (0, half)]
+        by_hand = (parts[0] + parts[1]).to(torch.bfloat16)
+        assert np.array_equal(words(m.mma_rows(x, split=2)), words(by_hand))
+    plan = m.mirror_cublas(rows=(8, 16, 64, 128))
+    assert all(v is not None for v in plan.values()), plan
+    for M in plan:
+        xm = torch.randn((M, K), device="cuda").to(torch.bfloat16)
+        assert np.array_equal(words(m.mma_rows(xm)), words(xm @ w.T)), (M, plan[M])
+    with pytest.raises(RuntimeError):
+        ck.r4_mma(m._a, x, N, K, split=7)  # 7 does not divide the tile count
+
+
 def test_many_rows_rebuild_path():
     from binade_b200.cuda import r4
 
