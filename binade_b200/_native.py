@@ -45,6 +45,7 @@ _SIGNATURES = {
         "bn_f1_to_r4": [_vp, _vp, _u64, _vp, _vp, _u64, _vp, _vp, _i64, _i64, _vp, _vp, _vp, _vp, _u64, _vp, _vp, _vp],
         "bn_r4_gather_grouped": [_vp, C.POINTER(R4Struct), _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _vp, _vp, _vp],
         "bn_push_gather": [_vp, _vp, _int, _vp, _u64, _vp, _int, _int, _vp, _vp],
+        "bn_push_gather_beside": [_vp, _vp, _int, _vp, _u64, _vp, _int, _int, _vp, _vp],
         "bn_r4_mma": [_vp, _i64, C.POINTER(R4Struct), _i64, _i64, _i64, _vp, _i64, _vp],
         "bn_r4_mma_split": [_vp, _i64, C.POINTER(R4Struct), _i64, _i64, _i64, _vp, _i64, _int, _vp],
         "bn_r4_rows": [_vp, _i64, C.POINTER(R4Struct), _i64, _i64, _i64, _vp, _i64, _vp],

@@ -111,6 +111,88 @@ __global__ void __launch_bounds__(1024, 1) push_gather_kernel(PushArgs a) {
   for (uint64_t i = threadIdx.x; i < total16; i += blockDim.x) to[i] = __ldcv(from + i);  // peers wrote it: no stale cache line
 }
 
+// ---- the same exchange as three small kernels, for a stream of its own beside other work. The
+// fused kernel above holds an SM (1024 threads) for as long as its peer is late, and next to
+// this library's matvec blocks nothing that large fits, so that SM's next matvec block waits
+// with it. Here the stores and the copy-out are grids of 128-thread blocks with at most 40
+// registers a thread, which fit beside the largest matvec block (832 threads x 72 registers),
+// and the wait on the peers' flags is a single warp. `counter` holds four words for this form:
+// [0] the call number (advanced by the last block of the last kernel), [1] and [3] tickets of the
+// two grids (reset by their last block), [2] whether the wait succeeded.
+constexpr int XCH_SMALL_THREADS = 128, XCH_SMALL_BLOCKS = 16;
+
+__device__ __forceinline__ uint32_t call_number(const uint32_t *counter) { return *reinterpret_cast<const volatile uint32_t *>(counter) + 1u; }
+
+__global__ void __launch_bounds__(XCH_SMALL_THREADS, 12) push_stores_kernel(PushArgs a) {
+  asm volatile("griddepcontrol.wait;" ::: "memory");  // the slices are the previous kernel's output
+  const uint32_t seq = call_number(a.counter);
+  const uint64_t area_at = XCH_DATA_OFFSET + (uint64_t)(seq & 1u) * a.area;
+  const uint64_t first = (uint64_t)blockIdx.x * XCH_SMALL_THREADS + threadIdx.x, step = (uint64_t)gridDim.x * XCH_SMALL_THREADS;
+  for (int g = 0; g < a.segments; g++) {
+    const uint64_t n16 = a.bytes[g] / 16, at = area_at + a.base[g] + (uint64_t)a.rank * a.bytes[g];
+    const uint4 *src = reinterpret_cast<const uint4 *>(a.local[g]);
+    for (uint64_t i0 = first; i0 < n16; i0 += 4 * step) {  // four loads in flight per thread
+      uint4 v[4];
+#pragma unroll
+      for (int j = 0; j < 4; j++)
+        if (i0 + j * step < n16) v[j] = src[i0 + j * step];
+      for (int p = 0; p < a.world; p++) {
+        uint4 *dst = reinterpret_cast<uint4 *>(a.peer[(a.rank + p) % a.world] + at);
+#pragma unroll
+        for (int j = 0; j < 4; j++)
+          if (i0 + j * step < n16) dst[i0 + j * step] = v[j];
+      }
+    }
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const uint32_t ticket = atomicAdd(a.counter + 1, 1u);
+    if (ticket == gridDim.x - 1) {  // every block's stores are out: tell the peers
+      __threadfence_system();
+      a.counter[1] = 0;
+      for (int p = 0; p < a.world; p++) st_release_sys(reinterpret_cast<uint32_t *>(a.peer[p]) + a.rank, seq);
+    }
+  }
+}
+
+__global__ void __launch_bounds__(32) push_wait_kernel(PushArgs a) {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  const uint32_t seq = call_number(a.counter);
+  const uint32_t *mine = reinterpret_cast<const uint32_t *>(a.peer[a.rank]);
+  int ok = 1;
+  if ((int)threadIdx.x < a.world) ok = wait_reached(mine + threadIdx.x, seq, a.wait_ns) ? 1 : 0;
+  ok = __all_sync(0xFFFFFFFFu, ok);
+  if (threadIdx.x == 0) a.counter[2] = (uint32_t)ok;
+}
+
+__global__ void __launch_bounds__(XCH_SMALL_THREADS, 12) push_collect_kernel(PushArgs a) {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  const uint32_t seq = call_number(a.counter);
+  if (*reinterpret_cast<const volatile uint32_t *>(a.counter + 2)) {
+    const uint64_t area_at = XCH_DATA_OFFSET + (uint64_t)(seq & 1u) * a.area;
+    const uint4 *from = reinterpret_cast<const uint4 *>(a.peer[a.rank] + area_at);
+    uint4 *to = reinterpret_cast<uint4 *>(a.out);
+    const uint64_t total16 = (a.base[a.segments - 1] + (uint64_t)a.world * a.bytes[a.segments - 1]) / 16;
+    const uint64_t first = (uint64_t)blockIdx.x * XCH_SMALL_THREADS + threadIdx.x, step = (uint64_t)gridDim.x * XCH_SMALL_THREADS;
+    for (uint64_t i0 = first; i0 < total16; i0 += 4 * step) {  // peers wrote it: no stale cache line
+      uint4 v[4];
+#pragma unroll
+      for (int j = 0; j < 4; j++)
+        if (i0 + j * step < total16) v[j] = __ldcv(from + i0 + j * step);
+#pragma unroll
+      for (int j = 0; j < 4; j++)
+        if (i0 + j * step < total16) to[i0 + j * step] = v[j];
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    const uint32_t ticket = atomicAdd(a.counter + 3, 1u);
+    if (ticket == gridDim.x - 1) a.counter[3] = 0, a.counter[0] = seq;  // the call is over
+  }
+}
+
 int exchange_status(int *status) {
   BN_CUDA(cudaMemcpyFromSymbol(status, g_exchange_error, sizeof(int)));
   return BN_OK;
@@ -124,7 +206,7 @@ int exchange_status_reset() {
 
 }  // namespace bn
 
-extern "C" int bn_push_gather(const void *const *locals, const uint64_t *bytes, int segments, const uint64_t *peers, uint64_t area_bytes, void *out, int rank, int world, uint32_t *counter, void *stream) {
+static int push_gather(bool beside, const void *const *locals, const uint64_t *bytes, int segments, const uint64_t *peers, uint64_t area_bytes, void *out, int rank, int world, uint32_t *counter, void *stream) {
   if (!locals || !bytes || !peers || !out || !counter || world < 1 || world > bn::XCH_MAX_RANKS || rank < 0 || rank >= world || segments < 1 || segments > bn::XCH_MAX_SEGMENTS)
     return bn::fail(BN_ERR_ARG, "bn_push_gather: bad rank, world (1..8), segment count (1..8) or null pointer");
   bn::PushArgs a{};
@@ -147,8 +229,25 @@ extern "C" int bn_push_gather(const void *const *locals, const uint64_t *bytes, 
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;  // its launch overlaps the tail of the kernel that produces the slices
   cfg.attrs = attr, cfg.numAttrs = 1;
-  BN_CUDA(cudaLaunchKernelEx(&cfg, bn::push_gather_kernel, a));
-  return bn::launched("push_gather_kernel");
+  if (!beside) {
+    BN_CUDA(cudaLaunchKernelEx(&cfg, bn::push_gather_kernel, a));
+    return bn::launched("push_gather_kernel");
+  }
+  cfg.gridDim = dim3(bn::XCH_SMALL_BLOCKS), cfg.blockDim = dim3(bn::XCH_SMALL_THREADS);
+  BN_CUDA(cudaLaunchKernelEx(&cfg, bn::push_stores_kernel, a));
+  cfg.gridDim = dim3(1), cfg.blockDim = dim3(32);
+  BN_CUDA(cudaLaunchKernelEx(&cfg, bn::push_wait_kernel, a));
+  cfg.gridDim = dim3(bn::XCH_SMALL_BLOCKS), cfg.blockDim = dim3(bn::XCH_SMALL_THREADS);
+  BN_CUDA(cudaLaunchKernelEx(&cfg, bn::push_collect_kernel, a));
+  return bn::launched("push_collect_kernel");
+}
+
+extern "C" int bn_push_gather(const void *const *locals, const uint64_t *bytes, int segments, const uint64_t *peers, uint64_t area_bytes, void *out, int rank, int world, uint32_t *counter, void *stream) {
+  return push_gather(false, locals, bytes, segments, peers, area_bytes, out, rank, world, counter, stream);
+}
+
+extern "C" int bn_push_gather_beside(const void *const *locals, const uint64_t *bytes, int segments, const uint64_t *peers, uint64_t area_bytes, void *out, int rank, int world, uint32_t *counter, void *stream) {
+  return push_gather(true, locals, bytes, segments, peers, area_bytes, out, rank, world, counter, stream);
 }
 
 extern "C" int bn_set_wait_limit_ns(uint64_t ns) {

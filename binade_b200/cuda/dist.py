@@ -124,7 +124,7 @@ class PushGather:
         self.buf.zero_()
         self.handle = symm_mem.rendezvous(self.buf, group)
         self.peers = (ctypes.c_uint64 * self.world)(*[int(p) for p in self.handle.buffer_ptrs])
-        self.counter = torch.zeros(1, dtype=torch.int32, device=dev)
+        self.counter = torch.zeros(4, dtype=torch.int32, device=dev)  # call number; the three-kernel form also keeps two tickets and the wait's outcome here
         self.group, self.dead = group, False
         torch.cuda.synchronize()
         dist.barrier(group)  # every buffer is zeroed before anyone's first flag arrives
@@ -148,9 +148,10 @@ class PushGather:
             _native.call("cuda", "bn_device_status_reset")
             raise RuntimeError(f"a bounded wait of the peer-store exchange ran out (device status {int(flag.item()):#x} on some rank): the gathered data is incomplete; this exchange is retired")
 
-    def _push(self, pieces):
+    def _push(self, pieces, beside: bool = False):
         """One exchange of 1..8 contiguous device tensors (16-byte aligned, sizes a multiple of
-        16 bytes): returns, per piece, the uint8 view [world, bytes] of the gathered slices."""
+        16 bytes): returns, per piece, the uint8 view [world, bytes] of the gathered slices.
+        beside: the three-small-kernels form, for an exchange on a stream of its own."""
         import ctypes
 
         from .kernels import _call, _p
@@ -161,7 +162,7 @@ class PushGather:
         n = len(pieces)
         ptrs = (ctypes.c_void_p * n)(*[t.data_ptr() for t in pieces])
         lens = (ctypes.c_uint64 * n)(*sizes)
-        _call("bn_push_gather", ctypes.cast(ptrs, ctypes.c_void_p), ctypes.cast(lens, ctypes.c_void_p), n, ctypes.cast(self.peers, ctypes.c_void_p), self.area, _p(self.out), self.rank, self.world, _p(self.counter))
+        _call("bn_push_gather_beside" if beside else "bn_push_gather", ctypes.cast(ptrs, ctypes.c_void_p), ctypes.cast(lens, ctypes.c_void_p), n, ctypes.cast(self.peers, ctypes.c_void_p), self.area, _p(self.out), self.rank, self.world, _p(self.counter))
         out, at = [], 0
         for sz in sizes:
             out.append(self.out[at : at + self.world * sz].view(self.world, sz))
@@ -172,7 +173,7 @@ class PushGather:
     def _pushable(t: torch.Tensor) -> bool:
         return t.is_contiguous() and t.data_ptr() % 16 == 0 and (t.numel() * t.element_size()) % 16 == 0 and t.numel() > 0
 
-    def gather_rows(self, ys):
+    def gather_rows(self, ys, beside: bool = False):
         """Single-row slices ys[j] [.., w_j] (one row each) of 1..8 projections -> their full
         rows [.., world * w_j], written by the kernel in their final layout: the results are
         views of this rank's buffer, no copy before or after. None if a slice cannot be pushed
@@ -180,7 +181,7 @@ class PushGather:
         takes another route."""
         if self.dead or not 1 <= len(ys) <= 8 or any(y.numel() != y.shape[-1] or not self._pushable(y) for y in ys):
             return None
-        return [g.view(y.dtype).reshape(*y.shape[:-1], self.world * y.shape[-1]) for g, y in zip(self._push(list(ys)), ys)]
+        return [g.view(y.dtype).reshape(*y.shape[:-1], self.world * y.shape[-1]) for g, y in zip(self._push(list(ys), beside), ys)]
 
     def __call__(self, flat: torch.Tensor) -> torch.Tensor:
         if self.dead:
@@ -223,7 +224,7 @@ def make_exchange(group=None, max_bytes: int = 1 << 20):
     return ex if int(flag.item()) == 1 else None
 
 
-def gather_all(slices, group=None, exchange=None, stream=None):
+def gather_all(slices, group=None, exchange=None, stream=None, _beside: bool = False):
     """One collective for up to eight single-row slices [.., w_j] of evenly sharded projections:
     returns their full rows [.., world * w_j] in rank order = row order. Through the peer-store
     kernel when an exchange is given and the slices can be pushed as they are, else one library
@@ -243,9 +244,9 @@ def gather_all(slices, group=None, exchange=None, stream=None):
         for y in slices:
             y.record_stream(stream)
         with torch.cuda.stream(stream):
-            return gather_all(slices, group, exchange)
+            return gather_all(slices, group, exchange, _beside=True)
     if exchange is not None:
-        fast = exchange.gather_rows(list(slices))
+        fast = exchange.gather_rows(list(slices), _beside)
         if fast is not None:
             return fast
     widths = [y.shape[-1] for y in slices]

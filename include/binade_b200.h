@@ -281,6 +281,15 @@ int bn_r4_gather_grouped(const uint16_t *x, const bn_r4 *w, const uint32_t *xi, 
 int bn_push_gather(const void *const *locals, const uint64_t *bytes, int segments,
                    const uint64_t *peers, uint64_t area_bytes, void *out, int rank, int world,
                    uint32_t *counter, void *stream);
+/* The same exchange for a stream of its own, beside other kernels (the next products overlap
+ * it): three small launches instead of one kernel that holds an SM while its peer is late: the
+ * stores and the copy-out as grids of 128-thread blocks that fit on an SM next to this library's
+ * largest matvec block, the wait on the peers' flags as a single warp. `counter` points at FOUR
+ * zeroed uint32 here (call number, two tickets, the wait's outcome); one set of buffers may mix
+ * both forms. */
+int bn_push_gather_beside(const void *const *locals, const uint64_t *bytes, int segments,
+                          const uint64_t *peers, uint64_t area_bytes, void *out, int rank, int world,
+                          uint32_t *counter, void *stream);
 
 /* Device-side status of the calling thread's current device: 0, or non-zero once a kernel of
  * this library gave up a bounded wait or refused a launch whose shared-memory window did not
