@@ -452,6 +452,18 @@ def run_ours(args) -> dict | None:
         per_shape[name] = {"us": round(us, 2), "gbs": round(nbytes / us / 1e3, 1), "pct_of_8tbs": round(nbytes / us / 1e3 / NOMINAL_HBM_GBS * 100, 1), "bf16_gemv_us": round(us_bf16, 2), "speedup_vs_bf16": round(us_bf16 / us, 3)}
         del dense, outs
 
+    # with several GPUs: every rank's own step without the exchange (the four local launches, same
+    # rotation), so that the loss against one GPU can be split into the slowest GPU's pace and the
+    # exchange's cost
+    local_by_rank = None
+    if world > 1:
+        local_groups_all = [[r4.R4LinearGroup([by_name[nm][2][c] for nm in g]) for g in groups] for c in range(copies)]
+        us_local = graph_us(lambda i: [grp(xs[k_]) for grp, k_ in zip(local_groups_all[i % copies], group_k)], iters=120)
+        every = [torch.zeros(1, device=dev) for _ in range(world)]
+        dist.all_gather(every, torch.tensor([us_local], device=dev))
+        local_by_rank = [round(float(t.item()), 2) for t in every]
+        del local_groups_all
+
     # the step's four launches, each alone (same rotation)
     per_launch = {}
     for gi, g in enumerate(groups if not args.quick else []):
@@ -577,6 +589,7 @@ def run_ours(args) -> dict | None:
         "parity": parity,
         "shapes": per_shape,
         "launches": per_launch,
+        "local_step_us_by_rank": local_by_rank,
         "speedup_vs_bf16_gemv_per_token": round(sum(v["bf16_gemv_us"] for v in per_shape.values()) / sum(v["us"] for v in per_shape.values()), 3) if per_shape else None,
         "expander": {"ms_per_layer": round(expand_ms, 3), "gbs": round(expand_bytes / expand_ms / 1e6, 1), "algorithmic_bytes": expand_bytes, "esc_columns_ms_per_layer": round(columns_ms, 3), "host_pack_s": round(host_pack_s, 2), "host_pack_cores": cpu_cores(), "gpu_pack_s": round(gpu_pack_s, 4)},
         "roofline": {"bound": "hbm", "kernel": f"r4_oct_kernel (all {len(groups)} launches of a step), averaged over them", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"], "peak_source": peaks["source"], "bytes_per_launch": per_launch_bytes, "traffic": per_launch_bytes * NCU_TRAFFIC_RATIO, "traffic_source": "assumed, not measured in this run: DRAM read + write bytes of one ncu capture of the same kernel on the gate matrix, scaled to the average launch by its bytes"},

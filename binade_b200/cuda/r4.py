@@ -33,7 +33,7 @@ FUSED_MAX_ROWS = 4  # input rows served by the fused decode kernel in the docume
 MMA_MAX_ROWS = 256  # input rows served by the tensor-core decode GEMM (one pass over the weights; 256 is the MMA's widest N); beyond, rebuild + cuBLAS
 
 
-MMA_MAX_PASSES = 2  # passes of MMA_MAX_ROWS rows that still beat rebuild + cuBLAS (15360 x 3840: 55 us a pass against 108 us for the rebuild)
+MMA_MAX_PASSES = 1  # passes of MMA_MAX_ROWS rows that still beat rebuild + cuBLAS (15360 x 3840: 55 us a pass against 44 us for the rebuild: beyond one pass the rebuild wins)
 
 
 class BinadeLinear(nn.Module):
