@@ -95,10 +95,10 @@ __global__ void __launch_bounds__(1024, 1) push_gather_kernel(PushArgs a) {
       }
     }
   }
-  __threadfence_system();
-  __syncthreads();
+  __syncthreads();  // every thread's stores are ordered before the fences of the threads that raise the flags
   uint32_t *const mine = reinterpret_cast<uint32_t *>(a.peer[a.rank]);
   if ((int)threadIdx.x < a.world) {
+    __threadfence_system();
     st_release_sys(reinterpret_cast<uint32_t *>(a.peer[threadIdx.x]) + a.rank, seq);  // done[rank] on peer
     if (!wait_reached(mine + threadIdx.x, seq, a.wait_ns)) s_ok = 0;
   }
@@ -144,9 +144,12 @@ __global__ void __launch_bounds__(XCH_SMALL_THREADS, 12) push_stores_kernel(Push
       }
     }
   }
-  __threadfence_system();
+  // (one system-scope fence by the thread that raises the flags, after a barrier and a ticket
+  // that order every thread's stores before it: a system-scope fence per thread, 2048 of them a
+  // call, slowed the products running beside this kernel by five microseconds a step)
   __syncthreads();
   if (threadIdx.x == 0) {
+    __threadfence();
     const uint32_t ticket = atomicAdd(a.counter + 1, 1u);
     if (ticket == gridDim.x - 1) {  // every block's stores are out: tell the peers
       __threadfence_system();
