@@ -51,10 +51,15 @@ __device__ __forceinline__ uint64_t global_ns() {
   return t;
 }
 
-__device__ __forceinline__ void st_release_sys(uint32_t *p, uint32_t v) { asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory"); }
-__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t *p) {
+// Flags are written and polled with relaxed system-scope accesses; the ordering comes from one
+// system-scope fence before the flag stores (release side) and one after the flag was seen
+// (acquire side). Release stores and acquire loads carry a fence each, and system-scope fences
+// are not local events: issued per flag, or per poll of a spinning wait, they slow the kernels
+// running beside the exchange.
+__device__ __forceinline__ void st_relaxed_sys(uint32_t *p, uint32_t v) { asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory"); }
+__device__ __forceinline__ uint32_t ld_relaxed_sys(const uint32_t *p) {
   uint32_t v;
-  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
   return v;
 }
 // Waits until *p has reached `want` (counters only grow; the difference is taken modulo 2^32),
@@ -64,7 +69,10 @@ __device__ __forceinline__ bool wait_reached(const uint32_t *p, uint32_t want, u
   for (;;) {
 #pragma unroll 1
     for (int i = 0; i < 64; i++)
-      if ((int32_t)(ld_acquire_sys(p) - want) >= 0) return true;
+      if ((int32_t)(ld_relaxed_sys(p) - want) >= 0) {
+        __threadfence_system();  // acquire: the peer's data stores are visible to what follows
+        return true;
+      }
     if (global_ns() - t0 > limit_ns) break;
   }
   atomicExch(&g_exchange_error, 1);
@@ -99,7 +107,7 @@ __global__ void __launch_bounds__(1024, 1) push_gather_kernel(PushArgs a) {
   uint32_t *const mine = reinterpret_cast<uint32_t *>(a.peer[a.rank]);
   if ((int)threadIdx.x < a.world) {
     __threadfence_system();
-    st_release_sys(reinterpret_cast<uint32_t *>(a.peer[threadIdx.x]) + a.rank, seq);  // done[rank] on peer
+    st_relaxed_sys(reinterpret_cast<uint32_t *>(a.peer[threadIdx.x]) + a.rank, seq);  // done[rank] on peer
     if (!wait_reached(mine + threadIdx.x, seq, a.wait_ns)) s_ok = 0;
   }
   __syncthreads();
@@ -154,7 +162,7 @@ __global__ void __launch_bounds__(XCH_SMALL_THREADS, 12) push_stores_kernel(Push
     if (ticket == gridDim.x - 1) {  // every block's stores are out: tell the peers
       __threadfence_system();
       a.counter[1] = 0;
-      for (int p = 0; p < a.world; p++) st_release_sys(reinterpret_cast<uint32_t *>(a.peer[p]) + a.rank, seq);
+      for (int p = 0; p < a.world; p++) st_relaxed_sys(reinterpret_cast<uint32_t *>(a.peer[p]) + a.rank, seq);
     }
   }
 }
