@@ -172,6 +172,19 @@ __device__ __forceinline__ void mma_store_side(const MmaArgs &a, const MmaWindow
   tc_fence_after();
   const int r = (int)(warp * 32 + lane);
   if (!ok) return;
+  if (a.split == 1) {  // the common case, kept free of the slice loop
+    for (int c = 0; c < a.BN; c += 8) {
+      uint32_t v[8];
+      asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+                   : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7])
+                   : "r"(tmem + ((warp * 32u) << 16) + (uint32_t)c));
+      asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+      for (int i = 0; i < 8; i++)
+        if (c + i < a.M && r < rows) a.y[(int64_t)(c + i) * a.y_stride + row_base + r] = f32_to_bf16_bits(__uint_as_float(v[i]));
+    }
+    return;
+  }
   for (int c = 0; c < a.BN; c += 8) {
     float sum[8];
     for (int sl = 0; sl < a.split; sl++) {  // the slices' sums, added in slice order
