@@ -1,19 +1,23 @@
 // Fused R4-decode GEMM for up to 256 input rows on the 5th-generation tensor cores (tcgen05):
 //   Y[m, n] = sum_k X[m, k] W[n, k]      X [M, K] BF16, W [N, K] in R4, Y [M, N] BF16
 // computed as D = W_tile . X^T so that the few input rows sit in the MMA's N dimension:
-//   A operand  up to 112 weight rows x 128 k, decoded from R4 to BF16 by the CUDA cores straight
+//   A operand  a block's weight rows x 128 k, decoded from R4 to BF16 by the CUDA cores straight
 //              into shared memory in the tensor core's K-major 128-byte-swizzled layout
 //   B operand  BN = M rounded up to 16 input rows x 128 k, brought in by TMA (2-D tensor map over
 //              X with the same swizzle; rows past M and columns past K arrive as zeros)
 //   D          128 x BN fp32 accumulators in tensor memory (TMEM), read back with tcgen05.ld
-// One block per SM, each with an equal share of the weight rows. 14 warps decode (8 rows each
-// per stage: a weight row stays with one warp, so its escape cursor is a register; raw bytes and
-// codes are fetched two stages ahead into registers), one warp issues the TMA copies and the
-// MMAs; a ring of stages (mbarriers: `full` armed by the decoders and the TMA bytes, `empty` by
-// tcgen05.commit) lets decode run ahead. The weights are read once whatever M. Accumulation order
-// inside an MMA is the hardware's: this path is not bit-identical to the documented lane order of
-// the one-row kernels (the outputs are checked against an fp32 reference to one BF16 unit in the
-// last place).
+// One block per SM, each with an equal share of the weight rows; one warp issues the TMA copies
+// and the MMAs; a ring of stages (mbarriers: `full` armed by the decoders and the TMA bytes,
+// `empty` by tcgen05.commit) lets decode run ahead. Two decode sides:
+//   r4_mma_oct_kernel  up to 128 input rows, K % 16 == 0: 26 warps, eight threads per weight row,
+//                      private cp.async rings (the batch-1 matvec's decode, oct.cuh)
+//   r4_mma_kernel      the rest: 14 warps, a warp per row and stage, 8 rows each, raw bytes and
+//                      codes fetched two stages ahead into registers
+// The weights are read once whatever M. The sum over K is the hardware's: 16 k per MMA step, in
+// order, from zero, in fp32: not the documented lane order of the one-row kernels, but the
+// order of cuBLAS's BF16 GEMM on this GPU, whose outputs this kernel reproduces bit for bit;
+// where cuBLAS splits K, `split` slices are summed in accumulators of their own and added in
+// slice order by the epilogue (bn_r4_mma_split).
 //
 // Every wait is bounded: when one gives up, a status flag is set, every thread still reaches the
 // end of the kernel, and the tensor memory is released.

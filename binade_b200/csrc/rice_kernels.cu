@@ -6,7 +6,8 @@
 //   low plane     n*k bits, bit b of weight i at i*k + b
 //   unary planes  j = 0 .. qmax-1: one bit per weight still alive (q >= j), set iff q > j
 // The bit offset of a lane inside a plane is the number of alive weights before it: a warp
-// prefix sum over per-lane alive counts, done with three ballots.
+// prefix sum over per-lane alive counts, done with three ballots. The expander of matrices with
+// many rows maps several rows to a warp instead (rice_r4_wide_kernel, further down).
 #include <atomic>
 
 #include "common.cuh"
