@@ -13,8 +13,10 @@ Before anything is timed, every matrix of the workload is checked at full size a
 oracle: the expander's arrays, the dense decode and the matvec, bit for bit.
 
 With N > 1 (launched by torch.distributed.run, one rank per GPU) every rank holds its own row
-shard of an N-times taller layer (same per-GPU work: weak scaling) and all-gathers each group's
-outputs inside the timed step; the gathered vectors are checked on every rank.
+shard of an N-times taller layer (same per-GPU work: weak scaling) and all-gathers the step's
+seven output slices with one exchange per step inside the timed region, on a second stream so
+that it overlaps the next step's products; the gathered vectors are checked on every rank,
+before the timing (eager steps) and after it (what the timed graphs left in their buffers).
 """
 
 from __future__ import annotations
