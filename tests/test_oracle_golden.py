@@ -142,3 +142,30 @@ def test_format1_oracle_against_reference_vectors(name):
         o.np_f1_decode(meta, idx, esc[:-1], table, *w.shape)
     with pytest.raises(ValueError):
         o.np_f1_decode(meta, idx[:-4], esc, table, *w.shape)
+
+
+def test_esc_columns_restatement_against_a_plain_loop():
+    """oracle.esc_columns (the definition the GPU builder is checked against) itself, against a
+    weight-by-weight walk of the R4 arrays on a tensor dense with escapes and a short last tile."""
+    rng = np.random.default_rng(5)
+    R, K = 9, 272
+    u = rng.integers(0, 1 << 16, size=(R, K), dtype=np.uint16)
+    a = o.pack_r4(u)
+    esc_cols, col_esc = o.esc_columns(a)
+    T = -(-K // 128)
+    codes = a["codes"].reshape(R, T * 32)
+    n = a["esc"].size - 1
+    assert n > 100 and esc_cols.size == n + 8 and not esc_cols[n:].any()
+    for r in range(R):
+        cursor = int(a["row_esc"][r])
+        buckets = [[] for _ in range(16)]
+        for k in range(T * 128):
+            if (int(codes[r, k // 4]) >> (4 * (k % 4))) & 15 == 15:
+                buckets[(k % 128) // 8].append(int(a["esc"][cursor]))
+                cursor += 1
+        start = 0
+        for c in range(16):
+            assert int(col_esc[r, c]) == start, (r, c)
+            at = int(a["row_esc"][r]) + start
+            assert list(esc_cols[at : at + len(buckets[c])]) == buckets[c], (r, c)
+            start += len(buckets[c])
