@@ -268,3 +268,20 @@ def test_gpu_only_paths_fail_loudly_without_a_device():
         unpack.unpack({k: g[k] for k in ("raw", "table", "meta", "bits", "roff")})
     with pytest.raises(NotImplementedError):
         unpack.PackedModel(GOLDEN / "packed_model" / "packed", gpu=False)
+
+
+def test_cli_pack_writes_both_formats(tmp_path):
+    """`python -m binade_b200.cli pack SRC --out DIR [--format 1]`: the command line reaches the
+    packer with its options, and the shards are the golden ones."""
+    import subprocess
+    import sys
+
+    src = _source_model(tmp_path)
+    for version, want in (("2", "packed"), ("1", "packed_v1")):
+        out = tmp_path / f"cli{version}"
+        r = subprocess.run([sys.executable, "-m", "binade_b200.cli", "pack", str(src), "--out", str(out), "--format", version], cwd=ROOT, capture_output=True, text=True)
+        assert r.returncode == 0, r.stderr
+        assert "bits/weight" in r.stdout
+        assert (out / "model.safetensors").read_bytes() == (GOLDEN / "packed_model" / want / "model.safetensors").read_bytes()
+    bad = subprocess.run([sys.executable, "-m", "binade_b200.cli", "frobnicate"], cwd=ROOT, capture_output=True, text=True)
+    assert bad.returncode != 0 and "usage" in (bad.stderr + bad.stdout)
